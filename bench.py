@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the lightning-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C2|C3|C4]
+
+One "step" is one pass of the hot path over one batch of synthetic input.  The default workload
+is configuration 2 (lasd forward + backward, bf16, B=8 N=8192 H=32 D=E=128, per-head decay,
+fp32 initial state); C3 (lavd fwd+bwd) and C4 (64-token decode loop) can be selected.  With
+N > 1 GPUs (torchrun, one rank per GPU) every rank runs its own batch of the same shape -- the
+(batch, head) pairs are independent recurrences, so there is no data-path collective -- and the
+reported value is the total over ranks divided by the slowest rank's time (weak scaling).
+
+Rank 0 prints ONE JSON line.  `value` is timed with inputs resident in HBM; `e2e` repeats the
+measurement through the public Python API with pinned HOST buffers, host->device copies of all
+inputs and device->host copies of all outputs inside the timed region.  `roofline` is for the
+dominant kernel, `cpu_baseline` times the CPU oracle (a port of the reference's torch operators)
+on a bounded slice of the same workload on the host cores.
+
+--impl reference times the reference's own CPU algorithm (the oracle port under oracle/; the
+reference checkout itself does not travel to the GPU box) on the same configuration.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------------------------
+def make_workload(name, rank):
+    from xopes_b200 import workloads as W
+    cfg = dict(W.CONFIGS[name])
+    seed = rank  # every rank draws its own batch
+    if name == "C2":
+        w = W.lasd_inputs(cfg["B"], cfg["N"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, seed)
+        tokens = cfg["B"] * cfg["N"]
+        alg_bytes = tokens * cfg["H"] * (W.BYTES_LASD_FWD + W.BYTES_LASD_BWD)
+        units = "tokens"
+    elif name == "C3":
+        w = W.lavd_inputs(cfg["B"], cfg["N"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, seed)
+        tokens = cfg["B"] * cfg["N"]
+        alg_bytes = tokens * cfg["H"] * (W.BYTES_LAVD_FWD + W.BYTES_LAVD_BWD)
+        units = "tokens"
+    elif name == "C4":
+        w = W.decode_inputs(cfg["B"], cfg["H"], cfg["D"], cfg["E"], cfg["steps"], False, seed=seed)
+        tokens = cfg["B"] * cfg["steps"]
+        alg_bytes = cfg["steps"] * W.decode_bytes_per_step(cfg["B"], cfg["H"], cfg["D"], cfg["E"], False)
+        units = "tokens"
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    return cfg, w, tokens, alg_bytes, units
+
+
+def pin(t):
+    return t.contiguous().pin_memory()
+
+
+class LasdStep:
+    """Configuration 2: forward + backward of lasd through the public API."""
+    launches_per_step = 4  # o pass, dq pass, dk pass, dv pass
+
+    def __init__(self, w, dev):
+        import xopes_b200 as xb
+        self.xb = xb
+        self.dev = dev
+        self.host = {k: pin(v) for k, v in w.items()}
+        self.d = {k: v.to(dev, non_blocking=True) for k, v in self.host.items()}
+        self.h2d = sum(v.numel() * v.element_size() for v in self.host.values())
+        self.out_host = None
+
+    def _fb(self, d):
+        q, k, v = (d[x].requires_grad_() for x in ("q", "k", "v"))
+        o, sf = self.xb.lightning_attn_func(q, k, v, ld=d["ld"], initial_state=d["initial_state"],
+                                            decay_type="scalar")
+        o.backward(d["do"])
+        res = (o.detach(), sf, q.grad, k.grad, v.grad)
+        q.grad = k.grad = v.grad = None
+        return res
+
+    def step(self):
+        return self._fb(self.d)
+
+    def step_e2e(self):
+        d = {k: v.to(self.dev, non_blocking=True) for k, v in self.host.items()}
+        res = self._fb(d)
+        if self.out_host is None:
+            self.out_host = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
+        for hbuf, r in zip(self.out_host, res):
+            hbuf.copy_(r, non_blocking=True)
+        self.d2h = sum(r.numel() * r.element_size() for r in res)
+        return res
+
+
+class LavdStep(LasdStep):
+    launches_per_step = 6  # o, dq, dk, dv passes + log-decay reverse cumsum (+ state term)
+
+    def _fb(self, d):
+        q, k, v, ldk = (d[x].requires_grad_() for x in ("q", "k", "v", "ldk"))
+        o, sf = self.xb.lightning_attn_func(q, k, v, ldk=ldk, decay_type="vector")
+        o.backward(d["do"])
+        res = (o.detach(), sf, q.grad, k.grad, v.grad, ldk.grad)
+        q.grad = k.grad = v.grad = ldk.grad = None
+        return res
+
+
+class DecodeStep:
+    """Configuration 4: one step = the 64-token decode loop, state carried in place."""
+
+    def __init__(self, w, dev):
+        import xopes_b200 as xb
+        self.xb = xb
+        self.dev = dev
+        self.ld = w["ld"].to(dev)
+        self.state0 = w["state"].to(dev)
+        self.state = self.state0.clone()
+        self.host_toks = [{k: pin(v) for k, v in t.items()} for t in w["steps"]]
+        self.toks = [{k: v.to(dev) for k, v in t.items()} for t in self.host_toks]
+        self.launches_per_step = len(self.toks)
+        b, _, h, e = self.toks[0]["v"].shape
+        self.o = torch.empty(len(self.toks), b, 1, h, e, dtype=torch.bfloat16, device=dev)
+        self.h2d = sum(v.numel() * v.element_size() for t in self.host_toks for v in t.values())
+        self.out_host = torch.empty(self.o.shape, dtype=self.o.dtype, pin_memory=True)
+        self.d2h = self.o.numel() * self.o.element_size()
+
+    def step(self):
+        for i, t in enumerate(self.toks):
+            self.xb.lasd_decode_step(t["q"], t["k"], t["v"], self.ld, self.state, out=self.o[i])
+        return self.o
+
+    def step_e2e(self):
+        for i, t in enumerate(self.host_toks):
+            q, k, v = (t[x].to(self.dev, non_blocking=True) for x in ("q", "k", "v"))
+            self.xb.lasd_decode_step(q, k, v, self.ld, self.state, out=self.o[i])
+        self.out_host.copy_(self.o, non_blocking=True)
+        return self.o
+
+
+def time_steps(fn, steps, warmup, world, sampler=None):
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, clocks
+
+
+# --------------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference's torch operators)
+# --------------------------------------------------------------------------------------------
+def cpu_slice_tokens_per_s(name, cfg, seed=0):
+    """Times the CPU oracle on a bounded slice of the workload and scales to the full
+    configuration: (b,h) pairs are independent, so the full job costs (B*H / slice pairs) times
+    the slice.  Returns (tokens/s for the full configuration, description, seconds spent)."""
+    from oracle import lightning_attn_oracle as orc
+    from xopes_b200 import workloads as W
+    threads = torch.get_num_threads()
+    if name == "C2":
+        bs, hs, n = 1, 2, cfg["N"]
+        w = W.lasd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
+        f = {k: v.float() for k, v in w.items()}
+        ld = f["ld"]
+        t0 = time.perf_counter()
+        orc.lasd_forward(f["q"], f["k"], f["v"], ld, f["initial_state"])
+        orc.lasd_backward(f["q"], f["k"], f["v"], ld, f["do"], f["initial_state"], None)
+        dt = time.perf_counter() - t0
+        scale = cfg["B"] * cfg["H"] / (bs * hs)
+        val = cfg["B"] * cfg["N"] / (dt * scale)
+        sample = (f"oracle lasd fwd+bwd on a (B={bs},H={hs},N={n}) slice, {dt:.1f} s; scaled by "
+                  f"B*H/{bs * hs}={scale:.0f} (independent (b,h) recurrences)")
+    elif name == "C3":
+        bs, hs, n = 1, 2, 4096
+        w = W.lavd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
+        f = {k: v.float() for k, v in w.items()}
+        t0 = time.perf_counter()
+        orc.lavd_forward(f["q"], f["k"], f["v"], f["ldk"], None)
+        orc.lavd_backward(f["q"], f["k"], f["v"], f["ldk"], None, f["do"])
+        dt = time.perf_counter() - t0
+        scale = cfg["B"] * cfg["H"] / (bs * hs) * (cfg["N"] / n)
+        val = cfg["B"] * cfg["N"] / (dt * scale)
+        sample = (f"oracle lavd fwd+bwd on a (B={bs},H={hs},N={n}) slice, {dt:.1f} s; scaled by "
+                  f"{scale:.0f} (pairs x sequence length; cost is linear in N)")
+    else:  # C4
+        steps = 8
+        w = W.decode_inputs(cfg["B"], cfg["H"], cfg["D"], cfg["E"], steps, False, seed=seed)
+        st = w["state"]
+        t0 = time.perf_counter()
+        for t in w["steps"]:
+            _, st = orc.decode_step_scalar(t["q"].float(), t["k"].float(), t["v"].float(), w["ld"], st)
+        dt = time.perf_counter() - t0
+        val = cfg["B"] * steps / dt
+        sample = f"oracle decode, {steps} of {cfg['steps']} steps at full batch, {dt:.1f} s"
+    return val, sample, threads
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's CPU algorithm for the path (oracle port; the reference is
+    Python + Triton and its checkout is not present on the GPU box) on the host cores."""
+    if rank != 0:
+        return
+    from xopes_b200 import workloads as W
+    cfg = dict(W.CONFIGS[args.workload])
+    torch.set_num_threads(os.cpu_count() or 1)
+    vals = []
+    t_all0 = time.perf_counter()
+    total = args.warmup + args.steps
+    sample = ""
+    for i in range(total):
+        val, sample, threads = cpu_slice_tokens_per_s(args.workload, cfg, seed=i)
+        if i >= args.warmup:
+            vals.append(val)
+        if time.perf_counter() - t_all0 > 240 and len(vals) >= 1:
+            break  # keep the whole run within a few minutes
+    val = sum(vals) / len(vals)
+    tokens = cfg["B"] * (cfg.get("N") or cfg.get("steps"))
+    line = {
+        "impl": "reference", "metric": metric_name(args.workload), "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": len(vals), "warmup": args.warmup,
+        "ms_per_step": tokens / val * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, cfg, world),
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def metric_name(workload):
+    return {"C2": "lasd fwd+bwd tokens/s (bf16 N8K H32 D128)",
+            "C3": "lavd fwd+bwd tokens/s (bf16 N16K H16 D128)",
+            "C4": "decode tokens/s (B256 H32 D128, 64-step loop)"}[workload]
+
+
+def workload_config(name, cfg, world):
+    c = {"workload": f"{name}: " + {
+        "C2": "lasd forward+backward, per-head scalar decay, fp32 initial state",
+        "C3": "lavd forward+backward, ldk = logsigmoid(x)/16, no initial state",
+        "C4": "recurrent decode, scalar decay, 64-step loop, fp32 state in place"}[name]}
+    c.update({k: v for k, v in cfg.items() if k != "kind"})
+    c["partition"] = f"batch x head, one full batch per GPU, {world} GPU(s), no collective"
+    c["l2"] = "inputs per step exceed the 126 MB L2 (no flush needed)"
+    return c
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="C2", choices=["C2", "C3", "C4"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+
+    cfg, w, tokens, alg_bytes, _ = make_workload(args.workload, rank)
+    runner = {"C2": LasdStep, "C3": LavdStep, "C4": DecodeStep}[args.workload](w, dev)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, clocks = time_steps(runner.step, args.steps, warmup, world, sampler)
+    ms_step = ms / args.steps
+    value = tokens * world / (ms_step * 1e-3)
+
+    e2e = None
+    if not args.no_e2e:
+        ms_e, _ = time_steps(runner.step_e2e, max(2, args.steps // 3), 1, world)
+        ms_e /= max(2, args.steps // 3)
+        e2e = {"value": tokens * world / (ms_e * 1e-3), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(runner.h2d), "d2h_bytes_per_step": int(runner.d2h),
+               "ms_per_step": ms_e}
+
+    if rank == 0:
+        from xopes_b200 import _lib
+        peaks = measured_peaks()
+        launches = runner.launches_per_step
+        per_launch_bytes = alg_bytes / launches
+        per_launch_s = ms_step * 1e-3 / launches
+        achieved = per_launch_bytes / per_launch_s / 1e9
+        tensor_path = None
+        if args.workload == "C2":
+            tensor_path = _lib.load().la_lasd_path(cfg["N"], cfg["D"], cfg["E"], _lib.LA_BF16, 0)
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "peak_source": peaks["source"],
+                "kernel": {"C2": "chunk_pass_kernel" if tensor_path == 1 else "scan_kernel",
+                           "C3": "scan_kernel", "C4": "decode_kernel"}[args.workload],
+                "algorithmic_bytes_per_launch": per_launch_bytes,
+                "avg_launch_ms": per_launch_s * 1e3}
+        line = {
+            "metric": metric_name(args.workload), "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.workload, cfg, world),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            val, sample, threads = cpu_slice_tokens_per_s(args.workload, cfg)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": threads,
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

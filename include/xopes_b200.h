@@ -1,0 +1,139 @@
+/*
+ * xopes_b200 -- C ABI of the B200 (sm_100a) lightning-attention library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * i.e. a cudaStream_t), enqueues work on that stream and returns immediately: nothing here
+ * allocates, frees, synchronises or throws.  The caller owns every buffer.  The return value is
+ * LA_OK or a negative LA_ERR_* code; la_status_string() turns it into text.
+ *
+ * Tensor layout (same as the reference operators): q, k are (B, N, H, D), v, o are (B, N, H, E),
+ * row-major and contiguous; recurrent states are (B, H, D, E) fp32, contiguous.  `dtype` is the
+ * element type of q, k, v, o, do, dq, dk, dv.  Log decays and states are always fp32.
+ * With cu_seqlens (int64, device memory, M+1 entries, first 0, last N) B must be 1 and the M
+ * documents are independent sequences: states are (M, H, D, E).
+ *
+ * Citations name files of the reference project (Doraemonzzz/xopes) by their path in that
+ * project; they say which reference interface each entry point stands in for.
+ */
+#ifndef XOPES_B200_H_
+#define XOPES_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LA_API __attribute__((visibility("default")))
+#else
+#define LA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LA_OK 0
+#define LA_ERR_NULL_POINTER (-1)   /* a required pointer is NULL                                  */
+#define LA_ERR_BAD_SHAPE (-2)      /* a size is <= 0, or B != 1 with cu_seqlens                    */
+#define LA_ERR_UNSUPPORTED (-3)    /* dtype / head dimension outside what the kernels cover        */
+#define LA_ERR_CUDA (-4)           /* a CUDA runtime or driver call failed (launch, tensor map)    */
+#define LA_ERR_TOO_LARGE (-5)      /* a size exceeds a documented fixed maximum                    */
+#define LA_ERR_MISALIGNED (-6)     /* a pointer is not aligned as the chosen kernel requires       */
+#define LA_ERR_WORKSPACE (-7)      /* workspace pointer NULL or too small                          */
+
+enum la_dtype { LA_F32 = 0, LA_BF16 = 1, LA_F16 = 2 };
+
+/* flags for the lasd/lavd entry points */
+#define LA_FLAG_FORCE_RECURRENCE 1u /* never take the tcgen05 chunk kernels                       */
+#define LA_FLAG_REQUIRE_TENSOR 2u   /* fail with LA_ERR_UNSUPPORTED instead of taking the scan     */
+
+/* Library identification; bumps when the ABI changes. */
+LA_API int la_abi_version(void);
+LA_API const char *la_status_string(int status);
+
+/* Which kernel family a call with these parameters runs: 1 = tcgen05/TMA chunk kernels,
+ * 0 = fp32 CUDA-core scan kernels, negative = LA_ERR_*.  Pure host logic, no CUDA call. */
+LA_API int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned flags);
+
+/* Device-side watchdog word.  The tcgen05 kernels bound every mbarrier wait; a wait that runs
+ * out records a non-zero code here and the kernel returns early.  la_device_status() copies the
+ * word of the current device to the host (this one call synchronises the stream it is given). */
+LA_API int la_device_status(void *stream, int *status_out);
+LA_API int la_device_status_clear(void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Scalar decay (lasd).  ld is fp32 and addressed as ld[b*ld_sb + n*ld_sn + h*ld_sh] (element
+ * strides), so (B,N,H) tensors, (H,) per-head vectors (strides 0,0,1) and expanded views all work.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Forward: o and final_state from q, k, v, ld and an optional initial_state.
+ * Stands in for lasd_parallel_fwd (xopes/ops/lightning_attn/scalar_decay/lasd_parallel_triton.py:474-565)
+ * and, with LA_FLAG_FORCE_RECURRENCE or N == 1, lasd_recurrence_fwd
+ * (xopes/ops/lightning_attn/scalar_decay/lasd_recurrence_triton.py:116-164).
+ * initial_state and final_state may be NULL.  M is the number of documents (0 without cu_seqlens). */
+LA_API int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                int64_t ld_sn, int64_t ld_sh, const float *initial_state,
+                const int64_t *cu_seqlens, void *o, float *final_state, int64_t B, int64_t N,
+                int64_t H, int64_t D, int64_t E, int64_t M, int dtype, unsigned flags,
+                void *stream);
+
+/* Bytes of scratch la_lasd_bwd needs (0 when dld is not requested). */
+LA_API int64_t la_lasd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                                    int64_t M, int want_dld);
+
+/* Backward: dq, dk, dv (dtype), and optionally dld (fp32, contiguous (B,N,H)) and dinitial_state
+ * (fp32) from the forward inputs, do and an optional dfinal_state.  Recomputes the forward states.
+ * Stands in for lasd_parallel_bwd (scalar_decay/lasd_parallel_triton.py:569-754) and
+ * lasd_recurrence_bwd (scalar_decay/lasd_recurrence_triton.py:405-498).
+ * dld == NULL skips the log-decay gradient; workspace may then be NULL. */
+LA_API int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
+                const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
+                void *dv, float *dld, float *dinitial_state, void *workspace,
+                int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                int64_t M, int dtype, unsigned flags, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Vector decay (lavd).  ldk (B,N,H,D) and ldv (B,N,H,E) are fp32, contiguous; either may be NULL
+ * (not both).
+ * ------------------------------------------------------------------------------------------- */
+
+/* Stands in for lavd_parallel_fwd (xopes/ops/lightning_attn/vector_decay/lavd_parallel_triton.py:879-992)
+ * and lavd_recurrence_fwd (vector_decay/lavd_recurrence_triton.py:157-218). */
+LA_API int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
+                const float *initial_state, const int64_t *cu_seqlens, void *o,
+                float *final_state, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                int64_t M, int dtype, unsigned flags, void *stream);
+
+/* Bytes of scratch la_lavd_bwd needs when dfinal_state is given (one recomputed final state). */
+LA_API int64_t la_lavd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                                    int64_t M);
+
+/* Stands in for lavd_parallel_bwd (vector_decay/lavd_parallel_triton.py:996-1290) and
+ * lavd_recurrence_bwd (vector_decay/lavd_recurrence_triton.py:530-713).
+ * dldk (B,N,H,D) / dldv (B,N,H,E) are fp32 outputs, required exactly when ldk / ldv is given;
+ * they double as the kernels' accumulation buffers.  workspace is needed only with
+ * dfinal_state (it receives the recomputed final state for the log-decay gradient). */
+LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
+                const float *initial_state, const void *d_o, const float *dfinal_state,
+                const int64_t *cu_seqlens, void *dq, void *dk, void *dv, float *dldk, float *dldv,
+                float *dinitial_state, void *workspace, int64_t workspace_bytes, int64_t B,
+                int64_t N, int64_t H, int64_t D, int64_t E, int64_t M, int dtype, unsigned flags,
+                void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Single-token decode: one new token per sequence, state read, updated and written once.
+ * q, k (B,1,H,D), v, o (B,1,H,E); state_in / state_out (B,H,D,E) fp32 and MAY alias (in place).
+ * Stand in for _lasd_recurrence_fwd with N == 1 (scalar_decay/lasd_recurrence_triton.py:28-113)
+ * and _lavd_recurrence_fwd with N == 1 (vector_decay/lavd_recurrence_triton.py:28-154).
+ * ------------------------------------------------------------------------------------------- */
+LA_API int la_decode_scalar(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                     int64_t ld_sh, const float *state_in, float *state_out, void *o, int64_t B,
+                     int64_t H, int64_t D, int64_t E, int dtype, void *stream);
+
+LA_API int la_decode_vector(const void *q, const void *k, const void *v, const float *ldk,
+                     const float *ldv, const float *state_in, float *state_out, void *o,
+                     int64_t B, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XOPES_B200_H_ */

@@ -1,0 +1,297 @@
+"""GPU parity: the CUDA path (through the Python mirror of the reference interface, which calls the
+C ABI) against the committed reference vectors and against the CPU oracle on seeded inputs.
+
+Tolerances: relative L2 <= 1e-5 for fp32 outputs, <= 1e-2 for 16-bit outputs, gradients and
+final states."""
+import pytest
+import torch
+
+from oracle import lightning_attn_oracle as orc
+from util import TOL_BF16, TOL_FP32, assert_close, golden_cases, load_golden
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def cuda(g):
+    return {k: v.to(DEV) for k, v in g.items()}
+
+
+def leaf(t, dtype=None):
+    t = t.detach().clone()
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(DEV).requires_grad_()
+
+
+# ------------------------------------------------------------------------------------------------
+# golden vectors (outputs of the reference's torch operators), fp32
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("which", ["parallel", "recurrence", "fn"])
+@pytest.mark.parametrize("case", golden_cases("lasd_"))
+def test_lasd_golden(case, which):
+    import xopes_b200 as xb
+    fn = {"parallel": xb.lasd_parallel_triton, "recurrence": xb.lasd_recurrence_triton,
+          "fn": xb.lasd_fn}[which]
+    g = load_golden(case)
+    q, k, v, ld = leaf(g["q"]), leaf(g["k"]), leaf(g["v"]), leaf(g["ld"])
+    s0 = leaf(g["initial_state"]) if "initial_state" in g else None
+    cu = g["cu_seqlens"].to(DEV) if "cu_seqlens" in g else None
+    o, sf = fn(q, k, v, ld, initial_state=s0, cu_seqlens=cu)
+    assert_close("o", g["o"], o, TOL_FP32)
+    assert_close("final_state", g["final_state"], sf, TOL_FP32)
+    loss = (o * g["do"].to(DEV)).sum()
+    if "dfinal_state" in g:
+        loss = loss + (sf * g["dfinal_state"].to(DEV)).sum()
+    loss.backward()
+    for n, x in (("dq", q), ("dk", k), ("dv", v), ("dld", ld)):
+        assert_close(n, g[n], x.grad, TOL_FP32)
+    if s0 is not None:
+        assert_close("dinitial_state", g["dinitial_state"], s0.grad, TOL_FP32)
+
+
+@pytest.mark.parametrize("which", ["parallel", "recurrence"])
+@pytest.mark.parametrize("case", golden_cases("lavd_"))
+def test_lavd_golden(case, which):
+    import xopes_b200 as xb
+    fn = {"parallel": xb.lavd_parallel_triton, "recurrence": xb.lavd_recurrence_triton}[which]
+    g = load_golden(case)
+    q, v, ldk = leaf(g["q"]), leaf(g["v"]), leaf(g["ldk"])
+    k = leaf(g["k"]) if "k" in g else None
+    ldv = leaf(g["ldv"]) if "ldv" in g else None
+    s0 = leaf(g["initial_state"]) if "initial_state" in g else None
+    cu = g["cu_seqlens"].to(DEV) if "cu_seqlens" in g else None
+    o, sf = fn(q, k, v, ldk=ldk, ldv=ldv, initial_state=s0, cu_seqlens=cu)
+    assert_close("o", g["o"], o, TOL_FP32)
+    assert_close("final_state", g["final_state"], sf, TOL_FP32)
+    loss = (o * g["do"].to(DEV)).sum()
+    if "dfinal_state" in g:
+        loss = loss + (sf * g["dfinal_state"].to(DEV)).sum()
+    loss.backward()
+    assert_close("dq", g["dq"], q.grad, TOL_FP32)
+    assert_close("dv", g["dv"], v.grad, TOL_FP32)
+    assert_close("dldk", g["dldk"], ldk.grad, TOL_FP32)
+    if k is not None:
+        assert_close("dk", g["dk"], k.grad, TOL_FP32)
+    if ldv is not None:
+        assert_close("dldv", g["dldv"], ldv.grad, TOL_FP32)
+    if s0 is not None:
+        assert_close("dinitial_state", g["dinitial_state"], s0.grad, TOL_FP32)
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference's own test shapes (tests/lightning_attn/scalar_decay/test.py:13-32), seeded inputs
+# ------------------------------------------------------------------------------------------------
+def _lasd_seeded(b, n, h, d, e, seed, dtype, use_state, use_dfinal, weak_decay):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, n, h, d, generator=g) * d ** -0.5
+    k = torch.randn(b, n, h, d, generator=g) * d ** -0.5
+    v = torch.randn(b, n, h, e, generator=g)
+    if weak_decay:  # the reference test's decay: logsigmoid((1 + 0.01*randn) * 10)
+        ld = torch.nn.functional.logsigmoid((1 + 0.01 * torch.randn(b, n, h, generator=g)) * 10)
+    else:
+        ld = torch.nn.functional.logsigmoid(torch.randn(b, n, h, generator=g) + 2.0)
+    s0 = 0.1 * torch.randn(b, h, d, e, generator=g) if use_state else None
+    do = torch.randn(b, n, h, e, generator=g)
+    dsf = torch.randn(b, h, d, e, generator=g) if use_dfinal else None
+    cast = lambda t: t.to(dtype).float()  # noqa: E731  values exactly representable in dtype
+    return cast(q), cast(k), cast(v), ld, s0, cast(do), dsf
+
+
+def _run_lasd_case(fn, b, n, h, d, e, seed, dtype, use_state, use_dfinal, weak_decay, tol):
+    qf, kf, vf, ld, s0, dof, dsf = _lasd_seeded(b, n, h, d, e, seed, dtype, use_state, use_dfinal,
+                                                weak_decay)
+    q, k, v, ldc = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ld)
+    s0c = leaf(s0) if use_state else None
+    o, sf = fn(q, k, v, ldc, initial_state=s0c)
+    assert o.dtype == dtype and sf.dtype == torch.float32
+    ro, rsf = orc.lasd_forward(qf, kf, vf, ld, s0)
+    assert_close("o", ro, o.float(), tol)
+    assert_close("final_state", rsf, sf, tol)
+    loss = (o.float() * dof.to(DEV)).sum()
+    if use_dfinal:
+        loss = loss + (sf * dsf.to(DEV)).sum()
+    loss.backward()
+    rq, rk, rv, rld, rs0 = orc.lasd_backward(qf, kf, vf, ld, dof, s0, dsf)
+    assert_close("dq", rq, q.grad.float(), tol)
+    assert_close("dk", rk, k.grad.float(), tol)
+    assert_close("dv", rv, v.grad.float(), tol)
+    assert_close("dld", rld, ldc.grad, tol)
+    if use_state:
+        assert_close("dinitial_state", rs0, s0c.grad, tol)
+
+
+REF_SHAPES = [(2, 256, 8, 128, 64), (2, 257, 8, 64, 32), (2, 65, 7, 33, 63), (2, 270, 8, 64, 32),
+              (1, 300, 3, 255, 257), (2, 128, 4, 128, 128)]
+
+
+@pytest.mark.parametrize("shape", REF_SHAPES)
+@pytest.mark.parametrize("use_state,use_dfinal", [(True, True), (False, False)])
+def test_lasd_reference_shapes_fp32(shape, use_state, use_dfinal):
+    import xopes_b200 as xb
+    _run_lasd_case(xb.lasd_parallel_triton, *shape, seed=2024, dtype=torch.float32,
+                   use_state=use_state, use_dfinal=use_dfinal, weak_decay=True, tol=TOL_FP32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 300, 4, 128, 128), (1, 128, 2, 128, 128), (2, 200, 3, 64, 64),
+                                   (1, 1, 2, 128, 128), (1, 513, 2, 128, 128)])
+def test_lasd_16bit(shape, dtype):
+    import xopes_b200 as xb
+    _run_lasd_case(xb.lasd_fn, *shape, seed=7, dtype=dtype, use_state=True, use_dfinal=True,
+                   weak_decay=False, tol=TOL_BF16)
+
+
+def test_config1_fp32_forward():
+    """Benchmark configuration 1 in full: B2 N512 H8 D=E=64 fp32, per-head decay, no initial state."""
+    import xopes_b200 as xb
+    from xopes_b200 import workloads
+    w = workloads.lasd_inputs(2, 512, 8, 64, 64, dtype=torch.float32, seed=0, decay_step=1.0,
+                              use_state=False, use_do=False)
+    o, sf = xb.lightning_attn_func(w["q"].to(DEV), w["k"].to(DEV), w["v"].to(DEV),
+                                   ld=w["ld"].to(DEV), decay_type="scalar")
+    ro, rsf = orc.lasd_forward(w["q"], w["k"], w["v"], w["ld"])
+    assert_close("o", ro, o, TOL_FP32)
+    assert_close("final_state", rsf, sf, TOL_FP32)
+    # the default decay type ("constant") takes the same (H,) vector
+    o2, sf2 = xb.lightning_attn_func(w["q"].to(DEV), w["k"].to(DEV), w["v"].to(DEV), ld=w["ld"].to(DEV))
+    assert torch.equal(o, o2) and torch.equal(sf, sf2)
+
+
+def test_per_head_decay_gradient_is_summed():
+    import xopes_b200 as xb
+    b, n, h, d, e = 2, 70, 3, 32, 32
+    qf, kf, vf, _, s0, dof, dsf = _lasd_seeded(b, n, h, d, e, 5, torch.float32, True, True, False)
+    ld_h = torch.log(1 - 2.0 ** (-3 - torch.arange(h, dtype=torch.float32)))
+    q, k, v, ld = leaf(qf), leaf(kf), leaf(vf), leaf(ld_h)
+    o, sf = xb.lasd_fn(q, k, v, ld, initial_state=s0.to(DEV))
+    ((o * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    full = ld_h.view(1, 1, h).expand(b, n, h)
+    _, _, _, rld, _ = orc.lasd_backward(qf, kf, vf, full, dof, s0, dsf)
+    assert_close("dld", rld.sum((0, 1)), ld.grad, TOL_FP32)
+
+
+def test_broadcast_initial_state_and_unused_state_output():
+    import xopes_b200 as xb
+    b, n, h, d, e = 3, 40, 2, 16, 16
+    qf, kf, vf, ld, _, dof, _ = _lasd_seeded(b, n, h, d, e, 9, torch.float32, False, False, False)
+    s0 = 0.1 * torch.randn(h, d, e, generator=torch.Generator().manual_seed(1))
+    q, k, v, s0c = leaf(qf), leaf(kf), leaf(vf), leaf(s0)
+    o, _ = xb.lasd_fn(q, k, v, ld.to(DEV), initial_state=s0c)
+    (o * dof.to(DEV)).sum().backward()
+    ro, _ = orc.lasd_forward(qf, kf, vf, ld, s0)
+    assert_close("o", ro, o, TOL_FP32)
+    rq, rk, rv, _, rs0 = orc.lasd_backward(qf, kf, vf, ld, dof, s0.unsqueeze(0).expand(b, h, d, e))
+    assert_close("dq", rq, q.grad, TOL_FP32)
+    assert_close("dinitial_state", rs0.sum(0), s0c.grad, TOL_FP32)
+
+
+# ------------------------------------------------------------------------------------------------
+# vector decay, seeded
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16)])
+@pytest.mark.parametrize("use_ldv", [False, True])
+@pytest.mark.parametrize("shape", [(2, 130, 2, 64, 32), (1, 257, 2, 128, 128), (2, 65, 3, 33, 63)])
+def test_lavd_seeded(shape, use_ldv, dtype, tol):
+    import xopes_b200 as xb
+    b, n, h, d, e = shape
+    g = torch.Generator().manual_seed(31)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    qf = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    kf = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    vf = cast(torch.randn(b, n, h, e, generator=g))
+    ldk = torch.nn.functional.logsigmoid(torch.randn(b, n, h, d, generator=g))
+    ldv = torch.nn.functional.logsigmoid(torch.randn(b, n, h, e, generator=g) + 1) if use_ldv else None
+    s0 = 0.1 * torch.randn(b, h, d, e, generator=g)
+    dof = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = torch.randn(b, h, d, e, generator=g)
+    q, k, v, lk, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ldk), leaf(s0)
+    lv = leaf(ldv) if use_ldv else None
+    o, sf = xb.lavd_fn(q, k, v, ldk=lk, ldv=lv, initial_state=s0c)
+    ro, rsf = orc.lavd_forward(qf, kf, vf, ldk, ldv, s0)
+    assert_close("o", ro, o.float(), tol)
+    assert_close("final_state", rsf, sf, tol)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rlk, rlv, rs0 = orc.lavd_backward(qf, kf, vf, ldk, ldv, dof, s0, dsf)
+    assert_close("dq", rq, q.grad.float(), tol)
+    assert_close("dk", rk, k.grad.float(), tol)
+    assert_close("dv", rv, v.grad.float(), tol)
+    assert_close("dldk", rlk, lk.grad, tol)
+    if use_ldv:
+        assert_close("dldv", rlv, lv.grad, tol)
+    assert_close("dinitial_state", rs0, s0c.grad, tol)
+
+
+# ------------------------------------------------------------------------------------------------
+# varlen
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_FP32), (torch.bfloat16, TOL_BF16)])
+def test_lasd_varlen_documents_are_independent(dtype, tol):
+    import xopes_b200 as xb
+    lens = [1, 127, 128, 129, 300, 5, 256]
+    n, h, d, e = sum(lens), 2, 128, 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    qf, kf, vf, ld, _, dof, _ = _lasd_seeded(1, n, h, d, e, 3, dtype, False, False, False)
+    g = torch.Generator().manual_seed(4)
+    s0 = 0.1 * torch.randn(len(lens), h, d, e, generator=g)
+    dsf = torch.randn(len(lens), h, d, e, generator=g)
+    q, k, v, ldc, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ld), leaf(s0)
+    o, sf = xb.lasd_fn(q, k, v, ldc, initial_state=s0c, cu_seqlens=cu.to(DEV))
+    ro, rsf = orc.lasd_forward(qf, kf, vf, ld, s0, cu)
+    assert_close("o", ro, o.float(), tol)
+    assert_close("final_state", rsf, sf, tol)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rld, rs0 = orc.lasd_backward(qf, kf, vf, ld, dof, s0, dsf, cu)
+    assert_close("dq", rq, q.grad.float(), tol)
+    assert_close("dk", rk, k.grad.float(), tol)
+    assert_close("dv", rv, v.grad.float(), tol)
+    assert_close("dld", rld, ldc.grad, tol)
+    assert_close("dinitial_state", rs0, s0c.grad, tol)
+
+
+# ------------------------------------------------------------------------------------------------
+# decode
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("vector", [False, True])
+@pytest.mark.parametrize("shape", [(4, 3, 128, 128), (2, 2, 64, 32), (2, 2, 33, 256)])
+def test_decode_loop_in_place(shape, vector):
+    """A short decode loop (configuration 4 scaled down): bf16 tokens, fp32 state carried in place;
+    the oracle sees fp32 up-casts of the same bf16 inputs so that it carries an fp32 state too."""
+    import xopes_b200 as xb
+    from xopes_b200 import workloads
+    b, h, d, e = shape
+    w = workloads.decode_inputs(b, h, d, e, steps=5, vector=vector, seed=0)
+    state = w["state"].to(DEV).clone()
+    rstate = w["state"].clone()
+    for t in w["steps"]:
+        q, k, v = t["q"].to(DEV), t["k"].to(DEV), t["v"].to(DEV)
+        if vector:
+            o, s2 = xb.lavd_decode_step(q, k, v, t["ldk"].to(DEV), state)
+            ro, rstate = orc.decode_step_vector(t["q"].float(), t["k"].float(), t["v"].float(),
+                                                t["ldk"], rstate)
+        else:
+            o, s2 = xb.lasd_decode_step(q, k, v, w["ld"].to(DEV), state)
+            ro, rstate = orc.decode_step_scalar(t["q"].float(), t["k"].float(), t["v"].float(),
+                                                w["ld"], rstate)
+        assert s2.data_ptr() == state.data_ptr()
+        assert_close("o", ro, o.float(), TOL_BF16)
+        assert_close("state", rstate, state, TOL_FP32)
+
+
+def test_decode_matches_fn_with_one_token():
+    import xopes_b200 as xb
+    from xopes_b200 import workloads
+    w = workloads.decode_inputs(3, 2, 128, 128, steps=1, vector=True, seed=1)
+    t = w["steps"][0]
+    q, k, v, ldk = (t[x].to(DEV) for x in ("q", "k", "v", "ldk"))
+    s = w["state"].to(DEV)
+    o1, s1 = xb.lavd_fn(q, k, v, ldk=ldk, initial_state=s)
+    o2, s2 = xb.lavd_decode_step(q, k, v, ldk, s, inplace=False)
+    assert_close("o", o1.float(), o2.float(), 1e-6)
+    assert_close("state", s1, s2, 1e-6)
+    ld = w["ld"].to(DEV)
+    o1, s1 = xb.lasd_fn(q, k, v, ld, initial_state=s)
+    o2, s2 = xb.lasd_decode_step(q, k, v, ld, s, inplace=False)
+    assert_close("o", o1.float(), o2.float(), 1e-6)
+    assert_close("state", s1, s2, 1e-6)

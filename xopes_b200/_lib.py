@@ -1,0 +1,91 @@
+"""ctypes binding of libxopes_b200.so (the C ABI declared in include/xopes_b200.h).
+
+There is no fallback: if the shared library is missing the import of any operator raises, and
+every operator refuses non-CUDA tensors.  Build the library with `python -m xopes_b200.build`.
+"""
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libxopes_b200.so")
+
+LA_F32, LA_BF16, LA_F16 = 0, 1, 2
+FLAG_FORCE_RECURRENCE = 1
+FLAG_REQUIRE_TENSOR = 2
+
+_DTYPES = {torch.float32: LA_F32, torch.bfloat16: LA_BF16, torch.float16: LA_F16}
+
+_vp, _i64, _i32, _u32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint
+
+# name -> (restype, argtypes); mirrors include/xopes_b200.h one to one
+SIGNATURES = {
+    "la_abi_version": (_i32, []),
+    "la_status_string": (ctypes.c_char_p, [_i32]),
+    "la_lasd_path": (_i32, [_i64, _i64, _i64, _i32, _u32]),
+    "la_device_status": (_i32, [_vp, ctypes.POINTER(_i32)]),
+    "la_device_status_clear": (_i32, [_vp]),
+    "la_lasd_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
+                           _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_lasd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
+    "la_lasd_bwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                           _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32,
+                           _vp]),
+    "la_lavd_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                           _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_lavd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64]),
+    "la_lavd_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                           _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_decode_scalar": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp,
+                                _i64, _i64, _i64, _i64, _i32, _vp]),
+    "la_decode_vector": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                _i64, _i64, _i64, _i64, _i32, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library (once) and declare every entry point's signature."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. "
+            "Run `python -m xopes_b200.build` (needs nvcc). There is no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float32, bfloat16 or float16")
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("xopes_b200 operators run on CUDA tensors only (no CPU fallback)")
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        msg = load().la_status_string(rc).decode()
+        raise RuntimeError(f"{what} failed: {msg} (status {rc})")

@@ -1,0 +1,349 @@
+// extern "C" entry points: argument checks, choice of kernel family, pass orchestration.
+#include "chunk.cuh"
+#include "scan.cuh"
+
+namespace la {
+
+__device__ int g_status_word = 0;
+
+int *status_word_ptr() {
+  static int *ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int *>(p);
+  }
+  return ptrs[dev];
+}
+
+namespace {
+
+bool dtype_ok(int dtype) { return dtype == LA_F32 || dtype == LA_BF16 || dtype == LA_F16; }
+
+int check_common(const void *q, const void *k, const void *v, int64_t B, int64_t N, int64_t H,
+                 int64_t D, int64_t E, int64_t M, const int64_t *cu, int dtype) {
+  if (q == nullptr || k == nullptr || v == nullptr) return LA_ERR_NULL_POINTER;
+  if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  if (cu != nullptr && (B != 1 || M <= 0)) return LA_ERR_BAD_SHAPE;
+  if (!dtype_ok(dtype)) return LA_ERR_UNSUPPORTED;
+  if (N > (int64_t)1 << 30 || B > 65535 || H > 65535 || M > 65535) return LA_ERR_TOO_LARGE;
+  return LA_OK;
+}
+
+struct Seq {
+  int B, N, H, D, E, M;
+  const int64_t *cu;
+  int nb() const { return cu ? M : B; }
+};
+
+// The four directional passes expressed on the scan primitive.
+ScanParams base_params(const Seq &s, const float *ld, int64_t sb, int64_t sn, int64_t sh) {
+  ScanParams p;
+  p.B = s.B; p.N = s.N; p.H = s.H; p.M = s.M; p.cu = s.cu;
+  p.ld = ld; p.ld_sb = sb; p.ld_sn = sn; p.ld_sh = sh;
+  return p;
+}
+
+// rows = E (T = S^T): output pass and dv pass
+void rows_e(ScanParams &p, const Seq &s, const float *ldk, const float *ldv) {
+  p.R = s.E; p.C = s.D; p.st_rs = 1; p.st_cs = s.E; p.ldr = ldv; p.ldc = ldk;
+}
+// rows = D (T = S): dq pass and dk pass
+void rows_d(ScanParams &p, const Seq &s, const float *ldk, const float *ldv) {
+  p.R = s.D; p.C = s.E; p.st_rs = s.E; p.st_cs = 1; p.ldr = ldk; p.ldc = ldv;
+}
+
+int scan_forward(const Seq &s, const void *q, const void *k, const void *v, const float *ld,
+                 int64_t sb, int64_t sn, int64_t sh, const float *ldk, const float *ldv,
+                 const float *s0, void *o, float *sfin, int dtype, cudaStream_t st) {
+  ScanParams p = base_params(s, ld, sb, sn, sh);
+  rows_e(p, s, ldk, ldv);
+  p.a = v; p.b = k; p.w = q; p.out = o; p.t0 = s0; p.tfinal = sfin;
+  return launch_scan(p, dtype, st);
+}
+
+}  // namespace
+}  // namespace la
+
+using namespace la;
+
+extern "C" {
+
+int la_abi_version(void) { return 1; }
+
+const char *la_status_string(int status) {
+  switch (status) {
+    case LA_OK: return "ok";
+    case LA_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case LA_ERR_BAD_SHAPE: return "bad shape";
+    case LA_ERR_UNSUPPORTED: return "unsupported dtype or head dimension";
+    case LA_ERR_CUDA: return "CUDA call failed";
+    case LA_ERR_TOO_LARGE: return "size exceeds a fixed maximum";
+    case LA_ERR_MISALIGNED: return "pointer not aligned as required";
+    case LA_ERR_WORKSPACE: return "workspace missing or too small";
+  }
+  return "unknown status";
+}
+
+int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned flags) {
+  if (!dtype_ok(dtype)) return LA_ERR_UNSUPPORTED;
+  const bool tensor = !(flags & LA_FLAG_FORCE_RECURRENCE) && chunk_supported(N, D, E, dtype);
+  if (!tensor && (flags & LA_FLAG_REQUIRE_TENSOR)) return LA_ERR_UNSUPPORTED;
+  return tensor ? 1 : 0;
+}
+
+int la_device_status(void *stream, int *status_out) {
+  if (status_out == nullptr) return LA_ERR_NULL_POINTER;
+  int *p = status_word_ptr();
+  if (p == nullptr) return LA_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(status_out, p, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return LA_ERR_CUDA;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return LA_ERR_CUDA;
+  return LA_OK;
+}
+
+int la_device_status_clear(void *stream) {
+  int *p = status_word_ptr();
+  if (p == nullptr) return LA_ERR_CUDA;
+  if (cudaMemsetAsync(p, 0, sizeof(int), static_cast<cudaStream_t>(stream)) != cudaSuccess) return LA_ERR_CUDA;
+  return LA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// scalar decay
+// ------------------------------------------------------------------------------------------------
+int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                int64_t ld_sn, int64_t ld_sh, const float *initial_state,
+                const int64_t *cu_seqlens, void *o, float *final_state, int64_t B, int64_t N,
+                int64_t H, int64_t D, int64_t E, int64_t M, int dtype, unsigned flags,
+                void *stream) {
+  int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc != LA_OK) return rc;
+  if (o == nullptr || ld == nullptr) return LA_ERR_NULL_POINTER;
+  const int path = la_lasd_path(N, D, E, dtype, flags);
+  if (path < 0) return path;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
+  if (path == 1) {
+    ChunkPass c;
+    c.x = q; c.y = k; c.z = v; c.out = o;
+    c.ld = ld; c.ld_sb = ld_sb; c.ld_sn = ld_sn; c.ld_sh = ld_sh;
+    c.t0 = initial_state; c.tfinal = final_state; c.state_transposed = 0; c.reverse = 0;
+    c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens;
+    return launch_chunk_pass(c, dtype, st);
+  }
+  return scan_forward(s, q, k, v, ld, ld_sb, ld_sn, ld_sh, nullptr, nullptr, initial_state, o,
+                      final_state, dtype, st);
+}
+
+int64_t la_lasd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                                    int64_t M, int want_dld) {
+  if (!want_dld) return 0;
+  const int64_t nb = M > 0 ? M : B;
+  const int nt = scan_row_tiles((int)D, (int)E, (int)H, (int)nb);
+  return ((int64_t)2 * nt * B * N * H + nb * H * D * E) * (int64_t)sizeof(float);
+}
+
+int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
+                const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
+                void *dv, float *dld, float *dinitial_state, void *workspace,
+                int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                int64_t M, int dtype, unsigned flags, void *stream) {
+  int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc != LA_OK) return rc;
+  if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr || ld == nullptr)
+    return LA_ERR_NULL_POINTER;
+  const int path = la_lasd_path(N, D, E, dtype, flags);
+  if (path < 0) return path;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
+  const bool want_dld = dld != nullptr;
+  const int64_t bnh = B * N * H;
+  const int nt = path == 1 ? 1 : scan_row_tiles(s.D, s.E, s.H, s.nb());
+  float *slots_q = nullptr, *slots_k = nullptr, *ws_state = nullptr;
+  if (want_dld) {
+    if (workspace == nullptr ||
+        workspace_bytes < la_lasd_bwd_workspace_bytes(B, N, H, D, E, M, 1))
+      return LA_ERR_WORKSPACE;
+    slots_q = static_cast<float *>(workspace);
+    slots_k = slots_q + (int64_t)nt * bnh;
+    ws_state = slots_k + (int64_t)nt * bnh;
+  }
+  const bool state_term = want_dld && dfinal_state != nullptr;
+
+  if (path == 1) {
+    ChunkPass c;
+    c.ld = ld; c.ld_sb = ld_sb; c.ld_sn = ld_sn; c.ld_sh = ld_sh;
+    c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens;
+    // dq: (X,Y,Z) = (do, v, k), state S^T, forward direction
+    c.x = d_o; c.y = v; c.z = k; c.out = dq; c.t0 = initial_state; c.state_transposed = 1;
+    c.tfinal = state_term ? ws_state : nullptr; c.reverse = 0;
+    c.xrow = want_dld ? q : nullptr; c.rowdot = slots_q;
+    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
+    // dk: (v, do, q), state dS^T, reverse direction
+    c.x = v; c.y = d_o; c.z = q; c.out = dk; c.t0 = dfinal_state; c.state_transposed = 1;
+    c.tfinal = nullptr; c.reverse = 1;
+    c.xrow = want_dld ? k : nullptr; c.rowdot = slots_k;
+    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
+    // dv: (k, q, do), state dS, reverse direction; its end state is d initial_state
+    c.x = k; c.y = q; c.z = d_o; c.out = dv; c.t0 = dfinal_state; c.state_transposed = 0;
+    c.tfinal = dinitial_state; c.reverse = 1; c.xrow = nullptr; c.rowdot = nullptr;
+    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
+  } else {
+    // dq: T = S (rows D): a = k, b = v, w = do
+    ScanParams p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    rows_d(p, s, nullptr, nullptr);
+    p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state;
+    p.tfinal = state_term ? ws_state : nullptr;
+    if (want_dld) { p.x = q; p.xout = slots_q; p.xmode = 1; }
+    if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+    // dk: T = dS (rows D), reverse: a = q, b = do, w = v
+    p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    rows_d(p, s, nullptr, nullptr);
+    p.reverse = 1;
+    p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
+    if (want_dld) { p.x = k; p.xout = slots_k; p.xmode = 1; }
+    if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+    // dv: T = dS^T (rows E), reverse: a = do, b = q, w = k
+    p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    rows_e(p, s, nullptr, nullptr);
+    p.reverse = 1;
+    p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;
+    if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+  }
+  if (want_dld) {
+    rc = launch_dld_scalar(slots_q, nt, slots_k, nt, state_term ? ws_state : nullptr,
+                           dfinal_state, cu_seqlens, dld, s.B, s.N, s.H, s.D * s.E, s.M, st);
+    if (rc != LA_OK) return rc;
+  }
+  return LA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// vector decay
+// ------------------------------------------------------------------------------------------------
+int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
+                const float *initial_state, const int64_t *cu_seqlens, void *o,
+                float *final_state, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                int64_t M, int dtype, unsigned flags, void *stream) {
+  int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc != LA_OK) return rc;
+  if (o == nullptr || (ldk == nullptr && ldv == nullptr)) return LA_ERR_NULL_POINTER;
+  if (flags & LA_FLAG_REQUIRE_TENSOR) return LA_ERR_UNSUPPORTED;
+  Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
+  return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int64_t la_lavd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                                    int64_t M) {
+  (void)N;
+  const int64_t nb = M > 0 ? M : B;
+  return nb * H * D * E * (int64_t)sizeof(float);
+}
+
+int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
+                const float *initial_state, const void *d_o, const float *dfinal_state,
+                const int64_t *cu_seqlens, void *dq, void *dk, void *dv, float *dldk, float *dldv,
+                float *dinitial_state, void *workspace, int64_t workspace_bytes, int64_t B,
+                int64_t N, int64_t H, int64_t D, int64_t E, int64_t M, int dtype, unsigned flags,
+                void *stream) {
+  int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc != LA_OK) return rc;
+  if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return LA_ERR_NULL_POINTER;
+  if (ldk == nullptr && ldv == nullptr) return LA_ERR_NULL_POINTER;
+  if ((ldk != nullptr && dldk == nullptr) || (ldv != nullptr && dldv == nullptr)) return LA_ERR_NULL_POINTER;
+  if (flags & LA_FLAG_REQUIRE_TENSOR) return LA_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
+  float *ws_state = nullptr;
+  if (dfinal_state != nullptr) {
+    if (workspace == nullptr || workspace_bytes < la_lavd_bwd_workspace_bytes(B, N, H, D, E, M))
+      return LA_ERR_WORKSPACE;
+    ws_state = static_cast<float *>(workspace);
+  }
+  ScanParams p;
+  if (ldv != nullptr) {
+    // recompute o only to form o*do for dldv (the reference's optional dldv_o pass,
+    // vector_decay/lavd_parallel_triton.py:1104-1127)
+    p = base_params(s, nullptr, 0, 0, 0);
+    rows_e(p, s, ldk, ldv);
+    p.a = v; p.b = k; p.w = q; p.out = nullptr; p.t0 = initial_state;
+    p.x = d_o; p.xout = dldv; p.xmode = 2;
+    if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+  }
+  // dq
+  p = base_params(s, nullptr, 0, 0, 0);
+  rows_d(p, s, ldk, ldv);
+  p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state; p.tfinal = ws_state;
+  if (ldk != nullptr) { p.x = q; p.xout = dldk; p.xmode = 2; }
+  if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+  // dk
+  p = base_params(s, nullptr, 0, 0, 0);
+  rows_d(p, s, ldk, ldv);
+  p.reverse = 1;
+  p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
+  if (ldk != nullptr) { p.x = k; p.xout = dldk; p.xmode = 3; }
+  if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+  // dv
+  p = base_params(s, nullptr, 0, 0, 0);
+  rows_e(p, s, ldk, ldv);
+  p.reverse = 1;
+  p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;
+  if (ldv != nullptr) { p.x = v; p.xout = dldv; p.xmode = 3; }
+  if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
+  if (ldk != nullptr) {
+    rc = launch_revcumsum_vec(dldk, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.D, s.D,
+                              s.E, 1, s.M, st);
+    if (rc != LA_OK) return rc;
+  }
+  if (ldv != nullptr) {
+    rc = launch_revcumsum_vec(dldv, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.E, s.D,
+                              s.E, 0, s.M, st);
+    if (rc != LA_OK) return rc;
+  }
+  return LA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode
+// ------------------------------------------------------------------------------------------------
+static int decode_common(const void *q, const void *k, const void *v, const float *ld,
+                         int64_t ld_sb, int64_t ld_sh, const float *ldk, const float *ldv,
+                         const float *state_in, float *state_out, void *o, int64_t B, int64_t H,
+                         int64_t D, int64_t E, int dtype, void *stream) {
+  int rc = check_common(q, k, v, B, 1, H, D, E, 0, nullptr, dtype);
+  if (rc != LA_OK) return rc;
+  if (state_in == nullptr || state_out == nullptr || o == nullptr) return LA_ERR_NULL_POINTER;
+  if (B * H > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = launch_decode(q, k, v, ld, ld_sb, ld_sh, ldk, ldv, state_in, state_out, o, (int)B, (int)H,
+                     (int)D, (int)E, dtype, st);
+  if (rc != LA_ERR_UNSUPPORTED && rc != LA_ERR_MISALIGNED) return rc;
+  // shapes the vectorised kernel does not take: same update through the scan kernel (N = 1);
+  // it cannot run in place because tiles of one (b,h) live in different CTAs.
+  if (state_in == state_out) return rc;
+  Seq s{(int)B, 1, (int)H, (int)D, (int)E, 0, nullptr};
+  return scan_forward(s, q, k, v, ld, ld_sb, 0, ld_sh, ldk, ldv, state_in, o, state_out, dtype, st);
+}
+
+int la_decode_scalar(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                     int64_t ld_sh, const float *state_in, float *state_out, void *o, int64_t B,
+                     int64_t H, int64_t D, int64_t E, int dtype, void *stream) {
+  if (ld == nullptr) return LA_ERR_NULL_POINTER;
+  return decode_common(q, k, v, ld, ld_sb, ld_sh, nullptr, nullptr, state_in, state_out, o, B, H, D,
+                       E, dtype, stream);
+}
+
+int la_decode_vector(const void *q, const void *k, const void *v, const float *ldk,
+                     const float *ldv, const float *state_in, float *state_out, void *o,
+                     int64_t B, int64_t H, int64_t D, int64_t E, int dtype, void *stream) {
+  if (ldk == nullptr && ldv == nullptr) return LA_ERR_NULL_POINTER;
+  return decode_common(q, k, v, nullptr, 0, 0, ldk, ldv, state_in, state_out, o, B, H, D, E, dtype,
+                       stream);
+}
+
+}  // extern "C"

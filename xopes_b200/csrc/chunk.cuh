@@ -1,0 +1,35 @@
+// Host-visible interface of the tcgen05 / TMA chunk kernel for scalar decay (chunk_sm100.cu).
+#pragma once
+#include "common.cuh"
+
+namespace la {
+
+// One directional chunk-parallel pass over 128-token chunks, one CTA per (sequence, head),
+// running state T (128x128 fp32) resident in tensor memory:
+//
+//   W_c = [(X_c Y_c^T) (.) M_c] Z_c + diag(s_c) X_c T ;   T <- e^{g_c} T + (Y_c (.) u_c)^T Z_c
+//
+// forward direction: M_ij = e^{c_i-c_j}[i>=j], s = e^{c}, u = e^{g-c}   (c = inclusive cumsum of ld)
+// reverse direction: M_ij = e^{c_j-c_i}[j>=i], s = e^{g-c}, u = e^{c}, chunks visited last to first.
+// (X,Y,Z) = (q,k,v) gives o; (do,v,k) with the state transposed gives dq; (v,do,q) reversed and
+// transposed gives dk; (k,q,do) reversed gives dv
+// (xopes/ops/lightning_attn/scalar_decay/lasd_parallel_triton.py:548-563,651-733).
+struct ChunkPass {
+  const void *x = nullptr, *y = nullptr, *z = nullptr;  // (B,N,H,128) dtype
+  void *out = nullptr;                                   // (B,N,H,128) dtype
+  const void *xrow = nullptr;                            // optional (B,N,H,128): rowdot = sum_f xrow*W
+  float *rowdot = nullptr;                               // (B,N,H) fp32
+  const float *ld = nullptr;
+  int64_t ld_sb = 0, ld_sn = 0, ld_sh = 0;
+  const float *t0 = nullptr;                             // (nb,H,128,128) fp32 or null
+  float *tfinal = nullptr;                               // (nb,H,128,128) fp32 or null
+  int state_transposed = 0;                              // T[i][j] lives at state[j][i]
+  int reverse = 0;
+  const int64_t *cu = nullptr;
+  int B = 0, N = 0, H = 0, M = 0;
+};
+
+bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype);
+int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream);
+
+}  // namespace la

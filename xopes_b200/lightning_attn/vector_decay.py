@@ -1,0 +1,178 @@
+"""Lightning attention with per-token, per-dimension vector decay (lavd) on the CUDA library.
+
+Mirror of xopes/ops/lightning_attn/vector_decay/__init__.py:10-64 and of LavdParallelFunction
+(vector_decay/lavd_parallel_triton.py:1293-1486) / LavdRecurrenceFunction
+(vector_decay/lavd_recurrence_triton.py:716-849): same names, keyword arguments, layout, return
+and gradient order.
+
+Differences, all deliberate:
+  * final_state is returned in fp32 (the reference casts it to q.dtype,
+    vector_decay/lavd_torch.py:97); rounding it to q.dtype reproduces the reference value;
+  * cu_seqlens is honoured (documents independent, state reset at each boundary), where
+    lavd_torch ignores the argument (vector_decay/lavd_torch.py:16);
+  * k=None / v=None ("share" mode: k = 1-exp(ldk), v = 1-exp(ldv), lavd_torch.py:55-63) is
+    expanded here with torch elementwise ops, so autograd adds the chain-rule term
+    dldk += dk * (-exp(ldk)) of lavd_recurrence_triton.py:701-709 by itself.
+"""
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from .scalar_decay import _cu, _prep_state
+
+
+def _ld32(x):
+    if x is None:
+        return None
+    x = x.detach()
+    return (x if x.dtype == torch.float32 else x.float()).contiguous()
+
+
+class LavdFunction(torch.autograd.Function):
+    """forward(q, k, v, ldk, ldv, initial_state, cu_seqlens, flags) -> (o, final_state)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, ldk, ldv, initial_state, cu_seqlens, flags):
+        lib = _lib.load()
+        _lib.require_cuda(q, k, v, ldk, ldv, initial_state, cu_seqlens)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        b, n, h, d = q.shape
+        e = v.shape[-1]
+        cu, m = _cu(cu_seqlens, q.device)
+        if cu is not None and b != 1:
+            raise AssertionError("cu_seqlens is only supported for batch size 1")
+        nb = m if cu is not None else b
+        lk, lv = _ld32(ldk), _ld32(ldv)
+        s0 = None if initial_state is None else initial_state.detach().to(torch.float32).contiguous()
+        o = torch.empty(b, n, h, e, dtype=q.dtype, device=q.device)
+        sf = torch.empty(nb, h, d, e, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            rc = lib.la_lavd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lk), _lib.ptr(lv),
+                                 _lib.ptr(s0), _lib.ptr(cu), _lib.ptr(o), _lib.ptr(sf),
+                                 b, n, h, d, e, m, _lib.dtype_code(q), flags, _lib.stream_of(q))
+        _lib.check(rc, "la_lavd_fwd")
+        ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu)
+        ctx.flags = flags
+        ctx.state_dtype = None if initial_state is None else initial_state.dtype
+        ctx.set_materialize_grads(False)
+        return o, sf
+
+    @staticmethod
+    def backward(ctx, do, dfinal_state):
+        lib = _lib.load()
+        q, k, v, ldk, ldv, s0, cu = ctx.saved_tensors
+        b, n, h, d = q.shape
+        e = v.shape[-1]
+        m = 0 if cu is None else cu.numel() - 1
+        nb = m if cu is not None else b
+        if do is None:
+            do = torch.zeros(b, n, h, e, dtype=q.dtype, device=q.device)
+        do = do.contiguous().to(q.dtype)
+        dsf = None if dfinal_state is None else dfinal_state.to(torch.float32).contiguous()
+        lk, lv = _ld32(ldk), _ld32(ldv)
+        want_ds0 = s0 is not None and ctx.needs_input_grad[5]
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dldk = None if ldk is None else torch.empty(b, n, h, d, dtype=torch.float32, device=q.device)
+        dldv = None if ldv is None else torch.empty(b, n, h, e, dtype=torch.float32, device=q.device)
+        ds0 = torch.empty(nb, h, d, e, dtype=torch.float32, device=q.device) if want_ds0 else None
+        ws, ws_bytes = None, 0
+        if dsf is not None:
+            ws_bytes = lib.la_lavd_bwd_workspace_bytes(b, n, h, d, e, m)
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        with torch.cuda.device(q.device):
+            rc = lib.la_lavd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lk), _lib.ptr(lv),
+                                 _lib.ptr(s0), _lib.ptr(do), _lib.ptr(dsf), _lib.ptr(cu),
+                                 _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dldk),
+                                 _lib.ptr(dldv), _lib.ptr(ds0), _lib.ptr(ws), ws_bytes,
+                                 b, n, h, d, e, m, _lib.dtype_code(q), ctx.flags, _lib.stream_of(q))
+        _lib.check(rc, "la_lavd_bwd")
+        if dldk is not None:
+            dldk = dldk.to(ldk.dtype)
+        if dldv is not None:
+            dldv = dldv.to(ldv.dtype)
+        if want_ds0:
+            ds0 = ds0.to(ctx.state_dtype)
+        return dq, dk, dv, dldk, dldv, ds0, None, None
+
+
+def _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, flags):
+    if ldk is None and ldv is None:
+        raise AssertionError("At least one of ldk or ldv must be used")
+    if k is None:
+        if ldk is None:
+            raise AssertionError("ldk must be provided when k is None")
+        k = (1 - torch.exp(ldk.float())).to(q.dtype)
+    if v is None:
+        if ldv is None:
+            raise AssertionError("ldv must be provided when v is None")
+        v = (1 - torch.exp(ldv.float())).to(q.dtype)
+    b = q.shape[0]
+    nb = cu_seqlens.shape[0] - 1 if cu_seqlens is not None else b
+    s0 = _prep_state(initial_state, nb, q.shape[2], q.shape[3], v.shape[3])
+    return LavdFunction.apply(q, k, v, ldk, ldv, s0, cu_seqlens, flags)
+
+
+def lavd_parallel_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
+                       v: Optional[torch.Tensor] = None, ldk: Optional[torch.Tensor] = None,
+                       ldv: Optional[torch.Tensor] = None, use_ldk: bool = True,
+                       use_ldv: bool = False, initial_state: Optional[torch.Tensor] = None,
+                       cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
+                       save_ld: bool = True, save_a: bool = True, use_chunk_loop: bool = False,
+                       **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Signature of lavd_parallel_triton (lavd_parallel_triton.py:1415-1430); use_ldk / use_ldv are
+    derived from ldk / ldv being given, as there (:1462-1470)."""
+    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, 0)
+
+
+def lavd_recurrence_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
+                         v: Optional[torch.Tensor] = None, ldk: Optional[torch.Tensor] = None,
+                         ldv: Optional[torch.Tensor] = None, use_ldk: bool = True,
+                         use_ldv: bool = False, initial_state: Optional[torch.Tensor] = None,
+                         cu_seqlens: Optional[torch.LongTensor] = None,
+                         **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Signature of lavd_recurrence_triton: always the fp32 scan kernels."""
+    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, _lib.FLAG_FORCE_RECURRENCE)
+
+
+def lavd_fn(q: torch.Tensor, k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
+            ldk: Optional[torch.Tensor] = None, ldv: Optional[torch.Tensor] = None,
+            initial_state: Optional[torch.Tensor] = None,
+            cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
+            save_ld: bool = True, save_a: bool = True, use_chunk_loop: bool = False,
+            **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Dispatch of vector_decay/__init__.py:44-64."""
+    fn = lavd_parallel_cuda if q.shape[1] > 1 else lavd_recurrence_cuda
+    return fn(q=q, k=k, v=v, ldk=ldk, ldv=ldv, initial_state=initial_state, cu_seqlens=cu_seqlens,
+              save_states=save_states, save_ld=save_ld, save_a=save_a,
+              use_chunk_loop=use_chunk_loop)
+
+
+def lavd_decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                     ldk: Optional[torch.Tensor], state: torch.Tensor,
+                     ldv: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                     inplace: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One decode step with vector decay: q,k (B,1,H,D), v (B,1,H,E), ldk (B,1,H,D) fp32 and/or
+    ldv (B,1,H,E) fp32, fp32 state (B,H,D,E).  No autograd; in place by default."""
+    lib = _lib.load()
+    _lib.require_cuda(q, k, v, ldk, ldv, state)
+    b, n, h, d = q.shape
+    e = v.shape[-1]
+    if n != 1:
+        raise ValueError("decode takes exactly one token per sequence")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape) != (b, h, d, e):
+        raise ValueError("state must be a contiguous fp32 (B,H,D,E) tensor")
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    lk, lv = _ld32(ldk), _ld32(ldv)
+    new_state = state if inplace else torch.empty_like(state)
+    o = out if out is not None else torch.empty(b, 1, h, e, dtype=q.dtype, device=q.device)
+    with torch.cuda.device(q.device):
+        rc = lib.la_decode_vector(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lk), _lib.ptr(lv),
+                                  _lib.ptr(state), _lib.ptr(new_state), _lib.ptr(o), b, h, d, e,
+                                  _lib.dtype_code(q), _lib.stream_of(q))
+    _lib.check(rc, "la_decode_vector")
+    return o, new_state
+
+
+lavd_parallel_triton = lavd_parallel_cuda
+lavd_recurrence_triton = lavd_recurrence_cuda
