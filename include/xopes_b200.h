@@ -59,6 +59,13 @@ LA_API int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned fla
 LA_API int la_device_status(void *stream, int *status_out);
 LA_API int la_device_status_clear(void *stream);
 
+/* Self-test of the tensor-core building blocks (no counterpart in the reference): one
+ * 128x128x128 product D (fp32, row-major) from a, b (128x128, 16-bit, row-major, 16-byte aligned)
+ * through one of the operand staging forms the chunk kernels use.  variant 0: D = a b^T;
+ * 1, 2, 4: D = a b; 3: D = a^T b. */
+LA_API int la_debug_umma_probe(int variant, const void *a, const void *b, float *d, int dtype,
+                               void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Scalar decay (lasd).  ld is fp32 and addressed as ld[b*ld_sb + n*ld_sn + h*ld_sh] (element
  * strides), so (B,N,H) tensors, (H,) per-head vectors (strides 0,0,1) and expanded views all work.

@@ -10,14 +10,15 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
-
-
-@pytest.fixture(scope="session", autouse=True)
-def _built_library():
-    """The shared library is a build artefact (git-ignored): compile it if it is not there."""
-    from xopes_b200 import build
-    if not os.path.exists(build.LIB):
-        build.build()
+    # The shared library is a build artefact (git-ignored): compile it before collection imports
+    # the package, which refuses to import without it.
+    sys.path.insert(0, ROOT)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_xb_build", os.path.join(ROOT, "xopes_b200", "build.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    if not os.path.exists(b.LIB):
+        b.build()
 
 
 @pytest.fixture(scope="session")

@@ -4,9 +4,14 @@ The compute lives in libxopes_b200.so (hand-written CUDA behind a C ABI, include
 this package is the host-side mirror of the reference's Python operator interface.  Importing it
 loads the shared library and fails loudly if it has not been built.
 """
+import sys as _sys
+
 from . import _lib
 
-_lib.load()
+# `python -m xopes_b200.build` must be able to run before the library exists (or when it is stale)
+_BUILDING = "xopes_b200.build" in getattr(_sys, "orig_argv", [])
+if not _BUILDING:
+    _lib.load()
 
 from .lightning_attn import *  # noqa: E402,F401,F403
 from .lightning_attn import __all__ as _la_all  # noqa: E402

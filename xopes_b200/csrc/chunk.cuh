@@ -31,5 +31,7 @@ struct ChunkPass {
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype);
 int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream);
+// one 128x128x128 product through one operand staging variant (see chunk_sm100.cu)
+int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream);
 
 }  // namespace la

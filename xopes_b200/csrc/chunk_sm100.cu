@@ -1,6 +1,630 @@
-// placeholder until the tcgen05 kernel lands
+// Chunk-parallel scalar-decay pass on 5th-generation tensor cores (sm_100a).
+//
+// One CTA per (sequence, head) walks the sequence in 128-token chunks.  Per chunk it computes
+//
+//   P  = X Y^T                        tcgen05.mma, A and B from shared memory (K-major)
+//   P~ = P (.) decay mask             registers, written back to tensor memory as 16-bit
+//   W1 = P~ Z                         tcgen05.mma, A from tensor memory, B MN-major
+//   W2 = X T_in                       tcgen05.mma, B = 16-bit copy of the running state
+//   T  = e^g T_in + (Y (.) u)^T Z     tcgen05.mma accumulating into the resident fp32 state
+//   W  = W1 + diag(s) W2              epilogue, stored with TMA
+//
+// The 128x128 fp32 state T never leaves tensor memory between chunks, so HBM sees each operand
+// tile once per pass and the output once.  A producer warp keeps the next chunk's three tiles in
+// flight with plain (non-multicast) TMA loads while the four compute warps work on the current
+// one.  Shared memory: 2 stages x 3 tiles x 32 KB + 32 KB state copy = 224 KB; tensor memory:
+// T | P | W1 | W2 = 4 x 128 columns.
+//
+// Every mbarrier wait is bounded (sm100_ptx.cuh: mbar_wait); a wait that runs out sets the device
+// status word and the kernel finishes by itself.
+#include <cuda.h>
+
 #include "chunk.cuh"
+#include "sm100_ptx.cuh"
+
 namespace la {
-bool chunk_supported(int64_t, int64_t, int64_t, int) { return false; }
-int launch_chunk_pass(const ChunkPass &, int, cudaStream_t) { return LA_ERR_UNSUPPORTED; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kChunk = 128;
+constexpr int kTileBytes = 32768;  // [128][128] 16-bit = two TMA boxes of [128][64]
+constexpr int kBoxBytes = 16384;
+constexpr int kStages = 2;
+constexpr int kStageBytes = 3 * kTileBytes;
+constexpr int kOffTb = kStages * kStageBytes;
+constexpr int kOffSmall = kOffTb + kTileBytes;
+constexpr int kSmallBytes = 1024;
+constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;  // + slack to align the base to 1024 B
+constexpr int kThreads = 160;                               // 4 compute warps + 1 producer warp
+
+// tensor-memory columns
+constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
+
+// status codes written to the device status word
+constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104;
+
+struct Small {
+  unsigned long long full[kStages];
+  unsigned long long empty[kStages];
+  unsigned long long bar_p;
+  unsigned long long bar_w;
+  uint32_t tmem_base;
+  int abort_flag;
+  int issued;
+  int pad;
+  float wsum[4];
+  float cs[kChunk];
+};
+static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
+
+struct ChunkArgs {
+  const void *xrow;
+  float *rowdot;
+  void *out;
+  const float *ld;
+  long long ld_sb, ld_sn, ld_sh;
+  const float *t0;
+  float *tfinal;
+  int state_transposed, reverse;
+  const long long *cu;
+  int B, N, H, M;
+  int *status;
+};
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__nv_bfloat16> {
+  static constexpr uint32_t kAB = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+  }
+};
+template <> struct Fmt<__half> {
+  static constexpr uint32_t kAB = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&u));
+  }
+};
+
+// byte offset of the k-th 16-element slice of a K-major [128][128] tile (two boxes of 64 columns)
+__device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_o,
+                  const ChunkArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  Small *sm = reinterpret_cast<Small *>(gbase + kOffSmall);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = blockIdx.x / a.H, h = blockIdx.x - seq * a.H;
+  long long t_begin = 0, t_end = a.N;
+  int bidx = seq;
+  if (a.cu != nullptr) {
+    t_begin = a.cu[seq];
+    t_end = a.cu[seq + 1];
+    bidx = 0;
+  }
+  const int len = (int)(t_end - t_begin);
+  const int nc = (len + kChunk - 1) / kChunk;
+
+  const uint32_t bar_full = smem_u32(&sm->full[0]), bar_empty = smem_u32(&sm->empty[0]);
+  const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w);
+  volatile int *abort_flag = &sm->abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_p, 1);
+    mbar_init(bar_w, 1);
+    sm->abort_flag = 0;
+    sm->issued = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&sm->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&map_x);
+      prefetch_tmap(&map_y);
+      prefetch_tmap(&map_z);
+      int it = 0;
+      for (; it < nc; ++it) {
+        const int n = a.reverse ? (nc - 1 - it) : it;
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
+        if (*abort_flag) break;
+        const uint32_t fb = bar_full + 8 * s;
+        mbar_arrive_expect_tx(fb, 3 * kTileBytes);
+        const uint32_t dst = base + (uint32_t)s * kStageBytes;
+        const int tok0 = (int)t_begin + n * kChunk;
+        tma_load_4d(dst, &map_x, fb, 0, h, tok0, bidx);
+        tma_load_4d(dst + kBoxBytes, &map_x, fb, 64, h, tok0, bidx);
+        tma_load_4d(dst + kTileBytes, &map_y, fb, 0, h, tok0, bidx);
+        tma_load_4d(dst + kTileBytes + kBoxBytes, &map_y, fb, 64, h, tok0, bidx);
+        tma_load_4d(dst + 2 * kTileBytes, &map_z, fb, 0, h, tok0, bidx);
+        tma_load_4d(dst + 2 * kTileBytes + kBoxBytes, &map_z, fb, 64, h, tok0, bidx);
+      }
+      sm->issued = it;
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int i = tid;  // row of every 128-row tile this thread owns (= tensor-memory lane)
+    const uint32_t tl = tmem + ((uint32_t)(32 * warp) << 16);
+    const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
+    const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
+    const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
+    const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
+
+    // starting state -> tensor memory
+    for (int bt = 0; bt < 4; ++bt) {
+      uint32_t r[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const int c = bt * 32 + k;
+        float v = 0.f;
+        if (a.t0 != nullptr) v = a.t0[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))];
+        r[k] = __float_as_uint(v);
+      }
+      tmem_st32(tl + kColT + bt * 32, r);
+    }
+    tmem_wait_st();
+
+    uint8_t *tb_row = gbase + kOffTb;
+    for (int it = 0; it < nc; ++it) {
+      const int n = a.reverse ? (nc - 1 - it) : it;
+      const int s = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
+      const int L = min(kChunk, len - n * kChunk);
+      const long long tok = t_begin + (long long)n * kChunk + i;
+      const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
+      uint8_t *stage = gbase + (size_t)s * kStageBytes;
+
+      // ---- A: in-chunk inclusive cumulative log decay c_i and chunk total g
+      float c_i = (i < L) ? a.ld[bidx * a.ld_sb + tok * a.ld_sn + h * a.ld_sh] : 0.f;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float nb = __shfl_up_sync(0xffffffffu, c_i, off);
+        if (lane >= off) c_i += nb;
+      }
+      if (lane == 31) sm->wsum[warp] = c_i;
+      named_bar_sync(1, 128);
+      {
+        float pre = 0.f;
+        for (int w = 0; w < warp; ++w) pre += sm->wsum[w];
+        c_i += pre;
+      }
+      const float g = sm->wsum[0] + sm->wsum[1] + sm->wsum[2] + sm->wsum[3];
+      sm->cs[i] = c_i;
+      const float eg = expf(g);
+      const float s_i = a.reverse ? expf(g - c_i) : expf(c_i);
+      const float u_i = (i < L) ? (a.reverse ? expf(c_i) : expf(g - c_i)) : 0.f;
+
+      // ---- B/C: operands landed -> P = X Y^T
+      mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
+      tc_fence_after();
+      if (tid == 0) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColP, desc_kmajor(xs + kslice(ks)), desc_kmajor(ys + kslice(ks)), idesc_kk, ks > 0);
+        mma_commit(bar_p);
+      }
+
+      // ---- D: state in -> 16-bit copy in shared memory (B operand of X T_in); T <- e^g T
+#pragma unroll 1
+      for (int bt = 0; bt < 4; ++bt) {
+        uint32_t r[32];
+        tmem_ld32(tl + kColT + bt * 32, r);
+        tmem_wait_ld();
+        uint8_t *box = tb_row + (bt >> 1) * kBoxBytes;
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 v;
+          v.x = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 0]), __uint_as_float(r[pc * 8 + 1]));
+          v.y = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 2]), __uint_as_float(r[pc * 8 + 3]));
+          v.z = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 4]), __uint_as_float(r[pc * 8 + 5]));
+          v.w = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 6]), __uint_as_float(r[pc * 8 + 7]));
+          *reinterpret_cast<uint4 *>(box + sw128_offset(i, (bt & 1) * 4 + pc)) = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * eg);
+        tmem_st32(tl + kColT + bt * 32, r);
+      }
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      named_bar_sync(1, 128);
+
+      // ---- E: W2 = X T_in
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColW2, desc_kmajor(xs + kslice(ks)),
+                 desc_mnmajor(base + kOffTb + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
+      }
+
+      // ---- F: P ready -> masked 16-bit P~ in tensor memory; Y <- Y (.) u in place
+      mbar_wait(bar_p, par, abort_flag, a.status, kStP);
+      tc_fence_after();
+#pragma unroll 1
+      for (int bt = 0; bt < 4; ++bt) {
+        uint32_t pk[16];
+        const bool active = a.reverse ? (bt >= warp) : (bt <= warp);  // warp-uniform
+        if (active) {
+          uint32_t r[32];
+          tmem_ld32(tl + kColP + bt * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const int j = bt * 32 + k;
+            const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
+            float m0, m1;
+            if (!a.reverse) {
+              m0 = (j <= i) ? __expf(c_i - cj.x) : 0.f;
+              m1 = (j + 1 <= i) ? __expf(c_i - cj.y) : 0.f;
+            } else {
+              m0 = (j >= i && j < L) ? __expf(cj.x - c_i) : 0.f;
+              m1 = (j + 1 >= i && j + 1 < L) ? __expf(cj.y - c_i) : 0.f;
+            }
+            pk[k >> 1] = Fmt<T>::pack(__uint_as_float(r[k]) * m0, __uint_as_float(r[k + 1]) * m1);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+        }
+        tmem_st16(tl + kColP + bt * 16, pk);
+      }
+      {
+        uint8_t *yrow = stage + kTileBytes;
+#pragma unroll
+        for (int bx = 0; bx < 2; ++bx) {
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            uint4 *p = reinterpret_cast<uint4 *>(yrow + bx * kBoxBytes + sw128_offset(i, pc));
+            uint4 v = *p;
+            float2 f;
+            f = Fmt<T>::unpack(v.x); v.x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+            f = Fmt<T>::unpack(v.y); v.y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+            f = Fmt<T>::unpack(v.z); v.z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+            f = Fmt<T>::unpack(v.w); v.w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+            *p = v;
+          }
+        }
+      }
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      named_bar_sync(1, 128);
+
+      // ---- G: W1 = P~ Z ; T += (Y (.) u)^T Z
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + kColW1, tmem + kColP + ks * 8, desc_mnmajor(zs + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColT, desc_mnmajor(ys + ks * 2048, kBoxBytes), desc_mnmajor(zs + ks * 2048, kBoxBytes),
+                 idesc_mnmn, 1);
+        mma_commit(bar_w);
+      }
+
+      // ---- H: epilogue W = W1 + s_i W2
+      mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+      tc_fence_after();
+      const bool full_chunk = (L == kChunk);
+      const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
+      float rd = 0.f;
+#pragma unroll 1
+      for (int bt = 0; bt < 4; ++bt) {
+        uint32_t w1[32], w2[32];
+        tmem_ld32(tl + kColW1 + bt * 32, w1);
+        tmem_ld32(tl + kColW2 + bt * 32, w2);
+        tmem_wait_ld();
+        float w[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) w[k] = fmaf(s_i, __uint_as_float(w2[k]), __uint_as_float(w1[k]));
+        if (a.xrow != nullptr && i < L) {
+          const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {
+            const uint4 xv = xp[pc];
+            float2 f;
+            f = Fmt<T>::unpack(xv.x); rd = fmaf(f.x, w[pc * 8 + 0], rd); rd = fmaf(f.y, w[pc * 8 + 1], rd);
+            f = Fmt<T>::unpack(xv.y); rd = fmaf(f.x, w[pc * 8 + 2], rd); rd = fmaf(f.y, w[pc * 8 + 3], rd);
+            f = Fmt<T>::unpack(xv.z); rd = fmaf(f.x, w[pc * 8 + 4], rd); rd = fmaf(f.y, w[pc * 8 + 5], rd);
+            f = Fmt<T>::unpack(xv.w); rd = fmaf(f.x, w[pc * 8 + 6], rd); rd = fmaf(f.y, w[pc * 8 + 7], rd);
+          }
+        }
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 v;
+          v.x = Fmt<T>::pack(w[pc * 8 + 0], w[pc * 8 + 1]);
+          v.y = Fmt<T>::pack(w[pc * 8 + 2], w[pc * 8 + 3]);
+          v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
+          v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
+          if (full_chunk) {
+            // staging = this stage's X tile (dead once the MMAs above have completed)
+            *reinterpret_cast<uint4 *>(stage + (bt >> 1) * kBoxBytes + sw128_offset(i, (bt & 1) * 4 + pc)) = v;
+          } else if (i < L) {
+            reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + row_off + bt * 32)[pc] = v;
+          }
+        }
+      }
+      if (a.rowdot != nullptr && i < L) a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd;
+      if (full_chunk) fence_proxy_async();
+      tc_fence_before();
+      named_bar_sync(1, 128);
+      if (tid == 0) {
+        if (full_chunk) {
+          const int tok0 = (int)t_begin + n * kChunk;
+          tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
+          tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        mbar_arrive(bar_empty + 8 * s);
+      }
+    }
+
+    // end state -> global
+    if (a.tfinal != nullptr) {
+      tc_fence_after();
+      for (int bt = 0; bt < 4; ++bt) {
+        uint32_t r[32];
+        tmem_ld32(tl + kColT + bt * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = bt * 32 + k;
+          a.tfinal[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))] = __uint_as_float(r[k]);
+        }
+      }
+    }
+    if (tid == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    if (lane == 0 && sm->abort_flag != 0) {
+      // loads that were issued but never consumed must land before the CTA's shared memory is
+      // released; wait for them with a limit of their own
+      int dummy = 0;
+      for (int it = max(0, sm->issued - kStages); it < sm->issued; ++it)
+        mbar_wait(bar_full + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, &dummy, nullptr, 0, 1u << 20);
+    }
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// (B, N, H, 128) 16-bit tensor; one box = 128 tokens x 64 features of one head, 128-byte swizzle
+int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return LA_ERR_CUDA;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
+  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {256, (cuuint64_t)H * 256, (cuuint64_t)N * H * 256};
+  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == LA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
+}
+
+template <typename T>
+int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
+  alignas(64) CUtensorMap mx, my, mz, mo;
+  int rc;
+  if ((rc = make_map(&mx, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&mz, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&mo, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if (p.xrow != nullptr && (reinterpret_cast<uintptr_t>(p.xrow) & 15u)) return LA_ERR_MISALIGNED;
+  ChunkArgs a;
+  a.xrow = p.xrow; a.rowdot = p.xrow ? p.rowdot : nullptr; a.out = p.out;
+  a.ld = p.ld; a.ld_sb = p.ld_sb; a.ld_sn = p.ld_sn; a.ld_sh = p.ld_sh;
+  a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
+  a.cu = reinterpret_cast<const long long *>(p.cu);
+  a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
+  a.status = status_word_ptr();
+  if (a.status == nullptr) return LA_ERR_CUDA;
+  auto kern = chunk_pass_kernel<T>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return LA_ERR_CUDA;
+    attr_set = true;
+  }
+  const int nb = p.cu ? p.M : p.B;
+  kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, mo, a);
+  return launch_status();
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Self-test of the tensor-core building blocks: one 128x128x128 product per variant, operands
+// staged exactly as the chunk kernel stages them.
+//   0: D = A B^T   (A, B K-major from TMA)            -- the X Y^T product
+//   1: D = A B     (A K-major, B MN-major from TMA)   -- operand forms of X T and P~ Z
+//   2: D = A B     (A through registers into tensor memory, B MN-major)
+//   3: D = A^T B   (A, B MN-major from TMA)           -- the state update
+//   4: D = A B     (B written to shared memory by threads in the swizzled layout)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128, 1)
+umma_probe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                  const T *a_g, const T *b_g, float *d, int variant, int *status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  Small *sm = reinterpret_cast<Small *>(gbase + 2 * kTileBytes);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const uint32_t bar_full = smem_u32(&sm->full[0]), bar_mma = smem_u32(&sm->bar_w);
+  volatile int *abort_flag = &sm->abort_flag;
+  if (tid == 0) {
+    mbar_init(bar_full, 1);
+    mbar_init(bar_mma, 1);
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&sm->tmem_base), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const uint32_t as = base, bs = base + kTileBytes;
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar_full, 2 * kTileBytes);
+    tma_load_4d(as, &map_a, bar_full, 0, 0, 0, 0);
+    tma_load_4d(as + kBoxBytes, &map_a, bar_full, 64, 0, 0, 0);
+    tma_load_4d(bs, &map_b, bar_full, 0, 0, 0, 0);
+    tma_load_4d(bs + kBoxBytes, &map_b, bar_full, 64, 0, 0, 0);
+  }
+  mbar_wait(bar_full, 0, abort_flag, status, kStFull);
+  const uint32_t tl = tmem + ((uint32_t)(32 * warp) << 16);
+  if (variant == 2) {
+    for (int bt = 0; bt < 4; ++bt) {
+      uint32_t pk[16];
+      const uint32_t *src = reinterpret_cast<const uint32_t *>(a_g + tid * 128 + bt * 32);
+#pragma unroll
+      for (int k = 0; k < 16; ++k) pk[k] = src[k];
+      tmem_st16(tl + 128 + bt * 16, pk);
+    }
+    tmem_wait_st();
+  }
+  if (variant == 4) {
+    for (int pc = 0; pc < 16; ++pc) {
+      const uint4 v = reinterpret_cast<const uint4 *>(b_g + tid * 128)[pc];
+      *reinterpret_cast<uint4 *>(gbase + kTileBytes + (pc >> 3) * kBoxBytes + sw128_offset(tid, pc & 7)) = v;
+    }
+    fence_proxy_async();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    for (int ks = 0; ks < 8; ++ks) {
+      if (variant == 0)
+        mma_ss(tmem, desc_kmajor(as + kslice(ks)), desc_kmajor(bs + kslice(ks)),
+               instr_desc(Fmt<T>::kAB, 0, 0, 128, 128), ks > 0);
+      else if (variant == 1 || variant == 4)
+        mma_ss(tmem, desc_kmajor(as + kslice(ks)), desc_mnmajor(bs + ks * 2048, kBoxBytes),
+               instr_desc(Fmt<T>::kAB, 0, 1, 128, 128), ks > 0);
+      else if (variant == 2)
+        mma_ts(tmem, tmem + 128 + ks * 8, desc_mnmajor(bs + ks * 2048, kBoxBytes),
+               instr_desc(Fmt<T>::kAB, 0, 1, 128, 128), ks > 0);
+      else
+        mma_ss(tmem, desc_mnmajor(as + ks * 2048, kBoxBytes), desc_mnmajor(bs + ks * 2048, kBoxBytes),
+               instr_desc(Fmt<T>::kAB, 1, 1, 128, 128), ks > 0);
+    }
+    mma_commit(bar_mma);
+  }
+  mbar_wait(bar_mma, 0, abort_flag, status, kStW);
+  tc_fence_after();
+  for (int bt = 0; bt < 4; ++bt) {
+    uint32_t r[32];
+    tmem_ld32(tl + bt * 32, r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int k = 0; k < 32; ++k) d[tid * 128 + bt * 32 + k] = __uint_as_float(r[k]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+template <typename T>
+int probe_t(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream) {
+  alignas(64) CUtensorMap ma, mb;
+  int rc;
+  if ((rc = make_map(&ma, a, dtype, 1, 128, 1)) != LA_OK) return rc;
+  if ((rc = make_map(&mb, b, dtype, 1, 128, 1)) != LA_OK) return rc;
+  int *status = status_word_ptr();
+  if (status == nullptr) return LA_ERR_CUDA;
+  const int smem = 2 * kTileBytes + kSmallBytes + 1024;
+  auto kern = umma_probe_kernel<T>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return LA_ERR_CUDA;
+  kern<<<1, 128, smem, stream>>>(ma, mb, static_cast<const T *>(a), static_cast<const T *>(b), d, variant, status);
+  return launch_status();
+}
+
+}  // namespace
+
+int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream) {
+  if (a == nullptr || b == nullptr || d == nullptr) return LA_ERR_NULL_POINTER;
+  if (variant < 0 || variant > 4) return LA_ERR_BAD_SHAPE;
+  if (dtype == LA_BF16) return probe_t<__nv_bfloat16>(variant, a, b, d, dtype, stream);
+  if (dtype == LA_F16) return probe_t<__half>(variant, a, b, d, dtype, stream);
+  return LA_ERR_UNSUPPORTED;
+}
+
+bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
+  return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
+}
+
+int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream) {
+  if (p.x == nullptr || p.y == nullptr || p.z == nullptr || p.out == nullptr || p.ld == nullptr)
+    return LA_ERR_NULL_POINTER;
+  const int nb = p.cu ? p.M : p.B;
+  if (nb <= 0 || p.H <= 0 || p.N <= 0) return LA_ERR_BAD_SHAPE;
+  if ((int64_t)nb * p.H > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, dtype, stream);
+  if (dtype == LA_F16) return launch_t<__half>(p, dtype, stream);
+  return LA_ERR_UNSUPPORTED;
+}
+
 }  // namespace la

@@ -114,7 +114,9 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
     }
     if (tid < ntok) {
       float lam = 1.f;
-      if (has_ld) lam = expf(p.ld[bidx * p.ld_sb + tok(tid) * p.ld_sn + h * p.ld_sh]);
+      // exp in double, rounded once: a per-head constant decay is applied at every token, so an
+      // ulp of error in it compounds linearly with the sequence length
+      if (has_ld) lam = (float)exp((double)p.ld[bidx * p.ld_sb + tok(tid) * p.ld_sn + h * p.ld_sh]);
       lam_s[tid] = lam;
     }
     __syncthreads();
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(256) decode_kernel(const T *__restrict__ q, co
   float *dk_s = k_s + D;          // [D] row decay factor (includes the scalar decay)
 
   float lam = 1.f;
-  if (ld != nullptr) lam = expf(ld[b * ld_sb + h * ld_sh]);
+  if (ld != nullptr) lam = (float)exp((double)ld[b * ld_sb + h * ld_sh]);
   for (int d = tid; d < D; d += 256) {
     q_s[d] = Cvt<T>::to_f(q[(int64_t)bh * D + d]);
     k_s[d] = Cvt<T>::to_f(k[(int64_t)bh * D + d]);
