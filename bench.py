@@ -106,9 +106,12 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 # workloads
 # --------------------------------------------------------------------------------------------
-def make_workload(name, rank):
+def make_workload(name, rank, shape=None):
     from xopes_b200 import workloads as W
     cfg = dict(W.CONFIGS[name])
+    if shape:  # smaller case of the same kernel, for profiler captures
+        b, n, h = (int(x) for x in shape.split(","))
+        cfg.update(B=b, N=n, H=h) if name != "C4" else cfg.update(B=b, H=h)
     seed = rank  # every rank draws its own batch
     if name == "C2":
         w = W.lasd_inputs(cfg["B"], cfg["N"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, seed)
@@ -350,6 +353,7 @@ def main():
     ap.add_argument("--workload", default="C2", choices=["C2", "C3", "C4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shape", default=None, help="B,N,H override (profiling a smaller case)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
@@ -365,7 +369,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     warmup = max(args.warmup, 3)
 
-    cfg, w, tokens, alg_bytes, _ = make_workload(args.workload, rank)
+    cfg, w, tokens, alg_bytes, _ = make_workload(args.workload, rank, args.shape)
     runner = {"C2": LasdStep, "C3": LavdStep, "C4": DecodeStep}[args.workload](w, dev)
     torch.cuda.synchronize()
 

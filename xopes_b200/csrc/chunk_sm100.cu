@@ -34,9 +34,12 @@ constexpr int kStages = 2;
 constexpr int kStageBytes = 3 * kTileBytes;
 constexpr int kOffTb = kStages * kStageBytes;
 constexpr int kOffSmall = kOffTb + kTileBytes;
-constexpr int kSmallBytes = 1024;
+constexpr int kSmallBytes = 2048;
 constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;  // + slack to align the base to 1024 B
-constexpr int kThreads = 160;                               // 4 compute warps + 1 producer warp
+constexpr int kComputeThreads = 256;                        // two warpgroups, each owns 64 columns
+constexpr int kProducerWarp = 8;
+constexpr int kThreads = kComputeThreads + 32;
+constexpr float kLog2e = 1.4426950408889634f;
 
 // tensor-memory columns
 constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
@@ -54,7 +57,9 @@ struct Small {
   int issued;
   int pad;
   float wsum[4];
-  float cs[kChunk];
+  float cs[kChunk];   // inclusive cumulative log2 decay of each row of the chunk
+  float bs[kChunk];   // per-column factor of the factorised decay mask
+  float rd[kChunk];   // row-dot partial of the second warpgroup
 };
 static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
 
@@ -97,6 +102,20 @@ template <> struct Fmt<__half> {
 // byte offset of the k-th 16-element slice of a K-major [128][128] tile (two boxes of 64 columns)
 __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
 
+__device__ __forceinline__ float ex2(float x) {  // 2^x, single MUFU
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Thread layout of the compute warps: warpgroup wg = warp / 4 owns columns [64 wg, 64 wg + 64) of
+// every 128-column row, quadrant q4 = warp % 4 owns rows (= tensor-memory lanes) [32 q4, 32 q4 + 32).
+//
+// Decay mask.  With c = in-chunk inclusive cumulative log2 decay, the weight of (row i, column j)
+// is 2^(c_i - c_j) for j <= i (forward) or 2^(c_j - c_i) for j >= i (reverse).  For a 32-column
+// batch that lies wholly on the allowed side of the diagonal the weight factorises as
+// A_i(batch) * B_j with both exponents <= 0 (reference point: the batch edge nearest the diagonal),
+// so only the diagonal batch pays one exponential per element.
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -135,7 +154,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     sm->issued = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     tmem_alloc(smem_u32(&sm->tmem_base), 512);
     tmem_relinquish();
   }
@@ -144,7 +163,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_tmap(&map_x);
@@ -173,15 +192,18 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ compute warps
-    const int i = tid;  // row of every 128-row tile this thread owns (= tensor-memory lane)
-    const uint32_t tl = tmem + ((uint32_t)(32 * warp) << 16);
+    const int wg = warp >> 2, q4 = warp & 3;
+    const int i = q4 * 32 + lane;  // row of every 128-row tile this thread works on
+    const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
     const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
     const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
     const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
+    const bool rev = a.reverse != 0;
 
-    // starting state -> tensor memory
-    for (int bt = 0; bt < 4; ++bt) {
+    // starting state -> tensor memory (this warpgroup's 64 columns)
+    for (int b2 = 0; b2 < 2; ++b2) {
+      const int bt = 2 * wg + b2;
       uint32_t r[32];
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
@@ -194,9 +216,18 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
     tmem_wait_st();
 
-    uint8_t *tb_row = gbase + kOffTb;
+    auto load_ld = [&](int it) -> float {
+      if (it >= nc) return 0.f;
+      const int n = rev ? (nc - 1 - it) : it;
+      const int L = min(kChunk, len - n * kChunk);
+      if (i >= L) return 0.f;
+      const long long tok = t_begin + (long long)n * kChunk + i;
+      return a.ld[bidx * a.ld_sb + tok * a.ld_sn + h * a.ld_sh] * kLog2e;
+    };
+    float ld_next = load_ld(0);
+
     for (int it = 0; it < nc; ++it) {
-      const int n = a.reverse ? (nc - 1 - it) : it;
+      const int n = rev ? (nc - 1 - it) : it;
       const int s = it & 1;
       const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
       const int L = min(kChunk, len - n * kChunk);
@@ -204,25 +235,29 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
       uint8_t *stage = gbase + (size_t)s * kStageBytes;
 
-      // ---- A: in-chunk inclusive cumulative log decay c_i and chunk total g
-      float c_i = (i < L) ? a.ld[bidx * a.ld_sb + tok * a.ld_sn + h * a.ld_sh] : 0.f;
+      // ---- A: in-chunk inclusive cumulative log2 decay c_i, warp-end sums, chunk total g
+      float c_i = ld_next;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
         const float nb = __shfl_up_sync(0xffffffffu, c_i, off);
         if (lane >= off) c_i += nb;
       }
-      if (lane == 31) sm->wsum[warp] = c_i;
-      named_bar_sync(1, 128);
-      {
-        float pre = 0.f;
-        for (int w = 0; w < warp; ++w) pre += sm->wsum[w];
-        c_i += pre;
+      if (wg == 0 && lane == 31) sm->wsum[q4] = c_i;
+      named_bar_sync(1, kComputeThreads);
+      ld_next = load_ld(it + 1);  // in flight while this chunk is processed
+      float wend[5];              // wend[b] = cumulative decay at the end of row batch b-1
+      wend[0] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) wend[w + 1] = wend[w] + sm->wsum[w];
+      c_i += wend[q4];
+      const float g = wend[4];
+      const float eg = exp2f(g);
+      const float s_i = rev ? exp2f(g - c_i) : exp2f(c_i);
+      const float u_i = (i < L) ? (rev ? exp2f(c_i) : exp2f(g - c_i)) : 0.f;
+      if (wg == 0) {
+        sm->cs[i] = c_i;
+        sm->bs[i] = rev ? ((i < L) ? exp2f(c_i - wend[q4]) : 0.f) : exp2f(wend[q4 + 1] - c_i);
       }
-      const float g = sm->wsum[0] + sm->wsum[1] + sm->wsum[2] + sm->wsum[3];
-      sm->cs[i] = c_i;
-      const float eg = expf(g);
-      const float s_i = a.reverse ? expf(g - c_i) : expf(c_i);
-      const float u_i = (i < L) ? (a.reverse ? expf(c_i) : expf(g - c_i)) : 0.f;
 
       // ---- B/C: operands landed -> P = X Y^T
       mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
@@ -235,29 +270,42 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
 
       // ---- D: state in -> 16-bit copy in shared memory (B operand of X T_in); T <- e^g T
-#pragma unroll 1
-      for (int bt = 0; bt < 4; ++bt) {
-        uint32_t r[32];
-        tmem_ld32(tl + kColT + bt * 32, r);
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
+        tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
         tmem_wait_ld();
-        uint8_t *box = tb_row + (bt >> 1) * kBoxBytes;
+        uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 v;
-          v.x = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 0]), __uint_as_float(r[pc * 8 + 1]));
-          v.y = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 2]), __uint_as_float(r[pc * 8 + 3]));
-          v.z = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 4]), __uint_as_float(r[pc * 8 + 5]));
-          v.w = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 6]), __uint_as_float(r[pc * 8 + 7]));
-          *reinterpret_cast<uint4 *>(box + sw128_offset(i, (bt & 1) * 4 + pc)) = v;
+          v.x = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 0]), __uint_as_float(r0[pc * 8 + 1]));
+          v.y = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 2]), __uint_as_float(r0[pc * 8 + 3]));
+          v.z = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 4]), __uint_as_float(r0[pc * 8 + 5]));
+          v.w = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 6]), __uint_as_float(r0[pc * 8 + 7]));
+          *reinterpret_cast<uint4 *>(box + sw128_offset(i, pc)) = v;
         }
 #pragma unroll
-        for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) * eg);
-        tmem_st32(tl + kColT + bt * 32, r);
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 v;
+          v.x = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 0]), __uint_as_float(r1[pc * 8 + 1]));
+          v.y = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 2]), __uint_as_float(r1[pc * 8 + 3]));
+          v.z = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 4]), __uint_as_float(r1[pc * 8 + 5]));
+          v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
+          *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          r0[k] = __float_as_uint(__uint_as_float(r0[k]) * eg);
+          r1[k] = __float_as_uint(__uint_as_float(r1[k]) * eg);
+        }
+        tmem_st32(tl + kColT + (2 * wg) * 32, r0);
+        tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
       }
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kComputeThreads);
 
       // ---- E: W2 = X T_in
       if (tid == 0) {
@@ -268,65 +316,75 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                  desc_mnmajor(base + kOffTb + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
       }
 
-      // ---- F: P ready -> masked 16-bit P~ in tensor memory; Y <- Y (.) u in place
+      // ---- F: P ready -> masked 16-bit P~ (first 16 columns of each 32-column batch of P);
+      //         Y <- Y (.) u in place (this warpgroup's 64 columns)
       mbar_wait(bar_p, par, abort_flag, a.status, kStP);
       tc_fence_after();
 #pragma unroll 1
-      for (int bt = 0; bt < 4; ++bt) {
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = wg + 2 * b2;  // batches {0,2} / {1,3}: balances the triangular work
         uint32_t pk[16];
-        const bool active = a.reverse ? (bt >= warp) : (bt <= warp);  // warp-uniform
-        if (active) {
+        const bool dead = rev ? (bt < q4) : (bt > q4);  // warp-uniform
+        if (dead) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+        } else {
           uint32_t r[32];
           tmem_ld32(tl + kColP + bt * 32, r);
           tmem_wait_ld();
+          if (bt != q4) {
+            const float ai = rev ? exp2f(wend[bt] - c_i) : exp2f(c_i - wend[bt + 1]);
 #pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            const int j = bt * 32 + k;
-            const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
-            float m0, m1;
-            if (!a.reverse) {
-              m0 = (j <= i) ? __expf(c_i - cj.x) : 0.f;
-              m1 = (j + 1 <= i) ? __expf(c_i - cj.y) : 0.f;
-            } else {
-              m0 = (j >= i && j < L) ? __expf(cj.x - c_i) : 0.f;
-              m1 = (j + 1 >= i && j + 1 < L) ? __expf(cj.y - c_i) : 0.f;
+            for (int k = 0; k < 32; k += 4) {
+              const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + k]);
+              pk[(k >> 1) + 0] = Fmt<T>::pack(__uint_as_float(r[k + 0]) * (ai * bj.x), __uint_as_float(r[k + 1]) * (ai * bj.y));
+              pk[(k >> 1) + 1] = Fmt<T>::pack(__uint_as_float(r[k + 2]) * (ai * bj.z), __uint_as_float(r[k + 3]) * (ai * bj.w));
             }
-            pk[k >> 1] = Fmt<T>::pack(__uint_as_float(r[k]) * m0, __uint_as_float(r[k + 1]) * m1);
-          }
-        } else {
+          } else {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+            for (int k = 0; k < 32; k += 2) {
+              const int j = bt * 32 + k;
+              const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
+              float m0, m1;
+              if (!rev) {
+                m0 = (j <= i) ? ex2(c_i - cj.x) : 0.f;
+                m1 = (j + 1 <= i) ? ex2(c_i - cj.y) : 0.f;
+              } else {
+                m0 = (j >= i && j < L) ? ex2(cj.x - c_i) : 0.f;
+                m1 = (j + 1 >= i && j + 1 < L) ? ex2(cj.y - c_i) : 0.f;
+              }
+              pk[k >> 1] = Fmt<T>::pack(__uint_as_float(r[k]) * m0, __uint_as_float(r[k + 1]) * m1);
+            }
+          }
         }
-        tmem_st16(tl + kColP + bt * 16, pk);
+        tmem_st16(tl + kColP + bt * 32, pk);
       }
       {
-        uint8_t *yrow = stage + kTileBytes;
+        uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
 #pragma unroll
-        for (int bx = 0; bx < 2; ++bx) {
-#pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
-            uint4 *p = reinterpret_cast<uint4 *>(yrow + bx * kBoxBytes + sw128_offset(i, pc));
-            uint4 v = *p;
-            float2 f;
-            f = Fmt<T>::unpack(v.x); v.x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-            f = Fmt<T>::unpack(v.y); v.y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-            f = Fmt<T>::unpack(v.z); v.z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-            f = Fmt<T>::unpack(v.w); v.w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-            *p = v;
-          }
+        for (int pc = 0; pc < 8; ++pc) {
+          uint4 *p = reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc));
+          uint4 v = *p;
+          float2 f;
+          f = Fmt<T>::unpack(v.x); v.x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v.y); v.y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v.z); v.z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v.w); v.w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          *p = v;
         }
       }
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kComputeThreads);
 
       // ---- G: W1 = P~ Z ; T += (Y (.) u)^T Z
       if (tid == 0) {
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + kColW1, tmem + kColP + ks * 8, desc_mnmajor(zs + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
+          mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8,
+                 desc_mnmajor(zs + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
           mma_ss(tmem + kColT, desc_mnmajor(ys + ks * 2048, kBoxBytes), desc_mnmajor(zs + ks * 2048, kBoxBytes),
@@ -334,14 +392,15 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         mma_commit(bar_w);
       }
 
-      // ---- H: epilogue W = W1 + s_i W2
+      // ---- H: epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
       mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       tc_fence_after();
       const bool full_chunk = (L == kChunk);
       const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
       float rd = 0.f;
 #pragma unroll 1
-      for (int bt = 0; bt < 4; ++bt) {
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = 2 * wg + b2;
         uint32_t w1[32], w2[32];
         tmem_ld32(tl + kColW1 + bt * 32, w1);
         tmem_ld32(tl + kColW2 + bt * 32, w2);
@@ -370,16 +429,18 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
           if (full_chunk) {
             // staging = this stage's X tile (dead once the MMAs above have completed)
-            *reinterpret_cast<uint4 *>(stage + (bt >> 1) * kBoxBytes + sw128_offset(i, (bt & 1) * 4 + pc)) = v;
+            *reinterpret_cast<uint4 *>(stage + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
           } else if (i < L) {
             reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + row_off + bt * 32)[pc] = v;
           }
         }
       }
-      if (a.rowdot != nullptr && i < L) a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd;
+      if (a.rowdot != nullptr && wg == 1) sm->rd[i] = rd;
       if (full_chunk) fence_proxy_async();
       tc_fence_before();
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kComputeThreads);
+      if (a.rowdot != nullptr && wg == 0 && i < L)
+        a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd + sm->rd[i];
       if (tid == 0) {
         if (full_chunk) {
           const int tok0 = (int)t_begin + n * kChunk;
@@ -395,7 +456,8 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // end state -> global
     if (a.tfinal != nullptr) {
       tc_fence_after();
-      for (int bt = 0; bt < 4; ++bt) {
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = 2 * wg + b2;
         uint32_t r[32];
         tmem_ld32(tl + kColT + bt * 32, r);
         tmem_wait_ld();
@@ -411,7 +473,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0 && sm->abort_flag != 0) {
       // loads that were issued but never consumed must land before the CTA's shared memory is
       // released; wait for them with a limit of their own
