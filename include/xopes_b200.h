@@ -59,6 +59,11 @@ LA_API int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned fla
 LA_API int la_device_status(void *stream, int *status_out);
 LA_API int la_device_status_clear(void *stream);
 
+/* Phase tracing of the chunk kernel (no counterpart in the reference): while buf is non-NULL,
+ * every chunk pass writes clock64() stamps of CTA 0, threads 0 and 32, at 15 phase boundaries
+ * per chunk into buf (device memory, 2 x 4096 x 16 int64).  NULL switches it off. */
+LA_API int la_debug_chunk_trace(void *buf);
+
 /* Self-test of the tensor-core building blocks (no counterpart in the reference): one
  * 128x128x128 product D (fp32, row-major) from a, b (128x128, 16-bit, row-major, 16-byte aligned)
  * through one of the operand staging forms the chunk kernels use.  variant 0: D = a b^T;

@@ -111,6 +111,11 @@ int la_device_status_clear(void *stream) {
   return LA_OK;
 }
 
+int la_debug_chunk_trace(void *buf) {
+  chunk_set_trace(static_cast<long long *>(buf));
+  return LA_OK;
+}
+
 int la_debug_umma_probe(int variant, const void *a, const void *b, float *d, int dtype, void *stream) {
   return umma_probe(variant, a, b, d, dtype, static_cast<cudaStream_t>(stream));
 }

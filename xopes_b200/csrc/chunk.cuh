@@ -31,6 +31,8 @@ struct ChunkPass {
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype);
 int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream);
+// phase timestamps of CTA 0 (2 x 4096 x 16 int64) are written to buf by later passes; null disables
+void chunk_set_trace(long long *buf);
 // one 128x128x128 product through one operand staging variant (see chunk_sm100.cu)
 int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream);
 

@@ -19,6 +19,8 @@
 // status word and the kernel finishes by itself.
 #include <cuda.h>
 
+#include <cstddef>
+
 #include "chunk.cuh"
 #include "sm100_ptx.cuh"
 
@@ -37,31 +39,41 @@ constexpr int kOffSmall = kOffTb + kTileBytes;
 constexpr int kSmallBytes = 2048;
 constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;  // + slack to align the base to 1024 B
 constexpr int kComputeThreads = 256;                        // two warpgroups, each owns 64 columns
-constexpr int kProducerWarp = 8;
-constexpr int kThreads = kComputeThreads + 32;
+constexpr int kProducerWarp = 8;                            // TMA loads
+constexpr int kMmaWarp = 9;                                 // tcgen05.mma issue
+constexpr int kStoreWarp = 10;                              // TMA stores of finished output tiles
+constexpr int kThreads = kComputeThreads + 3 * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // tensor-memory columns
 constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
 
 // status codes written to the device status word
-constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104;
+constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104, kStD = 105, kStF = 106, kStH = 107,
+              kStT = 108, kStY = 109;
 
 struct Small {
   unsigned long long full[kStages];
   unsigned long long empty[kStages];
-  unsigned long long bar_p;
-  unsigned long long bar_w;
+  unsigned long long bar_p;   // P = X Y^T complete                       (MMA warp -> compute)
+  unsigned long long bar_w;   // W1, W2 and the state update complete      (MMA warp -> compute)
+  unsigned long long bar_t;   // state update complete (T final for the chunk) (MMA warp -> compute)
+  unsigned long long bar_d;   // state copy written, T rescaled            (compute -> MMA warp)
+  unsigned long long bar_y;   // rescaled Y written                        (compute -> MMA warp)
+  unsigned long long bar_f;   // masked P~ written                         (compute -> MMA warp)
+  unsigned long long bar_h;   // output tile staged, W1/W2 consumed        (compute -> store and MMA warps)
   uint32_t tmem_base;
   int abort_flag;
   int issued;
   int pad;
-  float wsum[4];
-  float cs[kChunk];   // inclusive cumulative log2 decay of each row of the chunk
-  float bs[kChunk];   // per-column factor of the factorised decay mask
-  float rd[kChunk];   // row-dot partial of the second warpgroup
+  alignas(16) float wsum[4];
+  alignas(16) float cs[kChunk];   // inclusive cumulative log2 decay of each row of the chunk
+  alignas(16) float bs[kChunk];   // per-column factor of the factorised decay mask (read as float4)
+  alignas(16) float rd[kChunk];   // row-dot partial of the second warpgroup
 };
 static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
+static_assert(offsetof(Small, cs) % 16 == 0 && offsetof(Small, bs) % 16 == 0, "vector loads need 16 B");
+static_assert(kOffSmall % 16 == 0, "small area must start 16-byte aligned");
 
 struct ChunkArgs {
   const void *xrow;
@@ -75,7 +87,15 @@ struct ChunkArgs {
   const long long *cu;
   int B, N, H, M;
   int *status;
+  long long *trace;  // optional: clock64() at phase boundaries of CTA 0 (threads 0 and 32)
 };
+
+// trace[thread slot][chunk][point]: 16 points per chunk, 2 thread slots of 4096 chunks at most
+#define LA_TRACE(point)                                                                   \
+  do {                                                                                    \
+    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32) && it < 4096)      \
+      a.trace[((tid >> 5) * 4096 + it) * 16 + (point)] = clock64();                       \
+  } while (0)
 
 template <typename T> struct Fmt;
 template <> struct Fmt<__nv_bfloat16> {
@@ -138,9 +158,12 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   }
   const int len = (int)(t_end - t_begin);
   const int nc = (len + kChunk - 1) / kChunk;
+  const bool rev = a.reverse != 0;
 
   const uint32_t bar_full = smem_u32(&sm->full[0]), bar_empty = smem_u32(&sm->empty[0]);
   const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w);
+  const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
+  const uint32_t bar_t = smem_u32(&sm->bar_t), bar_y = smem_u32(&sm->bar_y);
   volatile int *abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -150,6 +173,11 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
     mbar_init(bar_p, 1);
     mbar_init(bar_w, 1);
+    mbar_init(bar_t, 1);
+    mbar_init(bar_d, kComputeThreads);
+    mbar_init(bar_y, kComputeThreads);
+    mbar_init(bar_f, kComputeThreads);
+    mbar_init(bar_h, kComputeThreads);
     sm->abort_flag = 0;
     sm->issued = 0;
     fence_barrier_init();
@@ -164,14 +192,14 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t tmem = sm->tmem_base;
 
   if (warp == kProducerWarp) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA loads
     if (lane == 0) {
       prefetch_tmap(&map_x);
       prefetch_tmap(&map_y);
       prefetch_tmap(&map_z);
       int it = 0;
       for (; it < nc; ++it) {
-        const int n = a.reverse ? (nc - 1 - it) : it;
+        const int n = rev ? (nc - 1 - it) : it;
         const int s = it & 1;
         const uint32_t ph = (uint32_t)(it >> 1) & 1u;
         mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
@@ -190,16 +218,86 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       sm->issued = it;
     }
     __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ tensor-core issue
+    if (lane == 0) {
+      const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
+      const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
+      const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
+      const uint64_t d_tb = desc_mnmajor(base + kOffTb, kBoxBytes);
+      for (int it = 0; it < nc; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
+        const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
+        const uint64_t d_xk = desc_kmajor(xs), d_yk = desc_kmajor(ys);
+        const uint64_t d_ymn = desc_mnmajor(ys, kBoxBytes), d_zmn = desc_mnmajor(zs, kBoxBytes);
+        // descriptor advance per 16-element K slice, in 16-byte units: K-major tiles step 32 B
+        // inside a 128 B row and jump to the second box after 4 slices; MN-major tiles step 16 rows
+        mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+          mma_ss(tmem + kColP, d_xk + ko, d_yk + ko, idesc_kk, ks > 0);
+        }
+        mma_commit(bar_p);
+        // W2 = X T_in: needs the state copy of this chunk and the previous epilogue's reads of W2
+        mbar_wait(bar_d, par, abort_flag, a.status, kStD);
+        if (it > 0) mbar_wait(bar_h, par ^ 1u, abort_flag, a.status, kStH);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+          mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
+        }
+        // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
+        // next chunk's state copy while P~ Z still runs
+        mbar_wait(bar_y, par, abort_flag, a.status, kStY);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+        mma_commit(bar_t);
+        mbar_wait(bar_f, par, abort_flag, a.status, kStF);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
+                 idesc_kmn, ks > 0);
+        mma_commit(bar_w);
+        // the next chunk's X Y^T overwrites P, which the product above reads as P~
+        mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kStoreWarp) {
+    // ------------------------------------------------------------------ TMA stores
+    if (lane == 0) {
+      for (int it = 0; it < nc; ++it) {
+        const int n = rev ? (nc - 1 - it) : it;
+        const int s = it & 1;
+        const uint32_t par = (uint32_t)it & 1u;
+        const int L = min(kChunk, len - n * kChunk);
+        mbar_wait(bar_h, par, abort_flag, a.status, kStH);
+        if (L == kChunk) {
+          const uint32_t xs = base + (uint32_t)s * kStageBytes;
+          const int tok0 = (int)t_begin + n * kChunk;
+          tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
+          tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        mbar_arrive(bar_empty + 8 * s);
+      }
+      tma_store_wait_all();
+    }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------------ compute warps
     const int wg = warp >> 2, q4 = warp & 3;
     const int i = q4 * 32 + lane;  // row of every 128-row tile this thread works on
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
-    const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
-    const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
-    const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
     const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
-    const bool rev = a.reverse != 0;
 
     // starting state -> tensor memory (this warpgroup's 64 columns)
     for (int b2 = 0; b2 < 2; ++b2) {
@@ -224,7 +322,87 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const long long tok = t_begin + (long long)n * kChunk + i;
       return a.ld[bidx * a.ld_sb + tok * a.ld_sn + h * a.ld_sh] * kLog2e;
     };
-    float ld_next = load_ld(0);
+
+    // Per-chunk decay quantities of this thread's row.
+    struct Decay {
+      float c;        // inclusive in-chunk cumulative log2 decay of row i
+      float wend[5];  // wend[b]: cumulative decay at the end of row batch b-1 (wend[4] = chunk total)
+      float eg, s, u; // e^g, output-row scale, Y-row scale
+    };
+    // A: cumulative decays of chunk `it`.  Contains a named barrier; cs/bs are overwritten only
+    // after it, i.e. after every thread has finished reading the previous chunk's values.
+    auto decay_of = [&](int it, float ldv) -> Decay {
+      Decay d;
+      const int n = rev ? (nc - 1 - it) : it;
+      const int L = min(kChunk, len - n * kChunk);
+      float c = ldv;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float nb = __shfl_up_sync(0xffffffffu, c, off);
+        if (lane >= off) c += nb;
+      }
+      if (wg == 0 && lane == 31) sm->wsum[q4] = c;
+      named_bar_sync(1, kComputeThreads);
+      d.wend[0] = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) d.wend[w + 1] = d.wend[w] + sm->wsum[w];
+      c += d.wend[q4];
+      const float g = d.wend[4];
+      d.c = c;
+      d.eg = ex2(g);
+      d.s = rev ? ex2(g - c) : ex2(c);
+      d.u = (i < L) ? (rev ? ex2(c) : ex2(g - c)) : 0.f;
+      if (wg == 0) {
+        sm->cs[i] = c;
+        sm->bs[i] = rev ? ((i < L) ? ex2(c - d.wend[q4]) : 0.f) : ex2(d.wend[q4 + 1] - c);
+      }
+      return d;
+    };
+    // D: state in -> 16-bit copy in shared memory (B operand of X T_in); T <- e^g T
+    auto state_copy = [&](float eg) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
+      tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
+      tmem_wait_ld();
+      uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        uint4 v;
+        v.x = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 0]), __uint_as_float(r0[pc * 8 + 1]));
+        v.y = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 2]), __uint_as_float(r0[pc * 8 + 3]));
+        v.z = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 4]), __uint_as_float(r0[pc * 8 + 5]));
+        v.w = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 6]), __uint_as_float(r0[pc * 8 + 7]));
+        *reinterpret_cast<uint4 *>(box + sw128_offset(i, pc)) = v;
+      }
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        uint4 v;
+        v.x = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 0]), __uint_as_float(r1[pc * 8 + 1]));
+        v.y = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 2]), __uint_as_float(r1[pc * 8 + 3]));
+        v.z = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 4]), __uint_as_float(r1[pc * 8 + 5]));
+        v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
+        *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
+      }
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        r0[k] = __float_as_uint(__uint_as_float(r0[k]) * eg);
+        r1[k] = __float_as_uint(__uint_as_float(r1[k]) * eg);
+      }
+      tmem_st32(tl + kColT + (2 * wg) * 32, r0);
+      tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar_d);
+    };
+
+    Decay cur{};
+    float ld_next = 0.f;
+    if (nc > 0) {
+      cur = decay_of(0, load_ld(0));
+      ld_next = load_ld(1);
+      state_copy(cur.eg);
+    }
 
     for (int it = 0; it < nc; ++it) {
       const int n = rev ? (nc - 1 - it) : it;
@@ -232,94 +410,37 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
-      const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
       uint8_t *stage = gbase + (size_t)s * kStageBytes;
+      const float c_i = cur.c;
 
-      // ---- A: in-chunk inclusive cumulative log2 decay c_i, warp-end sums, chunk total g
-      float c_i = ld_next;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float nb = __shfl_up_sync(0xffffffffu, c_i, off);
-        if (lane >= off) c_i += nb;
-      }
-      if (wg == 0 && lane == 31) sm->wsum[q4] = c_i;
-      named_bar_sync(1, kComputeThreads);
-      ld_next = load_ld(it + 1);  // in flight while this chunk is processed
-      float wend[5];              // wend[b] = cumulative decay at the end of row batch b-1
-      wend[0] = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) wend[w + 1] = wend[w] + sm->wsum[w];
-      c_i += wend[q4];
-      const float g = wend[4];
-      const float eg = exp2f(g);
-      const float s_i = rev ? exp2f(g - c_i) : exp2f(c_i);
-      const float u_i = (i < L) ? (rev ? exp2f(c_i) : exp2f(g - c_i)) : 0.f;
-      if (wg == 0) {
-        sm->cs[i] = c_i;
-        sm->bs[i] = rev ? ((i < L) ? exp2f(c_i - wend[q4]) : 0.f) : exp2f(wend[q4 + 1] - c_i);
-      }
-
-      // ---- B/C: operands landed -> P = X Y^T
+      LA_TRACE(0);
+      // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
       mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
-      tc_fence_after();
-      if (tid == 0) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColP, desc_kmajor(xs + kslice(ks)), desc_kmajor(ys + kslice(ks)), idesc_kk, ks > 0);
-        mma_commit(bar_p);
-      }
-
-      // ---- D: state in -> 16-bit copy in shared memory (B operand of X T_in); T <- e^g T
-      {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
-        tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
-        tmem_wait_ld();
-        uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 v;
-          v.x = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 0]), __uint_as_float(r0[pc * 8 + 1]));
-          v.y = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 2]), __uint_as_float(r0[pc * 8 + 3]));
-          v.z = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 4]), __uint_as_float(r0[pc * 8 + 5]));
-          v.w = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 6]), __uint_as_float(r0[pc * 8 + 7]));
-          *reinterpret_cast<uint4 *>(box + sw128_offset(i, pc)) = v;
-        }
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 v;
-          v.x = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 0]), __uint_as_float(r1[pc * 8 + 1]));
-          v.y = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 2]), __uint_as_float(r1[pc * 8 + 3]));
-          v.z = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 4]), __uint_as_float(r1[pc * 8 + 5]));
-          v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
-          *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
-        }
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          r0[k] = __float_as_uint(__uint_as_float(r0[k]) * eg);
-          r1[k] = __float_as_uint(__uint_as_float(r1[k]) * eg);
-        }
-        tmem_st32(tl + kColT + (2 * wg) * 32, r0);
-        tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
-      }
-      tmem_wait_st();
-      fence_proxy_async();
-      tc_fence_before();
-      named_bar_sync(1, kComputeThreads);
-
-      // ---- E: W2 = X T_in
-      if (tid == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColW2, desc_kmajor(xs + kslice(ks)),
-                 desc_mnmajor(base + kOffTb + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
-      }
-
-      // ---- F: P ready -> masked 16-bit P~ (first 16 columns of each 32-column batch of P);
-      //         Y <- Y (.) u in place (this warpgroup's 64 columns)
       mbar_wait(bar_p, par, abort_flag, a.status, kStP);
       tc_fence_after();
+      LA_TRACE(1);
+      {
+        uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
+        uint4 v[8];
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) v[pc] = *reinterpret_cast<const uint4 *>(ybox + sw128_offset(i, pc));
+        const float u_i = cur.u;
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) {
+          float2 f;
+          f = Fmt<T>::unpack(v[pc].x); v[pc].x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v[pc].y); v[pc].y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v[pc].z); v[pc].z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = Fmt<T>::unpack(v[pc].w); v[pc].w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+        }
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc) *reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc)) = v[pc];
+      }
+      fence_proxy_async();
+      mbar_arrive(bar_y);
+      LA_TRACE(2);
+
+      // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P)
 #pragma unroll 1
       for (int b2 = 0; b2 < 2; ++b2) {
         const int bt = wg + 2 * b2;  // batches {0,2} / {1,3}: balances the triangular work
@@ -333,7 +454,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           tmem_ld32(tl + kColP + bt * 32, r);
           tmem_wait_ld();
           if (bt != q4) {
-            const float ai = rev ? exp2f(wend[bt] - c_i) : exp2f(c_i - wend[bt + 1]);
+            const float ai = rev ? ex2(cur.wend[bt] - c_i) : ex2(c_i - cur.wend[bt + 1]);
 #pragma unroll
             for (int k = 0; k < 32; k += 4) {
               const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + k]);
@@ -359,44 +480,31 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         tmem_st16(tl + kColP + bt * 32, pk);
       }
-      {
-        uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
-#pragma unroll
-        for (int pc = 0; pc < 8; ++pc) {
-          uint4 *p = reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc));
-          uint4 v = *p;
-          float2 f;
-          f = Fmt<T>::unpack(v.x); v.x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v.y); v.y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v.z); v.z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v.w); v.w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          *p = v;
-        }
-      }
       tmem_wait_st();
-      fence_proxy_async();
       tc_fence_before();
-      named_bar_sync(1, kComputeThreads);
+      mbar_arrive(bar_f);
+      LA_TRACE(3);
 
-      // ---- G: W1 = P~ Z ; T += (Y (.) u)^T Z
-      if (tid == 0) {
+      // ---- while the tensor cores finish this chunk: decays and state copy of the next one
+      Decay nxt{};
+      if (it + 1 < nc) {  // uniform over the CTA
+        nxt = decay_of(it + 1, ld_next);
+        ld_next = load_ld(it + 2);
+        LA_TRACE(4);
+        mbar_wait(bar_t, par, abort_flag, a.status, kStT);  // T holds this chunk's final state
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8,
-                 desc_mnmajor(zs + ks * 2048, kBoxBytes), idesc_kmn, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColT, desc_mnmajor(ys + ks * 2048, kBoxBytes), desc_mnmajor(zs + ks * 2048, kBoxBytes),
-                 idesc_mnmn, 1);
-        mma_commit(bar_w);
+        LA_TRACE(5);
+        state_copy(nxt.eg);
       }
+      LA_TRACE(6);
 
-      // ---- H: epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
+      // ---- epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
       mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       tc_fence_after();
+      LA_TRACE(7);
       const bool full_chunk = (L == kChunk);
       const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
+      const float s_i = cur.s;
       float rd = 0.f;
 #pragma unroll 1
       for (int b2 = 0; b2 < 2; ++b2) {
@@ -435,22 +543,16 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
       }
-      if (a.rowdot != nullptr && wg == 1) sm->rd[i] = rd;
+      if (a.rowdot != nullptr) {  // uniform over the CTA
+        if (wg == 1) sm->rd[i] = rd;
+        named_bar_sync(2, kComputeThreads);
+        if (wg == 0 && i < L) a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd + sm->rd[i];
+      }
       if (full_chunk) fence_proxy_async();
       tc_fence_before();
-      named_bar_sync(1, kComputeThreads);
-      if (a.rowdot != nullptr && wg == 0 && i < L)
-        a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd + sm->rd[i];
-      if (tid == 0) {
-        if (full_chunk) {
-          const int tok0 = (int)t_begin + n * kChunk;
-          tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
-          tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
-          tma_store_commit();
-          tma_store_wait_read();
-        }
-        mbar_arrive(bar_empty + 8 * s);
-      }
+      mbar_arrive(bar_h);
+      LA_TRACE(8);
+      cur = nxt;
     }
 
     // end state -> global
@@ -468,7 +570,6 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
       }
     }
-    if (tid == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -523,6 +624,8 @@ int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
   return r == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
 }
 
+long long *g_trace = nullptr;
+
 template <typename T>
 int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
   alignas(64) CUtensorMap mx, my, mz, mo;
@@ -540,6 +643,7 @@ int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
+  a.trace = g_trace;
   auto kern = chunk_pass_kernel<T>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -673,6 +777,8 @@ int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, c
   if (dtype == LA_F16) return probe_t<__half>(variant, a, b, d, dtype, stream);
   return LA_ERR_UNSUPPORTED;
 }
+
+void chunk_set_trace(long long *buf) { g_trace = buf; }
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
   return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
