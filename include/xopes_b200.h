@@ -132,6 +132,18 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
                 void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Sequence-parallel scalar decay (no counterpart in the reference, which has no distributed code;
+ * the math is lasd_torch's varlen recurrence, scalar_decay/lasd_torch.py:61-103, cut at a rank
+ * boundary).  A rank whose first document started on an earlier rank runs la_lasd_fwd with a zero
+ * incoming state and then adds the missing term in place:
+ *     o[0,t,h,:] += exp(cum[t,h]) * q[0,t,h,:]^T s_in[h]      for t in [0, T1)
+ * q, o are (1,N,H,D) / (1,N,H,E); cum is fp32 (T1,H), the inclusive cumulative log decay from the
+ * rank's first token; s_in is fp32 (H,D,E), the document's true incoming state.
+ * ------------------------------------------------------------------------------------------- */
+LA_API int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int64_t T1,
+                             int64_t N, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Single-token decode: one new token per sequence, state read, updated and written once.
  * q, k (B,1,H,D), v, o (B,1,H,E); state_in / state_out (B,H,D,E) fp32 and MAY alias (in place).
  * Stand in for _lasd_recurrence_fwd with N == 1 (scalar_decay/lasd_recurrence_triton.py:28-113)

@@ -318,6 +318,19 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
 }
 
 // ------------------------------------------------------------------------------------------------
+// sequence-parallel correction
+// ------------------------------------------------------------------------------------------------
+int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int64_t T1,
+                      int64_t N, int64_t H, int64_t D, int64_t E, int dtype, void *stream) {
+  if (q == nullptr || o == nullptr || cum == nullptr || s_in == nullptr) return LA_ERR_NULL_POINTER;
+  if (T1 < 0 || T1 > N || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  if (!dtype_ok(dtype)) return LA_ERR_UNSUPPORTED;
+  if (N > (int64_t)1 << 30 || H > 65535) return LA_ERR_TOO_LARGE;
+  return launch_seqpar_correct(q, o, cum, s_in, (int)T1, (int)N, (int)H, (int)D, (int)E, dtype,
+                               static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------------------------
 // decode
 // ------------------------------------------------------------------------------------------------
 static int decode_common(const void *q, const void *k, const void *v, const float *ld,

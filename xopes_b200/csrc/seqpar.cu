@@ -1,0 +1,237 @@
+// Correction pass of the sequence-parallel scalar-decay forward.
+//
+// A rank that starts in the middle of a document first runs the ordinary varlen forward with a
+// zero incoming state.  Once the true incoming state S_in (H, D, E) of that document is known
+// (folded from the preceding ranks' chunk-end states), every token t of the document's local part
+// is missing the term
+//
+//     o_t += exp(cum_t) * q_t^T S_in ,   cum_t = sum of ld from the rank's first token to t.
+//
+// This file adds that term in place.  D = E = 128 with 16-bit tensors runs on tcgen05 (one
+// 128-token tile of q per CTA via TMA, S_in as a 16-bit MN-major operand); anything else runs a
+// plain fp32 kernel.
+#include <cuda.h>
+
+#include "chunk.cuh"
+#include "sm100_ptx.cuh"
+
+namespace la {
+namespace {
+
+using namespace ptx;
+
+// ------------------------------------------------------------------------------------------------
+// generic fp32 path: one thread per (token, head, e)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void seqpar_correct_generic(const T *__restrict__ q, T *o, const float *__restrict__ cum,
+                                       const float *__restrict__ s_in, int T1, int H, int D, int E) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)T1 * H * E;
+  if (idx >= total) return;
+  const int e = (int)(idx % E);
+  const int h = (int)((idx / E) % H);
+  const long long t = idx / ((long long)E * H);
+  const T *qr = q + (t * H + h) * (long long)D;
+  const float *s = s_in + (long long)h * D * E + e;
+  float acc = 0.f;
+  for (int d = 0; d < D; ++d) acc = fmaf(Cvt<T>::to_f(qr[d]), s[(long long)d * E], acc);
+  const float w = expf(cum[t * H + h]);
+  o[idx] = Cvt<T>::from_f(Cvt<T>::to_f(o[idx]) + w * acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// tensor-core path
+// ------------------------------------------------------------------------------------------------
+constexpr int kTile = 32768, kBox = 16384;
+
+struct SmallC {
+  unsigned long long full, done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T> struct FmtC;
+template <> struct FmtC<__nv_bfloat16> {
+  static constexpr uint32_t kAB = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+  }
+};
+template <> struct FmtC<__half> {
+  static constexpr uint32_t kAB = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&u));
+  }
+};
+
+// grid (tiles, H); 128 threads.  q is (1, N, H, 128); tokens [0, T1) are corrected.
+template <typename T>
+__global__ void __launch_bounds__(128, 1)
+seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *__restrict__ cum,
+                  const float *__restrict__ s_in, int T1, int H, int *status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  SmallC *sm = reinterpret_cast<SmallC *>(gbase + 2 * kTile);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int tok0 = tile * 128;
+  const uint32_t bar_full = smem_u32(&sm->full), bar_done = smem_u32(&sm->done);
+  volatile int *abort_flag = &sm->abort_flag;
+  if (tid == 0) {
+    mbar_init(bar_full, 1);
+    mbar_init(bar_done, 1);
+    sm->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&sm->tmem_base), 128);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const uint32_t qs = base, ss = base + kTile;
+  if (tid == 0) {
+    mbar_arrive_expect_tx(bar_full, kTile);
+    tma_load_4d(qs, &map_q, bar_full, 0, h, tok0, 0);
+    tma_load_4d(qs + kBox, &map_q, bar_full, 64, h, tok0, 0);
+  }
+  // S_in[h] row d (= tid) -> 16-bit, MN-major swizzled tile [d][e]
+  {
+    const float4 *src = reinterpret_cast<const float4 *>(s_in + ((long long)h * 128 + tid) * 128);
+#pragma unroll 4
+    for (int pc = 0; pc < 16; ++pc) {
+      const float4 a = src[pc * 2], b = src[pc * 2 + 1];
+      uint4 v;
+      v.x = FmtC<T>::pack(a.x, a.y); v.y = FmtC<T>::pack(a.z, a.w);
+      v.z = FmtC<T>::pack(b.x, b.y); v.w = FmtC<T>::pack(b.z, b.w);
+      *reinterpret_cast<uint4 *>(gbase + kTile + (pc >> 3) * kBox + sw128_offset(tid, pc & 7)) = v;
+    }
+  }
+  fence_proxy_async();
+  mbar_wait(bar_full, 0, abort_flag, status, 201);
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t idesc = instr_desc(FmtC<T>::kAB, 0, 1, 128, 128);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      mma_ss(tmem, desc_kmajor(qs + (uint32_t)(ks >> 2) * kBox + (uint32_t)(ks & 3) * 32u),
+             desc_mnmajor(ss + ks * 2048, kBox), idesc, ks > 0);
+    mma_commit(bar_done);
+  }
+  mbar_wait(bar_done, 0, abort_flag, status, 202);
+  tc_fence_after();
+  const int t = tok0 + tid;
+  const uint32_t tl = tmem + ((uint32_t)(32 * warp) << 16);
+  const float w = (t < T1) ? expf(cum[(long long)t * H + h]) : 0.f;
+  T *orow = o + ((long long)t * H + h) * 128;
+  for (int bt = 0; bt < 4; ++bt) {
+    uint32_t r[32];
+    tmem_ld32(tl + bt * 32, r);
+    tmem_wait_ld();
+    if (t < T1) {
+      uint4 *op = reinterpret_cast<uint4 *>(orow + bt * 32);
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        uint4 v = op[pc];
+        float2 f;
+        f = FmtC<T>::unpack(v.x); v.x = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 0]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 1]), f.y));
+        f = FmtC<T>::unpack(v.y); v.y = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 2]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 3]), f.y));
+        f = FmtC<T>::unpack(v.z); v.z = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 4]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 5]), f.y));
+        f = FmtC<T>::unpack(v.w); v.w = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 6]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 7]), f.y));
+        op[pc] = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+int make_q_map(CUtensorMap *m, const void *ptr, int dtype, int N, int H) {
+  static EncodeTiledFn enc = nullptr;
+  if (enc == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      return LA_ERR_CUDA;
+    enc = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
+  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, 1};
+  const cuuint64_t strides[3] = {256, (cuuint64_t)H * 256, (cuuint64_t)N * H * 256};
+  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == LA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
+}
+
+template <typename T>
+int launch_tc(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H, int dtype,
+              cudaStream_t st) {
+  alignas(64) CUtensorMap mq;
+  int rc = make_q_map(&mq, q, dtype, N, H);
+  if (rc != LA_OK) return rc;
+  if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(s_in)) & 15u) return LA_ERR_MISALIGNED;
+  int *status = status_word_ptr();
+  if (status == nullptr) return LA_ERR_CUDA;
+  const int smem = 2 * kTile + 64 + 1024;
+  auto kern = seqpar_correct_tc<T>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return LA_ERR_CUDA;
+  dim3 grid((T1 + 127) / 128, H);
+  kern<<<grid, 128, smem, st>>>(mq, static_cast<T *>(o), cum, s_in, T1, H, status);
+  return launch_status();
+}
+
+template <typename T>
+int launch_generic(const void *q, void *o, const float *cum, const float *s_in, int T1, int H, int D, int E,
+                   cudaStream_t st) {
+  const long long total = (long long)T1 * H * E;
+  const int threads = 256;
+  const long long blocks = (total + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return LA_ERR_TOO_LARGE;
+  seqpar_correct_generic<T><<<(unsigned)blocks, threads, 0, st>>>(static_cast<const T *>(q), static_cast<T *>(o),
+                                                                  cum, s_in, T1, H, D, E);
+  return launch_status();
+}
+
+}  // namespace
+
+int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,
+                          int D, int E, int dtype, cudaStream_t st) {
+  if (T1 <= 0) return LA_OK;
+  if (D == 128 && E == 128 && N >= 128 && (dtype == LA_BF16 || dtype == LA_F16)) {
+    return dtype == LA_BF16 ? launch_tc<__nv_bfloat16>(q, o, cum, s_in, T1, N, H, dtype, st)
+                            : launch_tc<__half>(q, o, cum, s_in, T1, N, H, dtype, st);
+  }
+  switch (dtype) {
+    case LA_F32: return launch_generic<float>(q, o, cum, s_in, T1, H, D, E, st);
+    case LA_BF16: return launch_generic<__nv_bfloat16>(q, o, cum, s_in, T1, H, D, E, st);
+    case LA_F16: return launch_generic<__half>(q, o, cum, s_in, T1, H, D, E, st);
+  }
+  return LA_ERR_UNSUPPORTED;
+}
+
+}  // namespace la

@@ -1,0 +1,181 @@
+"""Sequence-parallel scalar-decay forward for one long packed (varlen) stream.
+
+The reference has no distributed code; what is fixed by it is the single-device math of
+lasd_torch's varlen branch (xopes/ops/lightning_attn/scalar_decay/lasd_torch.py:61-103): documents
+are independent recurrences, the state restarts at every boundary.  Here the token stream is cut
+into contiguous ranges, one per rank, and a document that crosses a cut is stitched together:
+
+  phase 1 (local)    every rank runs the ordinary varlen forward on its tokens with a zero
+                     incoming state -> local o, per-document end states;
+  phase 2 (exchange) every rank publishes (S_loc, G, open_end, spans): the end state of its last
+                     local document, the summed log decay over that document's local part, and
+                     whether the document continues on the next rank / covers the whole rank.
+                     One all-gather (NCCL) moves them; each rank folds the ranks before it:
+                         S_in(r+1) = open_end(r) * ( S_loc(r) + spans(r) * exp(G(r)) * S_in(r) )
+  phase 3 (local)    a rank whose first document began earlier adds the missing term
+                         o_t += exp(cum_t) q_t^T S_in        (la_seqpar_correct)
+                     to that document's local tokens and exp(G_first) S_in to its end state.
+
+The three phases are separate functions so that tests can run them with any transport (gloo ranks
+on CPU, or several emulated ranks in one process); lasd_seqpar_forward composes them over
+torch.distributed.
+"""
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+
+@dataclass
+class ShardPlan:
+    start: int                 # first global token of this rank
+    end: int                   # one past the last
+    local_cu: List[int]        # document boundaries relative to `start` (first 0, last end-start)
+    doc_ids: List[int]         # global index of every local document
+    open_start: bool           # first local document began on an earlier rank
+    open_end: bool             # last local document continues on the next rank
+
+
+def token_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous, near-equal split of n_total tokens."""
+    per = (n_total + world - 1) // world
+    return min(rank * per, n_total), min((rank + 1) * per, n_total)
+
+
+def shard_documents(cu_seqlens: List[int], start: int, end: int) -> ShardPlan:
+    """Intersect the documents [cu[i], cu[i+1]) with the rank's range [start, end)."""
+    local_cu, doc_ids = [0], []
+    open_start = open_end = False
+    for i in range(len(cu_seqlens) - 1):
+        a, b = cu_seqlens[i], cu_seqlens[i + 1]
+        lo, hi = max(a, start), min(b, end)
+        if lo >= hi:
+            continue
+        if not doc_ids and a < start:
+            open_start = True
+        doc_ids.append(i)
+        local_cu.append(hi - start)
+        open_end = b > end
+    return ShardPlan(start, end, local_cu, doc_ids, open_start, open_end)
+
+
+def _ld_local(ld: torch.Tensor, t: int, h: int) -> torch.Tensor:
+    """Per-token log decay of the local range as a (T, H) fp32 view (expanded, not copied)."""
+    if ld.dim() == 1:
+        return ld.float().view(1, h).expand(t, h)
+    return ld.float().reshape(t, h)
+
+
+def _cuda_local_forward(q, k, v, ld, local_cu):
+    from .scalar_decay import lasd_fn
+    cu = torch.tensor(local_cu, dtype=torch.int64, device=q.device)
+    with torch.no_grad():
+        return lasd_fn(q, k, v, ld, cu_seqlens=cu)
+
+
+def _cuda_correct(q, o, cum, s_in, t1):
+    lib = _lib.load()
+    _lib.require_cuda(q, o, cum, s_in)
+    _, n, h, d = q.shape
+    e = o.shape[-1]
+    cum = cum.contiguous()
+    s_in = s_in.contiguous()
+    with torch.cuda.device(q.device):
+        rc = lib.la_seqpar_correct(_lib.ptr(q), _lib.ptr(o), _lib.ptr(cum), _lib.ptr(s_in), t1, n, h, d, e,
+                                   _lib.dtype_code(q), _lib.stream_of(q))
+    _lib.check(rc, "la_seqpar_correct")
+
+
+def local_phase(q, k, v, ld, plan: ShardPlan, local_forward: Optional[Callable] = None):
+    """Phase 1.  Returns (o, states, summary) where summary is the flat fp32 tensor a rank
+    publishes: [S_loc (H*D*E), G (H), open_end, spans]."""
+    fwd = local_forward or _cuda_local_forward
+    _, t, h, d = q.shape
+    o, states = fwd(q, k, v, ld, plan.local_cu)
+    e = o.shape[-1]
+    dev = q.device
+    summary = torch.zeros(h * d * e + h + 2, dtype=torch.float32, device=dev)
+    if plan.open_end:
+        last0 = plan.local_cu[-2]
+        summary[: h * d * e] = states[-1].reshape(-1)
+        summary[h * d * e: h * d * e + h] = _ld_local(ld, t, h)[last0:].sum(0)
+        summary[-2] = 1.0
+        summary[-1] = 1.0 if (plan.open_start and len(plan.doc_ids) == 1) else 0.0
+    return o, states, summary
+
+
+def fold_incoming_state(gathered: torch.Tensor, rank: int, h: int, d: int, e: int) -> torch.Tensor:
+    """Phase 2, after the all-gather: the true state entering `rank`, from the summaries of the
+    ranks before it (gathered is (world, H*D*E + H + 2)).  No host synchronisation."""
+    s_in = torch.zeros(h, d, e, dtype=torch.float32, device=gathered.device)
+    for r in range(rank):
+        row = gathered[r]
+        s_loc = row[: h * d * e].view(h, d, e)
+        g = row[h * d * e: h * d * e + h]
+        open_end, spans = row[-2], row[-1]
+        s_in = open_end * (s_loc + spans * torch.exp(g).view(h, 1, 1) * s_in)
+    return s_in
+
+
+def correct_phase(q, o, states, ld, s_in, plan: ShardPlan, correct: Optional[Callable] = None):
+    """Phase 3, in place on o and states."""
+    if not plan.open_start:
+        return
+    fix = correct or _cuda_correct
+    _, t, h, _ = q.shape
+    t1 = plan.local_cu[1]
+    cum = torch.cumsum(_ld_local(ld, t, h)[:t1], dim=0).contiguous()
+    fix(q, o, cum, s_in, t1)
+    states[0] += torch.exp(cum[t1 - 1]).view(h, 1, 1) * s_in
+
+
+def lasd_seqpar_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: torch.Tensor,
+                        cu_seqlens: torch.Tensor, group=None, exchange: str = "all_gather",
+                        local_forward: Optional[Callable] = None, correct: Optional[Callable] = None):
+    """Forward of lasd over a packed stream sharded by tokens across the ranks of `group`.
+
+    q, k (1, T_r, H, D) and v (1, T_r, H, E) are THIS rank's contiguous token range
+    (token_range(N, rank, world)); ld is (H,) or the local (1, T_r, H) slice; cu_seqlens holds the
+    GLOBAL document boundaries.  Returns (o_local, states, plan): o for the local tokens, and the
+    end state of every local document (for a document that continues on the next rank this is its
+    state at the end of this rank).
+
+    exchange = "all_gather": one collective, every rank folds its own prefix (default);
+               "chain": rank r receives S_in from r-1 and sends its outgoing state to r+1
+               (send/recv, world-1 serial hops).
+    """
+    import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    cu = [int(x) for x in cu_seqlens.tolist()]
+    n_total = cu[-1]
+    start, end = token_range(n_total, rank, world)
+    if q.shape[1] != end - start:
+        raise ValueError(f"rank {rank} holds {q.shape[1]} tokens, expected {end - start}")
+    plan = shard_documents(cu, start, end)
+    _, _, h, d = q.shape
+    e = v.shape[-1]
+    o, states, summary = local_phase(q, k, v, ld, plan, local_forward)
+    if exchange == "all_gather":
+        gathered = torch.empty(world * summary.numel(), dtype=torch.float32, device=summary.device)
+        dist.all_gather_into_tensor(gathered, summary, group=group)
+        s_in = fold_incoming_state(gathered.view(world, -1), rank, h, d, e)
+    elif exchange == "chain":
+        s_in = torch.zeros(h, d, e, dtype=torch.float32, device=summary.device)
+        if rank > 0:
+            dist.recv(s_in, src=dist.get_global_rank(group, rank - 1) if group else rank - 1, group=group)
+        if rank < world - 1:
+            s_out = fold_incoming_state_step(summary, s_in, h, d, e)
+            dist.send(s_out, dst=dist.get_global_rank(group, rank + 1) if group else rank + 1, group=group)
+    else:
+        raise ValueError(f"unknown exchange {exchange!r}")
+    correct_phase(q, o, states, ld, s_in, plan, correct)
+    return o, states, plan
+
+
+def fold_incoming_state_step(row: torch.Tensor, s_in: torch.Tensor, h: int, d: int, e: int) -> torch.Tensor:
+    """One hop of the fold: the state leaving a rank, given its summary row and its own S_in."""
+    s_loc = row[: h * d * e].view(h, d, e)
+    g = row[h * d * e: h * d * e + h]
+    return (row[-2] * (s_loc + row[-1] * torch.exp(g).view(h, 1, 1) * s_in)).contiguous()
