@@ -109,7 +109,7 @@ class ClockSampler:
 def make_workload(name, rank, shape=None):
     from xopes_b200 import workloads as W
     cfg = dict(W.CONFIGS[name])
-    if shape:  # smaller case of the same kernel, for profiler captures
+    if shape and name != "C5":  # smaller case of the same kernel, for profiler captures
         b, n, h = (int(x) for x in shape.split(","))
         cfg.update(B=b, N=n, H=h) if name != "C4" else cfg.update(B=b, H=h)
     seed = rank  # every rank draws its own batch
@@ -122,6 +122,18 @@ def make_workload(name, rank, shape=None):
         w = W.lavd_inputs(cfg["B"], cfg["N"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, seed)
         tokens = cfg["B"] * cfg["N"]
         alg_bytes = tokens * cfg["H"] * (W.BYTES_LAVD_FWD + W.BYTES_LAVD_BWD)
+        units = "tokens"
+    elif name == "C5":
+        import torch.distributed as dist
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        if shape:
+            cfg.update(N=int(shape.split(",")[1]), H=int(shape.split(",")[2]))
+        from xopes_b200.lightning_attn.seq_parallel import token_range
+        rng = token_range(cfg["N"], rank, world)
+        w = W.varlen_inputs(cfg["N"], cfg["docs"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, 0,
+                            token_range=rng)
+        tokens = cfg["N"]  # the whole stream: ranks split it (strong scaling)
+        alg_bytes = tokens * cfg["H"] * W.BYTES_LASD_FWD
         units = "tokens"
     elif name == "C4":
         w = W.decode_inputs(cfg["B"], cfg["H"], cfg["D"], cfg["E"], cfg["steps"], False, seed=seed)
@@ -217,6 +229,47 @@ class DecodeStep:
         return self.o
 
 
+class VarlenStep:
+    """Configuration 5: forward of one packed 1M-token stream of 64 documents.  One GPU runs the
+    varlen chunk kernel over the whole stream; with N ranks every rank owns a contiguous token
+    range and the ranks exchange chunk-end states (one NCCL all-gather) before a local correction
+    pass."""
+
+    def __init__(self, w, dev, world):
+        import xopes_b200 as xb
+        self.xb = xb
+        self.dev = dev
+        self.world = world
+        self.host = {k: pin(v) for k, v in w.items() if k != "cu_seqlens"}
+        self.cu_host = w["cu_seqlens"]
+        self.d = {k: v.to(dev) for k, v in self.host.items()}
+        self.cu = self.cu_host.to(dev)
+        self.h2d = sum(v.numel() * v.element_size() for v in self.host.values())
+        self.launches_per_step = 1 if world == 1 else 2
+        self.out_host = None
+
+    def _fwd(self, d):
+        with torch.no_grad():
+            if self.world == 1:
+                return self.xb.lasd_fn(d["q"], d["k"], d["v"], d["ld"], cu_seqlens=self.cu)
+            o, st, _ = self.xb.lasd_seqpar_forward(d["q"], d["k"], d["v"], d["ld"], self.cu_host)
+            return o, st
+
+    def step(self):
+        return self._fwd(self.d)
+
+    def step_e2e(self):
+        d = {k: v.to(self.dev, non_blocking=True) for k, v in self.host.items()}
+        o, st = self._fwd(d)
+        if self.out_host is None:
+            self.out_host = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True),
+                             torch.empty(st.shape, dtype=st.dtype, pin_memory=True)]
+        self.out_host[0].copy_(o, non_blocking=True)
+        self.out_host[1].copy_(st, non_blocking=True)
+        self.d2h = o.numel() * o.element_size() + st.numel() * st.element_size()
+        return o
+
+
 def time_steps(fn, steps, warmup, world, sampler=None):
     import torch.distributed as dist
     for _ in range(warmup):
@@ -255,8 +308,29 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
     from oracle import lightning_attn_oracle as orc
     from xopes_b200 import workloads as W
     threads = torch.get_num_threads()
+    if name == "C5":
+        lens = W.varlen_doc_lengths(cfg["N"], cfg["docs"], 0)
+        cu = [0] + [int(x) for x in torch.cumsum(lens, 0)]
+        # sample: the shortest document and as many leading documents as fit ~24K tokens
+        picks, budget = [int(torch.argmin(lens))], 24000
+        for i in range(cfg["docs"]):
+            if i not in picks and int(lens[i]) <= budget:
+                picks.append(i)
+                budget -= int(lens[i])
+        ntok, dt = 0, 0.0
+        for i in picks:
+            w = W.varlen_inputs(cfg["N"], cfg["docs"], cfg["H"], cfg["D"], cfg["E"], torch.bfloat16, 0,
+                                token_range=(cu[i], cu[i + 1]))
+            t0 = time.perf_counter()
+            orc.lasd_forward(w["q"].float(), w["k"].float(), w["v"].float(), w["ld"])
+            dt += time.perf_counter() - t0
+            ntok += cu[i + 1] - cu[i]
+        val = ntok / dt
+        sample = (f"oracle lasd forward on {len(picks)} of {cfg['docs']} documents ({ntok} tokens), "
+                  f"{dt:.1f} s; documents are independent, cost is linear in tokens")
+        return val, sample, threads
     if name == "C2":
-        bs, hs, n = 1, 2, cfg["N"]
+        bs, hs, n = 1, 16, cfg["N"]
         w = W.lasd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
         f = {k: v.float() for k, v in w.items()}
         ld = f["ld"]
@@ -328,18 +402,22 @@ def run_reference(args, rank, world):
 
 
 def metric_name(workload):
-    return {"C2": "lasd fwd+bwd tokens/s (bf16 N8K H32 D128)",
+    return {"C5": "lasd varlen fwd tokens/s (bf16 N1M 64 docs H16 D128)",
+            "C2": "lasd fwd+bwd tokens/s (bf16 N8K H32 D128)",
             "C3": "lavd fwd+bwd tokens/s (bf16 N16K H16 D128)",
             "C4": "decode tokens/s (B256 H32 D128, 64-step loop)"}[workload]
 
 
 def workload_config(name, cfg, world):
     c = {"workload": f"{name}: " + {
+        "C5": "lasd forward, one packed stream of 64 documents, sequence-sharded across ranks",
         "C2": "lasd forward+backward, per-head scalar decay, fp32 initial state",
         "C3": "lavd forward+backward, ldk = logsigmoid(x)/16, no initial state",
         "C4": "recurrent decode, scalar decay, 64-step loop, fp32 state in place"}[name]}
     c.update({k: v for k, v in cfg.items() if k != "kind"})
-    c["partition"] = f"batch x head, one full batch per GPU, {world} GPU(s), no collective"
+    c["partition"] = (f"contiguous token ranges over {world} GPU(s); one all-gather of chunk-end states"
+                      if name == "C5" else
+                      f"batch x head, one full batch per GPU, {world} GPU(s), no collective")
     c["l2"] = "inputs per step exceed the 126 MB L2 (no flush needed)"
     return c
 
@@ -350,7 +428,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="C2", choices=["C2", "C3", "C4"])
+    ap.add_argument("--workload", default="C2", choices=["C2", "C3", "C4", "C5"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--shape", default=None, help="B,N,H override (profiling a smaller case)")
@@ -370,19 +448,24 @@ def main():
     warmup = max(args.warmup, 3)
 
     cfg, w, tokens, alg_bytes, _ = make_workload(args.workload, rank, args.shape)
-    runner = {"C2": LasdStep, "C3": LavdStep, "C4": DecodeStep}[args.workload](w, dev)
+    if args.workload == "C5":
+        runner = VarlenStep(w, dev, world)
+    else:
+        runner = {"C2": LasdStep, "C3": LavdStep, "C4": DecodeStep}[args.workload](w, dev)
+    strong = args.workload == "C5"
     torch.cuda.synchronize()
 
     sampler = ClockSampler(local) if rank == 0 else None
     ms, clocks = time_steps(runner.step, args.steps, warmup, world, sampler)
     ms_step = ms / args.steps
-    value = tokens * world / (ms_step * 1e-3)
+    nrep = 1 if strong else world  # C5 splits one stream; the others replicate a batch per rank
+    value = tokens * nrep / (ms_step * 1e-3)
 
     e2e = None
     if not args.no_e2e:
         ms_e, _ = time_steps(runner.step_e2e, max(2, args.steps // 3), 1, world)
         ms_e /= max(2, args.steps // 3)
-        e2e = {"value": tokens * world / (ms_e * 1e-3), "unit": "tokens/s",
+        e2e = {"value": tokens * nrep / (ms_e * 1e-3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(runner.h2d), "d2h_bytes_per_step": int(runner.d2h),
                "ms_per_step": ms_e}
 
@@ -390,6 +473,8 @@ def main():
         from xopes_b200 import _lib
         peaks = measured_peaks()
         launches = runner.launches_per_step
+        if strong:
+            launches, alg_bytes = 1, alg_bytes / world  # the varlen forward kernel on this rank's share
         per_launch_bytes = alg_bytes / launches
         per_launch_s = ms_step * 1e-3 / launches
         achieved = per_launch_bytes / per_launch_s / 1e9
@@ -400,13 +485,14 @@ def main():
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None,
                 "peak_source": peaks["source"],
                 "kernel": {"C2": "chunk_pass_kernel" if tensor_path == 1 else "scan_kernel",
-                           "C3": "scan_kernel", "C4": "decode_kernel"}[args.workload],
+                           "C3": "scan_kernel", "C4": "decode_kernel",
+                           "C5": "chunk_pass_kernel"}[args.workload],
                 "algorithmic_bytes_per_launch": per_launch_bytes,
                 "avg_launch_ms": per_launch_s * 1e3}
         line = {
             "metric": metric_name(args.workload), "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, cfg, world),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps,

@@ -100,7 +100,10 @@ def local_phase(q, k, v, ld, plan: ShardPlan, local_forward: Optional[Callable] 
     if plan.open_end:
         last0 = plan.local_cu[-2]
         summary[: h * d * e] = states[-1].reshape(-1)
-        summary[h * d * e: h * d * e + h] = _ld_local(ld, t, h)[last0:].sum(0)
+        if ld.dim() == 1:
+            summary[h * d * e: h * d * e + h] = ld.float() * float(t - last0)
+        else:
+            summary[h * d * e: h * d * e + h] = _ld_local(ld, t, h)[last0:].sum(0)
         summary[-2] = 1.0
         summary[-1] = 1.0 if (plan.open_start and len(plan.doc_ids) == 1) else 0.0
     return o, states, summary
@@ -126,7 +129,14 @@ def correct_phase(q, o, states, ld, s_in, plan: ShardPlan, correct: Optional[Cal
     fix = correct or _cuda_correct
     _, t, h, _ = q.shape
     t1 = plan.local_cu[1]
-    cum = torch.cumsum(_ld_local(ld, t, h)[:t1], dim=0).contiguous()
+    if ld.dim() == 1:
+        # constant per-head decay: closed form, no scan
+        steps = torch.arange(1, t1 + 1, dtype=torch.float32, device=q.device)
+        cum = steps.view(t1, 1) * ld.float().view(1, h)
+    else:
+        # scan along the contiguous axis of a (H, T1) copy: torch's outer-dimension scan walks one
+        # column per thread and takes milliseconds for a few thousand tokens
+        cum = torch.cumsum(_ld_local(ld, t, h)[:t1].t().contiguous(), dim=1).t().contiguous()
     fix(q, o, cum, s_in, t1)
     states[0] += torch.exp(cum[t1 - 1]).view(h, 1, 1) * s_in
 

@@ -81,21 +81,30 @@ def varlen_doc_lengths(n_total, n_docs, seed=0):
     return lens
 
 
-def varlen_inputs(n_total, n_docs, h, d, e, dtype=torch.bfloat16, seed=0, block=65536):
-    """Configuration 5: one packed stream, q,k,v ~ N(0,1), q and k scaled by 1/sqrt(D), generated in
-    blocks of tokens to bound host memory; ld_h = log(1 - 2^(-5 - h/2))."""
+def varlen_inputs(n_total, n_docs, h, d, e, dtype=torch.bfloat16, seed=0, block=65536,
+                  token_range=None):
+    """Configuration 5: one packed stream, q,k,v ~ N(0,1), q and k scaled by 1/sqrt(D);
+    ld_h = log(1 - 2^(-5 - h/2)).  The stream is generated in blocks of `block` tokens, each from
+    its own generator seeded by (seed, block index), so a rank can generate just its own token
+    range [a, b) and still see exactly the values of the whole stream."""
     lens = varlen_doc_lengths(n_total, n_docs, seed)
     cu = torch.zeros(n_docs + 1, dtype=torch.int64)
     cu[1:] = torch.cumsum(lens, 0)
-    g = _gen(seed + 1)
-    q = torch.empty(1, n_total, h, d, dtype=dtype)
-    k = torch.empty(1, n_total, h, d, dtype=dtype)
-    v = torch.empty(1, n_total, h, e, dtype=dtype)
-    for s in range(0, n_total, block):
-        t = min(block, n_total - s)
-        q[0, s:s + t] = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
-        k[0, s:s + t] = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
-        v[0, s:s + t] = torch.randn(t, h, e, generator=g).to(dtype)
+    a, b = token_range if token_range is not None else (0, n_total)
+    q = torch.empty(1, b - a, h, d, dtype=dtype)
+    k = torch.empty(1, b - a, h, d, dtype=dtype)
+    v = torch.empty(1, b - a, h, e, dtype=dtype)
+    for j in range(a // block, (b + block - 1) // block):
+        s0, s1 = j * block, min((j + 1) * block, n_total)
+        t = s1 - s0
+        g = _gen((seed + 1) * 100003 + j)
+        qb = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
+        kb = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
+        vb = torch.randn(t, h, e, generator=g).to(dtype)
+        lo, hi = max(s0, a), min(s1, b)
+        q[0, lo - a:hi - a] = qb[lo - s0:hi - s0]
+        k[0, lo - a:hi - a] = kb[lo - s0:hi - s0]
+        v[0, lo - a:hi - a] = vb[lo - s0:hi - s0]
     return dict(q=q, k=k, v=v, ld=per_head_log_decay(h, 0.5), cu_seqlens=cu)
 
 
