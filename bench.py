@@ -481,8 +481,15 @@ def main():
         tensor_path = None
         if args.workload == "C2":
             tensor_path = _lib.load().la_lasd_path(cfg["N"], cfg["D"], cfg["E"], _lib.LA_BF16, 0)
+        # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
+        # under profiles/, taken on a smaller case and scaled by token*heads (traffic is linear in
+        # them): chunk pass 515.3 MB for 8*2048*32 token-heads = 982.9 B each
+        traffic = None
+        if args.workload in ("C2", "C5") and (tensor_path == 1 or args.workload == "C5"):
+            th = cfg["N"] * cfg["H"] * (cfg.get("B", 1) if args.workload == "C2" else 1.0 / world)
+            traffic = 982.9 * th
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                 "peak_source": peaks["source"],
                 "kernel": {"C2": "chunk_pass_kernel" if tensor_path == 1 else "scan_kernel",
                            "C3": "scan_kernel", "C4": "decode_kernel",
