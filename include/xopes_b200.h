@@ -103,6 +103,35 @@ LA_API int la_lasd_bwd(const void *q, const void *k, const void *v, const float 
                 int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
                 int64_t M, int dtype, unsigned flags, void *stream);
 
+/* la_lasd_bwd for callers that cannot hand over scratch memory.  It has no counterpart in the
+ * reference (whose Python drivers allocate freely with torch.empty).
+ *
+ * Some hosts of this library are not allowed to allocate device memory at the point where they
+ * call it: a serving runtime whose whole memory budget was carved up at start-up, a plugin whose
+ * "enqueue" hook is forbidden from touching the allocator, or a latency-critical loop where an
+ * allocator call could stall the device.  For them this entry point takes the same arguments as
+ * la_lasd_bwd minus workspace / workspace_bytes and keeps the scratch inside the library, in a
+ * fixed device array of LA_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds until
+ * the process exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - Limit: la_lasd_bwd_workspace_bytes(B, N, H, D, E, M, dld != NULL) must not exceed
+ *    LA_NOALLOC_SCRATCH_BYTES, otherwise LA_ERR_TOO_LARGE is returned and nothing is launched.
+ *    (Without dld the requirement is 0, so any size passes.)
+ *  - The first call on each device looks up the array's device address (one runtime query, with
+ *    that device current).  Make that first call before starting any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents.  Nothing in it needs
+ *    to be zero on entry (each call writes every word before reading it), but two calls whose
+ *    kernels overlap on the GPU -- different streams, or different threads on one device -- race
+ *    on it: serialise them. */
+#define LA_NOALLOC_SCRATCH_BYTES (8u << 20)
+LA_API int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, const float *ld,
+                               int64_t ld_sb, int64_t ld_sn, int64_t ld_sh,
+                               const float *initial_state, const void *d_o,
+                               const float *dfinal_state, const int64_t *cu_seqlens, void *dq,
+                               void *dk, void *dv, float *dld, float *dinitial_state, int64_t B,
+                               int64_t N, int64_t H, int64_t D, int64_t E, int64_t M, int dtype,
+                               unsigned flags, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Vector decay (lavd).  ldk (B,N,H,D) and ldv (B,N,H,E) are fp32, contiguous; either may be NULL
  * (not both).

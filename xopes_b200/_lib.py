@@ -34,6 +34,8 @@ SIGNATURES = {
     "la_lasd_bwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32,
                            _vp]),
+    "la_lasd_bwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
+                                   _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
     "la_lavd_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
     "la_lavd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64]),

@@ -232,6 +232,43 @@ int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, in
 }
 
 // ------------------------------------------------------------------------------------------------
+// la_lasd_bwd without caller scratch
+// ------------------------------------------------------------------------------------------------
+// Scratch that lives in the library image: one copy per GPU that loads the library, held until
+// the process exits.  Host code may not use the array's name as a pointer (on the host the name
+// is only a handle for the runtime); the device address is looked up once per device below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LA_NOALLOC_SCRATCH_BYTES];
+
+static void *noalloc_scratch_ptr() {
+  static void *ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess) return nullptr;
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                        int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
+                        const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
+                        void *dv, float *dld, float *dinitial_state, int64_t B, int64_t N, int64_t H,
+                        int64_t D, int64_t E, int64_t M, int dtype, unsigned flags, void *stream) {
+  if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  const int64_t need = la_lasd_bwd_workspace_bytes(B, N, H, D, E, M, dld != nullptr);
+  if (need > (int64_t)LA_NOALLOC_SCRATCH_BYTES) return LA_ERR_TOO_LARGE;
+  void *scratch = noalloc_scratch_ptr();
+  if (scratch == nullptr) return LA_ERR_CUDA;
+  // Nothing in the scratch has to start at zero: the row-dot slots and the recomputed final state
+  // are written in full by the dq / dk passes of this call before the reduction reads them.
+  return la_lasd_bwd(q, k, v, ld, ld_sb, ld_sn, ld_sh, initial_state, d_o, dfinal_state, cu_seqlens, dq,
+                     dk, dv, dld, dinitial_state, scratch, (int64_t)LA_NOALLOC_SCRATCH_BYTES, B, N, H, D, E,
+                     M, dtype, flags, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
 // vector decay
 // ------------------------------------------------------------------------------------------------
 int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
