@@ -91,11 +91,15 @@ struct ChunkArgs {
 };
 
 // trace[thread slot][chunk][point]: 16 points per chunk, 2 thread slots of 4096 chunks at most
+#ifdef LA_CHUNK_TRACE
 #define LA_TRACE(point)                                                                   \
   do {                                                                                    \
     if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32) && it < 4096)      \
       a.trace[((tid >> 5) * 4096 + it) * 16 + (point)] = clock64();                       \
   } while (0)
+#else
+#define LA_TRACE(point) do { } while (0)
+#endif
 
 template <typename T> struct Fmt;
 template <> struct Fmt<__nv_bfloat16> {
@@ -121,6 +125,11 @@ template <> struct Fmt<__half> {
 
 // byte offset of the k-th 16-element slice of a K-major [128][128] tile (two boxes of 64 columns)
 __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
+
+// two fp32 lanes per instruction (sm_100 packed fp32 pipe)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
 
 __device__ __forceinline__ float ex2(float x) {  // 2^x, single MUFU
   float y;
@@ -383,10 +392,12 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
         *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
       }
+      const float2 eg2 = make_float2(eg, eg);
 #pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        r0[k] = __float_as_uint(__uint_as_float(r0[k]) * eg);
-        r1[k] = __float_as_uint(__uint_as_float(r1[k]) * eg);
+      for (int k = 0; k < 32; k += 2) {
+        const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
+        r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
+        r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
       }
       tmem_st32(tl + kColT + (2 * wg) * 32, r0);
       tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
@@ -424,14 +435,14 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         uint4 v[8];
 #pragma unroll
         for (int pc = 0; pc < 8; ++pc) v[pc] = *reinterpret_cast<const uint4 *>(ybox + sw128_offset(i, pc));
-        const float u_i = cur.u;
+        const float2 u2 = make_float2(cur.u, cur.u);
 #pragma unroll
         for (int pc = 0; pc < 8; ++pc) {
           float2 f;
-          f = Fmt<T>::unpack(v[pc].x); v[pc].x = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v[pc].y); v[pc].y = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v[pc].z); v[pc].z = Fmt<T>::pack(f.x * u_i, f.y * u_i);
-          f = Fmt<T>::unpack(v[pc].w); v[pc].w = Fmt<T>::pack(f.x * u_i, f.y * u_i);
+          f = mul2(Fmt<T>::unpack(v[pc].x), u2); v[pc].x = Fmt<T>::pack(f.x, f.y);
+          f = mul2(Fmt<T>::unpack(v[pc].y), u2); v[pc].y = Fmt<T>::pack(f.x, f.y);
+          f = mul2(Fmt<T>::unpack(v[pc].z), u2); v[pc].z = Fmt<T>::pack(f.x, f.y);
+          f = mul2(Fmt<T>::unpack(v[pc].w), u2); v[pc].w = Fmt<T>::pack(f.x, f.y);
         }
 #pragma unroll
         for (int pc = 0; pc < 8; ++pc) *reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc)) = v[pc];
@@ -456,10 +467,13 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           if (bt != q4) {
             const float ai = rev ? ex2(cur.wend[bt] - c_i) : ex2(c_i - cur.wend[bt + 1]);
 #pragma unroll
+            const float2 ai2 = make_float2(ai, ai);
             for (int k = 0; k < 32; k += 4) {
               const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + k]);
-              pk[(k >> 1) + 0] = Fmt<T>::pack(__uint_as_float(r[k + 0]) * (ai * bj.x), __uint_as_float(r[k + 1]) * (ai * bj.y));
-              pk[(k >> 1) + 1] = Fmt<T>::pack(__uint_as_float(r[k + 2]) * (ai * bj.z), __uint_as_float(r[k + 3]) * (ai * bj.w));
+              const float2 p0 = mul2(f2(r[k + 0], r[k + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
+              const float2 p1 = mul2(f2(r[k + 2], r[k + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
+              pk[(k >> 1) + 0] = Fmt<T>::pack(p0.x, p0.y);
+              pk[(k >> 1) + 1] = Fmt<T>::pack(p1.x, p1.y);
             }
           } else {
 #pragma unroll
@@ -514,8 +528,13 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         tmem_ld32(tl + kColW2 + bt * 32, w2);
         tmem_wait_ld();
         float w[32];
+        const float2 s2 = make_float2(s_i, s_i);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) w[k] = fmaf(s_i, __uint_as_float(w2[k]), __uint_as_float(w1[k]));
+        for (int k = 0; k < 32; k += 2) {
+          const float2 t2 = fma2(s2, f2(w2[k], w2[k + 1]), f2(w1[k], w1[k + 1]));
+          w[k] = t2.x;
+          w[k + 1] = t2.y;
+        }
         if (a.xrow != nullptr && i < L) {
           const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
 #pragma unroll
