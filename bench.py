@@ -186,7 +186,7 @@ class LasdStep:
 
 
 class LavdStep(LasdStep):
-    launches_per_step = 6  # o, dq, dk, dv passes + log-decay reverse cumsum (+ state term)
+    launches_per_step = 4  # o, dq, dk, dv chunk passes (plus skipped fallback scans and one reverse cumsum)
 
     def _fb(self, d):
         q, k, v, ldk = (d[x].requires_grad_() for x in ("q", "k", "v", "ldk"))
@@ -492,7 +492,7 @@ def main():
                 "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                 "peak_source": peaks["source"],
                 "kernel": {"C2": "chunk_pass_kernel" if tensor_path == 1 else "scan_kernel",
-                           "C3": "scan_kernel", "C4": "decode_kernel",
+                           "C3": "lavd_pass_kernel", "C4": "decode_kernel",
                            "C5": "chunk_pass_kernel"}[args.workload],
                 "algorithmic_bytes_per_launch": per_launch_bytes,
                 "avg_launch_ms": per_launch_s * 1e3}

@@ -59,6 +59,11 @@ LA_API int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned fla
 LA_API int la_device_status(void *stream, int *status_out);
 LA_API int la_device_status_clear(void *stream);
 
+/* Reads (and synchronises the stream for) the word the last vector-decay call on this GPU left:
+ * non-zero means it fell back from the tensor-core kernels to the scan kernels.  No counterpart in
+ * the reference. */
+LA_API int la_debug_lavd_unsafe(void *stream, int *flag_out);
+
 /* Phase tracing of the chunk kernel (no counterpart in the reference): while buf is non-NULL,
  * every chunk pass writes clock64() stamps of CTA 0, threads 0 and 32, at 15 phase boundaries
  * per chunk into buf (device memory, 2 x 4096 x 16 int64).  NULL switches it off. */
@@ -136,6 +141,15 @@ LA_API int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, cons
  * Vector decay (lavd).  ldk (B,N,H,D) and ldv (B,N,H,E) are fp32, contiguous; either may be NULL
  * (not both).
  * ------------------------------------------------------------------------------------------- */
+
+/* Which kernel family a vector-decay call runs: 1 = tcgen05/TMA chunk kernels (16-bit inputs,
+ * D = E = 128, N >= 128, ldk only), 0 = fp32 scan kernels.  On path 1 a chunk whose decay is too
+ * strong for the tensor-core formulation (more than 2^-64 over half a chunk for bf16, 2^-10 for
+ * fp16) makes the same call
+ * rerun on the scan kernels, decided on the device.  The flag word behind that decision is one per
+ * GPU: vector-decay calls whose kernels overlap on one GPU must be serialised. */
+LA_API int la_lavd_path(int64_t N, int64_t D, int64_t E, int dtype, int has_ldk, int has_ldv,
+                        unsigned flags);
 
 /* Stands in for lavd_parallel_fwd (xopes/ops/lightning_attn/vector_decay/lavd_parallel_triton.py:879-992)
  * and lavd_recurrence_fwd (vector_decay/lavd_recurrence_triton.py:157-218). */

@@ -235,6 +235,60 @@ def test_lavd_seeded(shape, use_ldv, dtype, tol):
     assert_close("dinitial_state", rs0, s0c.grad, tol)
 
 
+def _lavd_unsafe_flag(lib):
+    import ctypes
+    f = ctypes.c_int(-1)
+    assert lib.la_debug_lavd_unsafe(torch.cuda.current_stream().cuda_stream, ctypes.byref(f)) == 0
+    return f.value
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("regime", ["weak", "medium", "strong"])
+@pytest.mark.parametrize("shape,lens", [((2, 384, 2), None), ((1, 300, 3), None), ((1, 128, 1), None),
+                                        ((1, 700, 2), [1, 127, 128, 129, 300, 15])])
+def test_lavd_tensor_path(shape, lens, regime, dtype, lib):
+    """Vector decay (ldk only) with D = E = 128 in 16 bit: the tcgen05 chunk kernels.  "weak" is the
+    benchmark's decay (logsigmoid(x)/16) and must stay on the tensor path; "strong" decays by far
+    more than 2^-64 per half chunk and must fall back to the scan kernels on its own."""
+    import xopes_b200 as xb
+    from xopes_b200 import _lib
+    b, n, h = shape
+    d = e = 128
+    assert lib.la_lavd_path(n, d, e, _lib.dtype_code(torch.empty(0, dtype=dtype)), 1, 0, 0) == 1
+    g = torch.Generator().manual_seed(17)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    x = torch.randn(b, n, h, d, generator=g)
+    ldk = {"weak": torch.nn.functional.logsigmoid(x) / 16,
+           "medium": torch.nn.functional.logsigmoid(x + 1),
+           "strong": torch.nn.functional.logsigmoid(x * 2 - 4)}[regime]
+    qf = cast(torch.randn(b, n, h, d, generator=g))
+    kf = cast((1 - torch.exp(ldk)) * torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    vf = cast(torch.randn(b, n, h, e, generator=g))
+    nb = b if lens is None else len(lens)
+    cu = None if lens is None else torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    s0 = 0.1 * torch.randn(nb, h, d, e, generator=g)
+    dof = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = 0.1 * torch.randn(nb, h, d, e, generator=g)  # upstream state gradient on the scale of the state
+    q, k, v, lk, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ldk), leaf(s0)
+    o, sf = xb.lavd_fn(q, k, v, ldk=lk, initial_state=s0c, cu_seqlens=None if cu is None else cu.to(DEV))
+    flag_fwd = _lavd_unsafe_flag(lib)
+    ro, rsf = orc.lavd_forward(qf, kf, vf, ldk, None, s0, cu)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    flag_bwd = _lavd_unsafe_flag(lib)
+    if regime == "weak":
+        assert flag_fwd == 0 and flag_bwd == 0, "benchmark-range decays must stay on the tensor path"
+    if regime == "strong":
+        assert flag_fwd != 0 and flag_bwd != 0, "out-of-range decays must fall back"
+    rq, rk, rv, rlk, _, rs0 = orc.lavd_backward(qf, kf, vf, ldk, None, dof, s0, dsf, cu)
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    assert_close("dldk", rlk, lk.grad, TOL_DLD_16BIT)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
 # ------------------------------------------------------------------------------------------------
 # varlen
 # ------------------------------------------------------------------------------------------------

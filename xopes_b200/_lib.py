@@ -26,6 +26,7 @@ SIGNATURES = {
     "la_lasd_path": (_i32, [_i64, _i64, _i64, _i32, _u32]),
     "la_device_status": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "la_device_status_clear": (_i32, [_vp]),
+    "la_debug_lavd_unsafe": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "la_debug_chunk_trace": (_i32, [_vp]),
     "la_debug_umma_probe": (_i32, [_i32, _vp, _vp, _vp, _i32, _vp]),
     "la_lasd_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
@@ -36,6 +37,7 @@ SIGNATURES = {
                            _vp]),
     "la_lasd_bwd_noalloc": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp,
                                    _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_lavd_path": (_i32, [_i64, _i64, _i64, _i32, _i32, _i32, _u32]),
     "la_lavd_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
     "la_lavd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64]),

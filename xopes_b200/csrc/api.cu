@@ -18,6 +18,21 @@ int *status_word_ptr() {
   return ptrs[dev];
 }
 
+__device__ int g_lavd_unsafe = 0;
+
+// device word the vector-decay chunk kernels raise when the inputs leave their safe range
+static int *lavd_unsafe_ptr() {
+  static int *ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (ptrs[dev] == nullptr) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_lavd_unsafe) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int *>(p);
+  }
+  return ptrs[dev];
+}
+
 namespace {
 
 bool dtype_ok(int dtype) { return dtype == LA_F32 || dtype == LA_BF16 || dtype == LA_F16; }
@@ -57,8 +72,10 @@ void rows_d(ScanParams &p, const Seq &s, const float *ldk, const float *ldv) {
 
 int scan_forward(const Seq &s, const void *q, const void *k, const void *v, const float *ld,
                  int64_t sb, int64_t sn, int64_t sh, const float *ldk, const float *ldv,
-                 const float *s0, void *o, float *sfin, int dtype, cudaStream_t st) {
+                 const float *s0, void *o, float *sfin, int dtype, cudaStream_t st,
+                 const int *enable = nullptr) {
   ScanParams p = base_params(s, ld, sb, sn, sh);
+  p.enable = enable;
   rows_e(p, s, ldk, ldv);
   p.a = v; p.b = k; p.w = q; p.out = o; p.t0 = s0; p.tfinal = sfin;
   return launch_scan(p, dtype, st);
@@ -108,6 +125,16 @@ int la_device_status_clear(void *stream) {
   int *p = status_word_ptr();
   if (p == nullptr) return LA_ERR_CUDA;
   if (cudaMemsetAsync(p, 0, sizeof(int), static_cast<cudaStream_t>(stream)) != cudaSuccess) return LA_ERR_CUDA;
+  return LA_OK;
+}
+
+int la_debug_lavd_unsafe(void *stream, int *flag_out) {
+  if (flag_out == nullptr) return LA_ERR_NULL_POINTER;
+  int *p = lavd_unsafe_ptr();
+  if (p == nullptr) return LA_ERR_CUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(flag_out, p, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return LA_ERR_CUDA;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return LA_ERR_CUDA;
   return LA_OK;
 }
 
@@ -271,6 +298,14 @@ int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, const float
 // ------------------------------------------------------------------------------------------------
 // vector decay
 // ------------------------------------------------------------------------------------------------
+int la_lavd_path(int64_t N, int64_t D, int64_t E, int dtype, int has_ldk, int has_ldv, unsigned flags) {
+  if (!dtype_ok(dtype)) return LA_ERR_UNSUPPORTED;
+  const bool tensor = !(flags & LA_FLAG_FORCE_RECURRENCE) &&
+                      lavd_chunk_supported(N, D, E, dtype, has_ldk != 0, has_ldv != 0);
+  if (!tensor && (flags & LA_FLAG_REQUIRE_TENSOR)) return LA_ERR_UNSUPPORTED;
+  return tensor ? 1 : 0;
+}
+
 int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, const float *ldv,
                 const float *initial_state, const int64_t *cu_seqlens, void *o,
                 float *final_state, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
@@ -278,10 +313,23 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
   int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc != LA_OK) return rc;
   if (o == nullptr || (ldk == nullptr && ldv == nullptr)) return LA_ERR_NULL_POINTER;
-  if (flags & LA_FLAG_REQUIRE_TENSOR) return LA_ERR_UNSUPPORTED;
+  const int path = la_lavd_path(N, D, E, dtype, ldk != nullptr, ldv != nullptr, flags);
+  if (path < 0) return path;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
-  return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype,
-                      static_cast<cudaStream_t>(stream));
+  const int *enable = nullptr;
+  if (path == 1) {
+    int *unsafe = lavd_unsafe_ptr();
+    if (unsafe == nullptr) return LA_ERR_CUDA;
+    if (cudaMemsetAsync(unsafe, 0, sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
+    LavdPass c;
+    c.x = q; c.y = k; c.z = v; c.ldk = ldk; c.out = o; c.t0 = initial_state; c.tfinal = final_state;
+    c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
+    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    enable = unsafe;  // the scan below runs only if a chunk left the tensor path's safe range
+  }
+  return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype, st,
+                      enable);
 }
 
 int64_t la_lavd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
@@ -302,7 +350,6 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return LA_ERR_NULL_POINTER;
   if (ldk == nullptr && ldv == nullptr) return LA_ERR_NULL_POINTER;
   if ((ldk != nullptr && dldk == nullptr) || (ldv != nullptr && dldv == nullptr)) return LA_ERR_NULL_POINTER;
-  if (flags & LA_FLAG_REQUIRE_TENSOR) return LA_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
   float *ws_state = nullptr;
@@ -311,11 +358,35 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
       return LA_ERR_WORKSPACE;
     ws_state = static_cast<float *>(workspace);
   }
+  const int path = la_lavd_path(N, D, E, dtype, ldk != nullptr, ldv != nullptr, flags);
+  if (path < 0) return path;
+  const int *enable = nullptr;
+  if (path == 1) {
+    int *unsafe = lavd_unsafe_ptr();
+    if (unsafe == nullptr) return LA_ERR_CUDA;
+    if (cudaMemsetAsync(unsafe, 0, sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
+    LavdPass c;
+    c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
+    // dq: (do, v, k), state S^T, forward; dldk = q * dq
+    c.x = d_o; c.y = v; c.z = k; c.out = dq; c.tmode = 1; c.state_transposed = 1; c.reverse = 0;
+    c.t0 = initial_state; c.tfinal = ws_state; c.xrow = q; c.dld = dldk; c.dld_sub = 0;
+    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    // dk: (v, do, q), state dS^T, reverse; dldk -= k * dk
+    c.x = v; c.y = d_o; c.z = q; c.out = dk; c.reverse = 1;
+    c.t0 = dfinal_state; c.tfinal = nullptr; c.xrow = k; c.dld_sub = 1;
+    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    // dv: (k, q, do), state dS, reverse; its end state is d initial_state
+    c.x = k; c.y = q; c.z = d_o; c.out = dv; c.tmode = 0; c.state_transposed = 0; c.reverse = 1;
+    c.t0 = dfinal_state; c.tfinal = dinitial_state; c.xrow = nullptr; c.dld = nullptr;
+    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    enable = unsafe;
+  }
   ScanParams p;
   if (ldv != nullptr) {
     // recompute o only to form o*do for dldv (the reference's optional dldv_o pass,
     // vector_decay/lavd_parallel_triton.py:1104-1127)
     p = base_params(s, nullptr, 0, 0, 0);
+  p.enable = enable;
     rows_e(p, s, ldk, ldv);
     p.a = v; p.b = k; p.w = q; p.out = nullptr; p.t0 = initial_state;
     p.x = d_o; p.xout = dldv; p.xmode = 2;
@@ -323,12 +394,14 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   }
   // dq
   p = base_params(s, nullptr, 0, 0, 0);
+  p.enable = enable;
   rows_d(p, s, ldk, ldv);
   p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state; p.tfinal = ws_state;
   if (ldk != nullptr) { p.x = q; p.xout = dldk; p.xmode = 2; }
   if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
   // dk
   p = base_params(s, nullptr, 0, 0, 0);
+  p.enable = enable;
   rows_d(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
@@ -336,6 +409,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
   // dv
   p = base_params(s, nullptr, 0, 0, 0);
+  p.enable = enable;
   rows_e(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;

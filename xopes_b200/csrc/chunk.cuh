@@ -31,6 +31,28 @@ struct ChunkPass {
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype);
 int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream);
+// One directional vector-decay (ldk) pass on tcgen05 (lavd_chunk_sm100.cu).  tmode = 0: the decay
+// acts on the contraction dimension of X Y^T (o and dv passes); tmode = 1: on the output dimension
+// (dq and dk passes, state transposed), with the optional log-decay-gradient accumulation
+// dld (+)= xrow * W.  `unsafe` is raised when a chunk's decay exceeds the range of the mid-chunk
+// reference; the caller then reruns on the scan kernels, predicated on that word.
+struct LavdPass {
+  const void *x = nullptr, *y = nullptr, *z = nullptr;
+  const float *ldk = nullptr;
+  void *out = nullptr;
+  const void *xrow = nullptr;
+  float *dld = nullptr;
+  int dld_sub = 0;
+  const float *t0 = nullptr;
+  float *tfinal = nullptr;
+  int state_transposed = 0, reverse = 0, tmode = 0;
+  const int64_t *cu = nullptr;
+  int B = 0, N = 0, H = 0, M = 0;
+  int *unsafe = nullptr;
+};
+bool lavd_chunk_supported(int64_t N, int64_t D, int64_t E, int dtype, bool has_ldk, bool has_ldv);
+int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream);
+
 // o[0,t,h,:] += exp(cum[t,h]) * q[0,t,h,:] S_in[h] for t < T1 (sequence-parallel correction, seqpar.cu)
 int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,
                           int D, int E, int dtype, cudaStream_t st);

@@ -1,0 +1,602 @@
+// Chunk-parallel vector-decay (key-side decay ldk) pass on 5th-generation tensor cores (sm_100a).
+//
+// Per (sequence, head) and 128-token chunk, with ck[i][d] the in-chunk inclusive cumulative log
+// decay of feature d, m[d] = ck at the middle row, g[d] = ck at the last row:
+//
+//   o  pass (X,Y,Z = q,k,v):   W = tril(Xs Ys^T) Z + Xs (diag(e^m) T) ;  T <- diag(e^g) T + (Ys e^{g-m})^T Z
+//        with Xs = X (.) e^{ck-m},  Ys = Y (.) e^{m-ck}   ("N" mode: the decay sits on the contraction
+//        dimension of X Y^T; the reverse-direction twin with (k,q,do) gives dv)
+//   dq pass (X,Y,Z = do,v,k):  W = [tril(X Y^T) Zs + X (T diag(e^m))] (.) e^{ck-m} ; T <- T diag(e^g) + Y^T (Zs e^{g-m})
+//        with Zs = Z (.) e^{m-ck}, T = S^T                ("T" mode: the decay sits on the output
+//        dimension; the reverse twin with (v,do,q) gives dk)
+//
+// Referencing the exponentials to the middle of the chunk keeps every factor within
+// e^{+-(half-chunk decay)}; masked-out products may overflow to inf and are removed by a select.
+// A chunk whose half-chunk decay exceeds 2^64 (bf16; 2^10 for fp16) raises the "unsafe" flag; the caller then reruns
+// the call on the fp32 scan kernels (predicated on that flag, no host round trip).
+//
+// Structure as in chunk_sm100.cu (state resident in tensor memory, TMA producer / MMA issuer /
+// TMA store warps, bounded mbarrier waits, no multicast), but single-stage: the chunk's operands
+// are three 16-bit tiles plus the 64 KB fp32 decay tile, and two more tiles hold the 16-bit state
+// copy and the rescaled update operand, which fills shared memory.
+#include <cuda.h>
+
+#include <cstddef>
+
+#include "chunk.cuh"
+#include "sm100_ptx.cuh"
+#include "tile_common.cuh"
+
+namespace la {
+namespace {
+
+using namespace ptx;
+using namespace tile;
+
+constexpr int kChunk = 128;
+constexpr int kTileBytes = 32768, kBoxBytes = 16384;
+constexpr int kOffX = 0, kOffY = kTileBytes, kOffZ = 2 * kTileBytes, kOffCk = 3 * kTileBytes;
+constexpr int kCkBytes = 65536;
+constexpr int kOffTb = kOffCk + kCkBytes, kOffU = kOffTb + kTileBytes, kOffSmall = kOffU + kTileBytes;
+constexpr int kSmallBytes = 2048;
+constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;
+constexpr int kLoadBytes = 3 * kTileBytes + kCkBytes;
+constexpr int kComputeThreads = 256;
+constexpr int kProducerWarp = 8, kMmaWarp = 9, kStoreWarp = 10;
+constexpr int kThreads = kComputeThreads + 96;
+constexpr float kLog2e = 1.4426950408889634f;
+// Largest half-chunk decay, in bits, the mid-chunk reference handles: operands are scaled by up to
+// 2^(+-bits) before they are rounded to 16 bit, so the element type's exponent range decides.
+template <typename T> struct SafeBits;
+template <> struct SafeBits<__nv_bfloat16> { static constexpr float value = 64.f; };
+template <> struct SafeBits<__half> { static constexpr float value = 10.f; };
+
+constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
+constexpr int kStFull = 301, kStEmpty = 302, kStP = 303, kStW = 304, kStD = 305, kStF = 306, kStH = 307, kStR = 308;
+
+struct Small {
+  unsigned long long full, empty, bar_p, bar_w, bar_r, bar_d, bar_f, bar_h;
+  uint32_t tmem_base;
+  int abort_flag;
+  int issued;
+  int pad;
+  alignas(16) float uvec[kChunk];  // scale of the state-update operand per feature
+  alignas(16) float cvec[kChunk];  // scale of the 16-bit state copy per feature
+  alignas(16) float gfac[kChunk];  // e^g per feature: decay of the state over the chunk
+};
+static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
+
+struct LavdArgs {
+  void *out;
+  const void *xrow;   // T mode: tensor multiplied into the output for the log-decay gradient
+  float *dld;         // T mode: (B,N,H,128) fp32 accumulator, stored (dld_sub = 0) or decremented
+  int dld_sub;
+  const float *t0;
+  float *tfinal;
+  int state_transposed, reverse;
+  const long long *cu;
+  int B, N, H, M;
+  int *status;
+  int *unsafe;
+};
+
+// byte offset of the float4 holding features [d, d+4) of row i in the 128B-swizzled fp32 decay tile
+__device__ __forceinline__ uint32_t ck_off(int i, int d) {
+  return (uint32_t)(d >> 5) * kBoxBytes + (uint32_t)i * 128u + (uint32_t)((((d & 31) >> 2) ^ (i & 7)) << 4);
+}
+__device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
+
+// One 16-byte piece (8 features starting at d0) of a 16-bit tile row times 2^(sgn*ckc) (and times
+// uvec for the update operand).
+template <typename T>
+__device__ __forceinline__ void scale_piece(uint4 v, const uint8_t *ck, int i, int d0, float sgn, bool zero_u,
+                                            const float *uvec, uint4 &scaled, uint4 &upd) {
+  const float4 c0 = *reinterpret_cast<const float4 *>(ck + ck_off(i, d0));
+  const float4 c1 = *reinterpret_cast<const float4 *>(ck + ck_off(i, d0 + 4));
+  const float4 u0 = *reinterpret_cast<const float4 *>(uvec + d0);
+  const float4 u1 = *reinterpret_cast<const float4 *>(uvec + d0 + 4);
+  float2 f, p, q;
+  f = mul2(Fmt<T>::unpack(v.x), make_float2(ex2(sgn * c0.x), ex2(sgn * c0.y)));
+  scaled.x = Fmt<T>::pack(f.x, f.y);
+  p = mul2(f, make_float2(u0.x, u0.y));
+  f = mul2(Fmt<T>::unpack(v.y), make_float2(ex2(sgn * c0.z), ex2(sgn * c0.w)));
+  scaled.y = Fmt<T>::pack(f.x, f.y);
+  q = mul2(f, make_float2(u0.z, u0.w));
+  upd.x = zero_u ? 0u : Fmt<T>::pack(p.x, p.y);
+  upd.y = zero_u ? 0u : Fmt<T>::pack(q.x, q.y);
+  f = mul2(Fmt<T>::unpack(v.z), make_float2(ex2(sgn * c1.x), ex2(sgn * c1.y)));
+  scaled.z = Fmt<T>::pack(f.x, f.y);
+  p = mul2(f, make_float2(u1.x, u1.y));
+  f = mul2(Fmt<T>::unpack(v.w), make_float2(ex2(sgn * c1.z), ex2(sgn * c1.w)));
+  scaled.w = Fmt<T>::pack(f.x, f.y);
+  q = mul2(f, make_float2(u1.z, u1.w));
+  upd.z = zero_u ? 0u : Fmt<T>::pack(p.x, p.y);
+  upd.w = zero_u ? 0u : Fmt<T>::pack(q.x, q.y);
+}
+
+template <typename T, bool TMODE>
+__global__ void __launch_bounds__(kThreads, 1)
+lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                 const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_ld,
+                 const __grid_constant__ CUtensorMap map_o, const LavdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gbase = smem_raw + (base - raw);
+  Small *sm = reinterpret_cast<Small *>(gbase + kOffSmall);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int seq = blockIdx.x / a.H, h = blockIdx.x - seq * a.H;
+  long long t_begin = 0, t_end = a.N;
+  int bidx = seq;
+  if (a.cu != nullptr) {
+    t_begin = a.cu[seq];
+    t_end = a.cu[seq + 1];
+    bidx = 0;
+  }
+  const int len = (int)(t_end - t_begin);
+  const int nc = (len + kChunk - 1) / kChunk;
+  const bool rev = a.reverse != 0;
+
+  const uint32_t bar_full = smem_u32(&sm->full), bar_empty = smem_u32(&sm->empty);
+  const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w), bar_r = smem_u32(&sm->bar_r);
+  const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
+  volatile int *abort_flag = &sm->abort_flag;
+
+  if (tid == 0) {
+    mbar_init(bar_full, 1);
+    mbar_init(bar_empty, 1);
+    mbar_init(bar_p, 1);
+    mbar_init(bar_w, 1);
+    mbar_init(bar_r, kComputeThreads);
+    mbar_init(bar_d, kComputeThreads);
+    mbar_init(bar_f, kComputeThreads);
+    mbar_init(bar_h, kComputeThreads);
+    sm->abort_flag = 0;
+    sm->issued = 0;
+    fence_barrier_init();
+  }
+  if (warp == kProducerWarp) {
+    tmem_alloc(smem_u32(&sm->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const uint32_t xs = base + kOffX, ys = base + kOffY, zs = base + kOffZ, cks = base + kOffCk;
+  const uint32_t tbs = base + kOffTb, us = base + kOffU;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ TMA loads (single stage)
+    if (lane == 0) {
+      int it = 0;
+      for (; it < nc; ++it) {
+        const int n = rev ? (nc - 1 - it) : it;
+        const uint32_t par = (uint32_t)it & 1u;
+        mbar_wait(bar_empty, par ^ 1u, abort_flag, a.status, kStEmpty);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(bar_full, kLoadBytes);
+        const int tok0 = (int)t_begin + n * kChunk;
+        tma_load_4d(xs, &map_x, bar_full, 0, h, tok0, bidx);
+        tma_load_4d(xs + kBoxBytes, &map_x, bar_full, 64, h, tok0, bidx);
+        tma_load_4d(ys, &map_y, bar_full, 0, h, tok0, bidx);
+        tma_load_4d(ys + kBoxBytes, &map_y, bar_full, 64, h, tok0, bidx);
+        tma_load_4d(zs, &map_z, bar_full, 0, h, tok0, bidx);
+        tma_load_4d(zs + kBoxBytes, &map_z, bar_full, 64, h, tok0, bidx);
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) tma_load_4d(cks + gq * kBoxBytes, &map_ld, bar_full, 32 * gq, h, tok0, bidx);
+      }
+      sm->issued = it;
+    }
+    __syncwarp();
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------------ tensor-core issue
+    if (lane == 0) {
+      const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
+      const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
+      const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
+      const uint64_t d_xk = desc_kmajor(xs), d_yk = desc_kmajor(ys), d_tb = desc_mnmajor(tbs, kBoxBytes);
+      const uint64_t d_zmn = desc_mnmajor(zs, kBoxBytes), d_ymn = desc_mnmajor(ys, kBoxBytes);
+      const uint64_t d_umn = desc_mnmajor(us, kBoxBytes);
+      for (int it = 0; it < nc; ++it) {
+        const uint32_t par = (uint32_t)it & 1u;
+        mbar_wait(bar_full, par, abort_flag, a.status, kStFull);
+        // N mode multiplies the rescaled X and Y; T mode the tiles as loaded
+        if (!TMODE) mbar_wait(bar_r, par, abort_flag, a.status, kStR);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+          mma_ss(tmem + kColP, d_xk + ko, d_yk + ko, idesc_kk, ks > 0);
+        }
+        mma_commit(bar_p);
+        mbar_wait(bar_d, par, abort_flag, a.status, kStD);
+        if (TMODE) mbar_wait(bar_r, par, abort_flag, a.status, kStR);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // W2 = X * (scaled 16-bit state copy)
+          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+          mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // state update: N mode U^T Z, T mode Y^T U
+          if (!TMODE)
+            mma_ss(tmem + kColT, d_umn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+          else
+            mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_umn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+        }
+        mbar_wait(bar_f, par, abort_flag, a.status, kStF);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)  // W1 = P~ Z (T mode: Z is the rescaled tile)
+          mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
+                 idesc_kmn, ks > 0);
+        mma_commit(bar_w);
+        mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kStoreWarp) {
+    // ------------------------------------------------------------------ TMA stores
+    if (lane == 0) {
+      for (int it = 0; it < nc; ++it) {
+        const int n = rev ? (nc - 1 - it) : it;
+        const uint32_t par = (uint32_t)it & 1u;
+        const int L = min(kChunk, len - n * kChunk);
+        mbar_wait(bar_h, par, abort_flag, a.status, kStH);
+        if (L == kChunk) {
+          const int tok0 = (int)t_begin + n * kChunk;
+          tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
+          tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        mbar_arrive(bar_empty);
+      }
+      tma_store_wait_all();
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const int wg = warp >> 2, q4 = warp & 3;
+    const int i = q4 * 32 + lane;  // tile row / tensor-memory lane
+    const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
+    const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
+    uint8_t *ck = gbase + kOffCk;
+    float *segtot = reinterpret_cast<float *>(gbase + kOffU);  // [8][128], before U is written
+
+    for (int b2 = 0; b2 < 2; ++b2) {  // starting state -> tensor memory
+      const int bt = 2 * wg + b2;
+      uint32_t r[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const int c = bt * 32 + k;
+        float v = 0.f;
+        if (a.t0 != nullptr) v = a.t0[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))];
+        r[k] = __float_as_uint(v);
+      }
+      tmem_st32(tl + kColT + bt * 32, r);
+    }
+    tmem_wait_st();
+
+    for (int it = 0; it < nc; ++it) {
+      const int n = rev ? (nc - 1 - it) : it;
+      const uint32_t par = (uint32_t)it & 1u;
+      const int L = min(kChunk, len - n * kChunk);
+      const long long tok = t_begin + (long long)n * kChunk + i;
+
+      mbar_wait(bar_full, par, abort_flag, a.status, kStFull);
+
+      // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
+      // Thread (d = tid % 128, half = tid / 128) scans rows [64 half, 64 half + 64) as four
+      // interleaved 16-row segments.
+      {
+        const int d = tid & 127, half = tid >> 7;
+        float run[4];
+#pragma unroll
+        for (int sg = 0; sg < 4; ++sg) run[sg] = 0.f;
+#pragma unroll 4
+        for (int r = 0; r < 16; ++r) {
+#pragma unroll
+          for (int sg = 0; sg < 4; ++sg) {
+            const int row = half * 64 + sg * 16 + r;
+            float *p = reinterpret_cast<float *>(ck + ck_off(row, d)) + (d & 3);
+            const float v = (row < L) ? *p * kLog2e : 0.f;
+            run[sg] += v;
+            *p = run[sg];
+          }
+        }
+#pragma unroll
+        for (int sg = 0; sg < 4; ++sg) segtot[(half * 4 + sg) * 128 + d] = run[sg];
+        named_bar_sync(1, kComputeThreads);
+        float pre[8];
+        float acc = 0.f;
+#pragma unroll
+        for (int sgl = 0; sgl < 8; ++sgl) {
+          pre[sgl] = acc;
+          acc += segtot[sgl * 128 + d];
+        }
+        const float m = pre[4], g = acc;  // ck at row 63 and at row 127
+#pragma unroll 4
+        for (int r = 0; r < 16; ++r) {
+#pragma unroll
+          for (int sg = 0; sg < 4; ++sg) {
+            const int row = half * 64 + sg * 16 + r;
+            float *p = reinterpret_cast<float *>(ck + ck_off(row, d)) + (d & 3);
+            *p = *p + (pre[half * 4 + sg] - m);
+          }
+        }
+        if (half == 0) {
+          sm->uvec[d] = rev ? ex2(m) : ex2(g - m);
+          sm->cvec[d] = rev ? ex2(g - m) : ex2(m);
+          sm->gfac[d] = ex2(g);
+          if (-m > SafeBits<T>::value || -(g - m) > SafeBits<T>::value) atomicExch(a.unsafe, 1);
+        }
+        named_bar_sync(1, kComputeThreads);
+      }
+
+      // ---- R: rescale operands in place, build the state-update operand U
+      if (!TMODE) {
+        const float sx = rev ? -1.f : 1.f;
+#pragma unroll 2
+        for (int pc = 0; pc < 8; ++pc) {  // X
+          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffX + wg * kBoxBytes + sw128_offset(i, pc));
+          uint4 sc, up;
+          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, sx, true, sm->uvec, sc, up);
+          *p = sc;
+        }
+#pragma unroll 2
+        for (int pc = 0; pc < 8; ++pc) {  // Y and U
+          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffY + wg * kBoxBytes + sw128_offset(i, pc));
+          uint4 sc, up;
+          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, -sx, i >= L, sm->uvec, sc, up);
+          *p = sc;
+          *reinterpret_cast<uint4 *>(gbase + kOffU + wg * kBoxBytes + sw128_offset(i, pc)) = up;
+        }
+      } else {
+        const float sz = rev ? 1.f : -1.f;
+#pragma unroll 2
+        for (int pc = 0; pc < 8; ++pc) {  // Z and U
+          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffZ + wg * kBoxBytes + sw128_offset(i, pc));
+          uint4 sc, up;
+          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, sz, i >= L, sm->uvec, sc, up);
+          *p = sc;
+          *reinterpret_cast<uint4 *>(gbase + kOffU + wg * kBoxBytes + sw128_offset(i, pc)) = up;
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(bar_r);
+
+      // ---- D: scaled 16-bit state copy (B operand of X T), decay of the resident state
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
+        tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
+        tmem_wait_ld();
+        uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
+        const float cv_row = sm->cvec[i], gf_row = sm->gfac[i];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          uint32_t(&r)[32] = hf ? r1 : r0;
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {
+            float2 c01, c23, c45, c67, g01, g23, g45, g67;
+            if (TMODE) {
+              const int d0 = wg * 64 + hf * 32 + pc * 8;
+              const float4 ca = *reinterpret_cast<const float4 *>(&sm->cvec[d0]);
+              const float4 cb = *reinterpret_cast<const float4 *>(&sm->cvec[d0 + 4]);
+              const float4 ga = *reinterpret_cast<const float4 *>(&sm->gfac[d0]);
+              const float4 gb = *reinterpret_cast<const float4 *>(&sm->gfac[d0 + 4]);
+              c01 = make_float2(ca.x, ca.y); c23 = make_float2(ca.z, ca.w);
+              c45 = make_float2(cb.x, cb.y); c67 = make_float2(cb.z, cb.w);
+              g01 = make_float2(ga.x, ga.y); g23 = make_float2(ga.z, ga.w);
+              g45 = make_float2(gb.x, gb.y); g67 = make_float2(gb.z, gb.w);
+            } else {
+              c01 = c23 = c45 = c67 = make_float2(cv_row, cv_row);
+              g01 = g23 = g45 = g67 = make_float2(gf_row, gf_row);
+            }
+            const float2 t01 = f2(r[pc * 8 + 0], r[pc * 8 + 1]), t23 = f2(r[pc * 8 + 2], r[pc * 8 + 3]);
+            const float2 t45 = f2(r[pc * 8 + 4], r[pc * 8 + 5]), t67 = f2(r[pc * 8 + 6], r[pc * 8 + 7]);
+            float2 s;
+            uint4 v;
+            s = mul2(t01, c01); v.x = Fmt<T>::pack(s.x, s.y);
+            s = mul2(t23, c23); v.y = Fmt<T>::pack(s.x, s.y);
+            s = mul2(t45, c45); v.z = Fmt<T>::pack(s.x, s.y);
+            s = mul2(t67, c67); v.w = Fmt<T>::pack(s.x, s.y);
+            *reinterpret_cast<uint4 *>(box + sw128_offset(i, hf * 4 + pc)) = v;
+            s = mul2(t01, g01); r[pc * 8 + 0] = __float_as_uint(s.x); r[pc * 8 + 1] = __float_as_uint(s.y);
+            s = mul2(t23, g23); r[pc * 8 + 2] = __float_as_uint(s.x); r[pc * 8 + 3] = __float_as_uint(s.y);
+            s = mul2(t45, g45); r[pc * 8 + 4] = __float_as_uint(s.x); r[pc * 8 + 5] = __float_as_uint(s.y);
+            s = mul2(t67, g67); r[pc * 8 + 6] = __float_as_uint(s.x); r[pc * 8 + 7] = __float_as_uint(s.y);
+          }
+        }
+        tmem_st32(tl + kColT + (2 * wg) * 32, r0);
+        tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
+        tmem_wait_st();
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(bar_d);
+      }
+
+      // ---- F: causal (or reverse-causal) 16-bit P~ in the first 16 columns of each 32-column batch
+      mbar_wait(bar_p, par, abort_flag, a.status, kStP);
+      tc_fence_after();
+#pragma unroll 1
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = wg + 2 * b2;
+        uint32_t pk[16];
+        const bool dead = rev ? (bt < q4) : (bt > q4);
+        if (dead) {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) pk[k] = 0u;
+        } else {
+          uint32_t r[32];
+          tmem_ld32(tl + kColP + bt * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const int j = bt * 32 + k;
+            bool k0, k1;
+            if (!rev) { k0 = j <= i; k1 = j + 1 <= i; }
+            else { k0 = (j >= i) && (j < L); k1 = (j + 1 >= i) && (j + 1 < L); }
+            // select, not multiply: masked-out entries may be inf or NaN
+            pk[k >> 1] = Fmt<T>::pack(k0 ? __uint_as_float(r[k]) : 0.f, k1 ? __uint_as_float(r[k + 1]) : 0.f);
+          }
+        }
+        tmem_st16(tl + kColP + bt * 32, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_f);
+
+      // ---- H: epilogue
+      mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+      tc_fence_after();
+      const bool full_chunk = (L == kChunk);
+      const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
+      const float so = rev ? -1.f : 1.f;
+#pragma unroll 1
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = 2 * wg + b2;
+        uint32_t w1[32], w2[32];
+        tmem_ld32(tl + kColW1 + bt * 32, w1);
+        tmem_ld32(tl + kColW2 + bt * 32, w2);
+        tmem_wait_ld();
+        float w[32], scl[32];
+#pragma unroll
+        for (int k = 0; k < 32; k += 4) {
+          float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (TMODE) {
+            const float4 c = *reinterpret_cast<const float4 *>(ck + ck_off(i, bt * 32 + k));
+            sc = make_float4(ex2(so * c.x), ex2(so * c.y), ex2(so * c.z), ex2(so * c.w));
+          }
+          w[k + 0] = __uint_as_float(w1[k + 0]) + __uint_as_float(w2[k + 0]);
+          w[k + 1] = __uint_as_float(w1[k + 1]) + __uint_as_float(w2[k + 1]);
+          w[k + 2] = __uint_as_float(w1[k + 2]) + __uint_as_float(w2[k + 2]);
+          w[k + 3] = __uint_as_float(w1[k + 3]) + __uint_as_float(w2[k + 3]);
+          scl[k + 0] = sc.x; scl[k + 1] = sc.y; scl[k + 2] = sc.z; scl[k + 3] = sc.w;
+        }
+        if (TMODE && a.dld != nullptr && i < L) {
+          // Log-decay gradient term x * W.  W = w * scl, but the product is formed as
+          // round16(x * scl) * w: round16(x * scl) is exactly the rescaled operand the twin pass
+          // feeds to the tensor cores, so the intra-chunk parts of q*dq and k*dk cancel term by term
+          // as they do in exact arithmetic.
+          const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
+          float4 *dp = reinterpret_cast<float4 *>(a.dld + row_off + bt * 32);
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) {
+            const uint4 xv = xp[pc];
+            float xs[8];
+            float2 t;
+            t = Fmt<T>::unpack(xv.x); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 0], t.y * scl[pc * 8 + 1])); xs[0] = t.x; xs[1] = t.y;
+            t = Fmt<T>::unpack(xv.y); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 2], t.y * scl[pc * 8 + 3])); xs[2] = t.x; xs[3] = t.y;
+            t = Fmt<T>::unpack(xv.z); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 4], t.y * scl[pc * 8 + 5])); xs[4] = t.x; xs[5] = t.y;
+            t = Fmt<T>::unpack(xv.w); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 6], t.y * scl[pc * 8 + 7])); xs[6] = t.x; xs[7] = t.y;
+            float4 lo = make_float4(xs[0] * w[pc * 8 + 0], xs[1] * w[pc * 8 + 1], xs[2] * w[pc * 8 + 2], xs[3] * w[pc * 8 + 3]);
+            float4 hi = make_float4(xs[4] * w[pc * 8 + 4], xs[5] * w[pc * 8 + 5], xs[6] * w[pc * 8 + 6], xs[7] * w[pc * 8 + 7]);
+            if (a.dld_sub) {
+              const float4 ol = dp[pc * 2], oh = dp[pc * 2 + 1];
+              lo = make_float4(ol.x - lo.x, ol.y - lo.y, ol.z - lo.z, ol.w - lo.w);
+              hi = make_float4(oh.x - hi.x, oh.y - hi.y, oh.z - hi.z, oh.w - hi.w);
+            }
+            dp[pc * 2] = lo;
+            dp[pc * 2 + 1] = hi;
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) w[k] *= scl[k];
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 v;
+          v.x = Fmt<T>::pack(w[pc * 8 + 0], w[pc * 8 + 1]);
+          v.y = Fmt<T>::pack(w[pc * 8 + 2], w[pc * 8 + 3]);
+          v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
+          v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
+          if (full_chunk) {
+            *reinterpret_cast<uint4 *>(gbase + kOffX + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
+          } else if (i < L) {
+            reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + row_off + bt * 32)[pc] = v;
+          }
+        }
+      }
+      if (full_chunk) fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar_h);
+    }
+
+    if (a.tfinal != nullptr) {  // end state -> global
+      tc_fence_after();
+      for (int b2 = 0; b2 < 2; ++b2) {
+        const int bt = 2 * wg + b2;
+        uint32_t r[32];
+        tmem_ld32(tl + kColT + bt * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int c = bt * 32 + k;
+          a.tfinal[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))] = __uint_as_float(r[k]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarp) {
+    if (lane == 0 && sm->abort_flag != 0) {
+      int dummy = 0;
+      if (sm->issued > 0)
+        mbar_wait(bar_full, (uint32_t)(sm->issued - 1) & 1u, &dummy, nullptr, 0, 1u << 20);
+    }
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <typename T, bool TMODE>
+int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
+  alignas(64) CUtensorMap mx, my, mz, ml, mo;
+  int rc;
+  if ((rc = make_map(&mx, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&mz, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&ml, p.ldk, LA_F32, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&mo, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if (p.dld != nullptr && ((reinterpret_cast<uintptr_t>(p.xrow) | reinterpret_cast<uintptr_t>(p.dld)) & 15u))
+    return LA_ERR_MISALIGNED;
+  LavdArgs a;
+  a.out = p.out; a.xrow = p.xrow; a.dld = p.xrow ? p.dld : nullptr; a.dld_sub = p.dld_sub;
+  a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
+  a.cu = reinterpret_cast<const long long *>(p.cu);
+  a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
+  a.status = status_word_ptr();
+  a.unsafe = p.unsafe;
+  if (a.status == nullptr || a.unsafe == nullptr) return LA_ERR_CUDA;
+  auto kern = lavd_pass_kernel<T, TMODE>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return LA_ERR_CUDA;
+  const int nb = p.cu ? p.M : p.B;
+  kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, ml, mo, a);
+  return launch_status();
+}
+
+}  // namespace
+
+bool lavd_chunk_supported(int64_t N, int64_t D, int64_t E, int dtype, bool has_ldk, bool has_ldv) {
+  return has_ldk && !has_ldv && (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
+}
+
+int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream) {
+  if (p.x == nullptr || p.y == nullptr || p.z == nullptr || p.out == nullptr || p.ldk == nullptr)
+    return LA_ERR_NULL_POINTER;
+  const int nb = p.cu ? p.M : p.B;
+  if (nb <= 0 || p.H <= 0 || p.N <= 0) return LA_ERR_BAD_SHAPE;
+  if (dtype == LA_BF16)
+    return p.tmode ? launch_t<__nv_bfloat16, true>(p, dtype, stream) : launch_t<__nv_bfloat16, false>(p, dtype, stream);
+  if (dtype == LA_F16)
+    return p.tmode ? launch_t<__half, true>(p, dtype, stream) : launch_t<__half, false>(p, dtype, stream);
+  return LA_ERR_UNSUPPORTED;
+}
+
+}  // namespace la

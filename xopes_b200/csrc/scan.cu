@@ -25,6 +25,7 @@ __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast
 template <typename T, int CC, int G>
 __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
   constexpr int CP = CC * G;  // padded column count
+  if (p.enable != nullptr && *p.enable == 0) return;
   const int tid = threadIdx.x;
   const int nthreads = blockDim.x;
   const int RT = nthreads / G;

@@ -33,6 +33,7 @@ struct ScanParams {
   const int64_t *cu = nullptr;                           // cu_seqlens (device) or null
   int B = 0, N = 0, H = 0, R = 0, C = 0, M = 0;
   int reverse = 0;
+  const int *enable = nullptr;  // optional device word: the kernel does nothing while it is 0
 };
 
 // Number of row tiles launch_scan will use for these sizes (size of xout's leading dimension in

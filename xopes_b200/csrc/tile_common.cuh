@@ -1,0 +1,85 @@
+// Pieces shared by the tcgen05 chunk kernels: 16-bit pack/unpack, packed fp32 helpers, tensor-map
+// construction.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace la {
+namespace tile {
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__nv_bfloat16> {
+  static constexpr uint32_t kAB = 1;  // tcgen05 kind::f16 operand format code
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
+  }
+};
+template <> struct Fmt<__half> {
+  static constexpr uint32_t kAB = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2 *>(&u));
+  }
+};
+
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) {
+  return make_float2(__uint_as_float(lo), __uint_as_float(hi));
+}
+__device__ __forceinline__ float ex2(float x) {  // 2^x, one MUFU op; 2^(-inf) = 0, 2^(+big) = +inf
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// (B, N, H, 128) tensor of 16-bit (dtype LA_BF16 / LA_F16) or fp32 (LA_F32) elements.  One box =
+// 128 tokens x 128 bytes of one head (64 16-bit or 32 fp32 features), 128-byte swizzle.
+inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return LA_ERR_CUDA;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
+  const cuuint64_t esz = dtype == LA_F32 ? 4 : 2;
+  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {128 * esz, (cuuint64_t)H * 128 * esz, (cuuint64_t)N * H * 128 * esz};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / esz), 1, 128, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == LA_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == LA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
+}
+
+}  // namespace tile
+}  // namespace la
