@@ -118,7 +118,8 @@ template <typename T, bool TMODE>
 __global__ void __launch_bounds__(kThreads, 1)
 lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_ld,
-                 const __grid_constant__ CUtensorMap map_o, const LavdArgs a) {
+                 const __grid_constant__ CUtensorMap map_o, const __grid_constant__ CUtensorMap map_dld,
+                 const LavdArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -249,6 +250,15 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           const int tok0 = (int)t_begin + n * kChunk;
           tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
           tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
+          if (TMODE && a.dld != nullptr) {
+            // the decay tile now holds this chunk's log-decay-gradient terms: store (dq pass) or
+            // add the negated terms (dk pass) as four fp32 boxes
+#pragma unroll
+            for (int gq = 0; gq < 4; ++gq) {
+              if (a.dld_sub) tma_reduce_add_4d(&map_dld, cks + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              else tma_store_4d(&map_dld, cks + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+            }
+          }
           tma_store_commit();
           tma_store_wait_read();
         }
@@ -495,6 +505,15 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             t = Fmt<T>::unpack(xv.w); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 6], t.y * scl[pc * 8 + 7])); xs[6] = t.x; xs[7] = t.y;
             float4 lo = make_float4(xs[0] * w[pc * 8 + 0], xs[1] * w[pc * 8 + 1], xs[2] * w[pc * 8 + 2], xs[3] * w[pc * 8 + 3]);
             float4 hi = make_float4(xs[4] * w[pc * 8 + 4], xs[5] * w[pc * 8 + 5], xs[6] * w[pc * 8 + 6], xs[7] * w[pc * 8 + 7]);
+            if (full_chunk) {
+              // stage in the decay tile (this thread's row, columns already consumed above); the
+              // store warp writes the tile out with TMA
+              const float sg = a.dld_sub ? -1.f : 1.f;
+              const int d0 = bt * 32 + pc * 8;
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
+              continue;
+            }
             if (a.dld_sub) {
               const float4 ol = dp[pc * 2], oh = dp[pc * 2 + 1];
               lo = make_float4(ol.x - lo.x, ol.y - lo.y, ol.z - lo.z, ol.w - lo.w);
@@ -556,7 +575,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
 template <typename T, bool TMODE>
 int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
-  alignas(64) CUtensorMap mx, my, mz, ml, mo;
+  alignas(64) CUtensorMap mx, my, mz, ml, mo, md;
   int rc;
   if ((rc = make_map(&mx, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
@@ -565,6 +584,10 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   if ((rc = make_map(&mo, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if (p.dld != nullptr && ((reinterpret_cast<uintptr_t>(p.xrow) | reinterpret_cast<uintptr_t>(p.dld)) & 15u))
     return LA_ERR_MISALIGNED;
+  // without a gradient buffer the map is never used; point it at the decay tensor to keep it valid
+  if ((rc = make_map(&md, p.dld != nullptr ? static_cast<const void *>(p.dld) : static_cast<const void *>(p.ldk),
+                     LA_F32, p.B, p.N, p.H)) != LA_OK)
+    return rc;
   LavdArgs a;
   a.out = p.out; a.xrow = p.xrow; a.dld = p.xrow ? p.dld : nullptr; a.dld_sub = p.dld_sub;
   a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
@@ -577,7 +600,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
     return LA_ERR_CUDA;
   const int nb = p.cu ? p.M : p.B;
-  kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, ml, mo, a);
+  kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, ml, mo, md, a);
   return launch_status();
 }
 

@@ -338,35 +338,64 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
   }
 }
 
-// One CTA per (sequence, head), one thread per feature f: in-place reverse cumulative sum over
-// tokens plus the state term (sum_option 0 / 1 of the reference kernel named above).
-__global__ void revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
-                                     const int64_t *cu, int N, int H, int F, int D, int E,
-                                     int f_is_row) {
-  const int h = blockIdx.x, seq = blockIdx.y, f = threadIdx.x;
-  if (f >= F) return;
+// One CTA per (sequence, head): in-place reverse cumulative sum over tokens of every feature f,
+// plus the state term (sum_option 0 / 1 of the reference kernel named above).  The sequence is cut
+// into `lanes` contiguous parts, one per group of Fpad threads: part sums, suffix offsets across
+// parts, then the running sum inside each part -- two reads and one write of the buffer.
+__global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
+                                                             const int64_t *cu, int N, int H, int F, int Fpad,
+                                                             int D, int E, int f_is_row) {
+  extern __shared__ float part[];  // [lanes + 1][Fpad]; row `lanes` holds the state term
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int lanes = blockDim.x / Fpad;
+  const int f = threadIdx.x % Fpad, ln = threadIdx.x / Fpad;
   int64_t t_begin = 0, t_end = N, bidx = seq;
   if (cu != nullptr) { t_begin = cu[seq]; t_end = cu[seq + 1]; bidx = 0; }
-  float run = 0.f;
-  if (sfin != nullptr && dsfin != nullptr) {
-    const int64_t base = ((int64_t)seq * H + h) * (int64_t)D * E;
-    if (f_is_row) {
-      for (int e = 0; e < E; ++e) run = fmaf(sfin[base + (int64_t)f * E + e], dsfin[base + (int64_t)f * E + e], run);
-    } else {
-      for (int d = 0; d < D; ++d) run = fmaf(sfin[base + (int64_t)d * E + f], dsfin[base + (int64_t)d * E + f], run);
-    }
-  }
+  const int64_t len = t_end - t_begin;
+  const int64_t per = (len + lanes - 1) / lanes;
+  const int64_t p0 = t_begin + ln * per, p1 = min(t_end, p0 + per);
   const int64_t stride = (int64_t)H * F;
   float *ptr = buf + ((bidx * N) * H + h) * (int64_t)F + f;
-  int64_t t = t_end - 1;
-  for (; t - 7 >= t_begin; t -= 8) {
+  const bool on = f < F;
+
+  float s = 0.f;
+  if (on) {
+    int64_t t = p0;
+    for (; t + 7 < p1; t += 8) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = ptr[(t + i) * stride];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[i];
+    }
+    for (; t < p1; ++t) s += ptr[t * stride];
+  }
+  part[ln * Fpad + f] = s;
+  if (ln == 0) {
+    float st = 0.f;
+    if (on && sfin != nullptr && dsfin != nullptr) {
+      const int64_t base = ((int64_t)seq * H + h) * (int64_t)D * E;
+      if (f_is_row) {
+        for (int e = 0; e < E; ++e) st = fmaf(sfin[base + (int64_t)f * E + e], dsfin[base + (int64_t)f * E + e], st);
+      } else {
+        for (int d = 0; d < D; ++d) st = fmaf(sfin[base + (int64_t)d * E + f], dsfin[base + (int64_t)d * E + f], st);
+      }
+    }
+    part[lanes * Fpad + f] = st;
+  }
+  __syncthreads();
+  if (!on) return;
+  float run = part[lanes * Fpad + f];
+  for (int l = lanes - 1; l > ln; --l) run += part[l * Fpad + f];
+  int64_t t = p1 - 1;
+  for (; t - 7 >= p0; t -= 8) {
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = ptr[(t - i) * stride];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run; }
   }
-  for (; t >= t_begin; --t) { run += ptr[t * stride]; ptr[t * stride] = run; }
+  for (; t >= p0; --t) { run += ptr[t * stride]; ptr[t * stride] = run; }
 }
 
 }  // namespace
@@ -386,10 +415,12 @@ int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfin
                          int M, cudaStream_t stream) {
   const int nb = cu ? M : B;
   dim3 grid(H, nb);
-  const int threads = ((F + 31) / 32) * 32;
-  if (threads > 1024) return LA_ERR_UNSUPPORTED;
-  revcumsum_vec_kernel<<<grid, threads, 0, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, D,
-                                                     E, f_is_row);
+  const int fpad = ((F + 31) / 32) * 32;
+  if (fpad > 1024) return LA_ERR_UNSUPPORTED;
+  const int lanes = 1024 / fpad;
+  const size_t smem = sizeof(float) * (size_t)(lanes + 1) * fpad;
+  revcumsum_vec_kernel<<<grid, lanes * fpad, smem, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, fpad,
+                                                             D, E, f_is_row);
   return launch_status();
 }
 
