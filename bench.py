@@ -330,7 +330,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
                   f"{dt:.1f} s; documents are independent, cost is linear in tokens")
         return val, sample, threads
     if name == "C2":
-        bs, hs, n = 1, 16, cfg["N"]
+        bs, hs, n = 2, 32, cfg["N"]
         w = W.lasd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
         f = {k: v.float() for k, v in w.items()}
         ld = f["ld"]
