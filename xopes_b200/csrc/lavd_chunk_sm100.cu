@@ -86,32 +86,75 @@ __device__ __forceinline__ uint32_t ck_off(int i, int d) {
 }
 __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
 
-// One 16-byte piece (8 features starting at d0) of a 16-bit tile row times 2^(sgn*ckc) (and times
-// uvec for the update operand).
-template <typename T>
-__device__ __forceinline__ void scale_piece(uint4 v, const uint8_t *ck, int i, int d0, float sgn, bool zero_u,
-                                            const float *uvec, uint4 &scaled, uint4 &upd) {
+// 2^(+-ckc) for the 8 features starting at d0 of row i.
+template <bool NEG>
+__device__ __forceinline__ void decay_factors(const uint8_t *ck, int i, int d0, float (&f)[8]) {
   const float4 c0 = *reinterpret_cast<const float4 *>(ck + ck_off(i, d0));
   const float4 c1 = *reinterpret_cast<const float4 *>(ck + ck_off(i, d0 + 4));
+  if (NEG) {
+    f[0] = ex2(-c0.x); f[1] = ex2(-c0.y); f[2] = ex2(-c0.z); f[3] = ex2(-c0.w);
+    f[4] = ex2(-c1.x); f[5] = ex2(-c1.y); f[6] = ex2(-c1.z); f[7] = ex2(-c1.w);
+  } else {
+    f[0] = ex2(c0.x); f[1] = ex2(c0.y); f[2] = ex2(c0.z); f[3] = ex2(c0.w);
+    f[4] = ex2(c1.x); f[5] = ex2(c1.y); f[6] = ex2(c1.z); f[7] = ex2(c1.w);
+  }
+}
+// One 16-byte piece (8 16-bit features) times the factors f.
+template <typename T>
+__device__ __forceinline__ uint4 scale8(uint4 v, const float (&f)[8], float2 (&prod)[4]) {
+  uint4 o;
+  prod[0] = mul2(Fmt<T>::unpack(v.x), make_float2(f[0], f[1])); o.x = Fmt<T>::pack(prod[0].x, prod[0].y);
+  prod[1] = mul2(Fmt<T>::unpack(v.y), make_float2(f[2], f[3])); o.y = Fmt<T>::pack(prod[1].x, prod[1].y);
+  prod[2] = mul2(Fmt<T>::unpack(v.z), make_float2(f[4], f[5])); o.z = Fmt<T>::pack(prod[2].x, prod[2].y);
+  prod[3] = mul2(Fmt<T>::unpack(v.w), make_float2(f[6], f[7])); o.w = Fmt<T>::pack(prod[3].x, prod[3].y);
+  return o;
+}
+// The state-update operand: the scaled piece times the per-feature vector uvec (zero rows past the
+// end of the sequence).
+template <typename T>
+__device__ __forceinline__ uint4 update8(const float2 (&prod)[4], const float *uvec, int d0, bool zero) {
   const float4 u0 = *reinterpret_cast<const float4 *>(uvec + d0);
   const float4 u1 = *reinterpret_cast<const float4 *>(uvec + d0 + 4);
-  float2 f, p, q;
-  f = mul2(Fmt<T>::unpack(v.x), make_float2(ex2(sgn * c0.x), ex2(sgn * c0.y)));
-  scaled.x = Fmt<T>::pack(f.x, f.y);
-  p = mul2(f, make_float2(u0.x, u0.y));
-  f = mul2(Fmt<T>::unpack(v.y), make_float2(ex2(sgn * c0.z), ex2(sgn * c0.w)));
-  scaled.y = Fmt<T>::pack(f.x, f.y);
-  q = mul2(f, make_float2(u0.z, u0.w));
-  upd.x = zero_u ? 0u : Fmt<T>::pack(p.x, p.y);
-  upd.y = zero_u ? 0u : Fmt<T>::pack(q.x, q.y);
-  f = mul2(Fmt<T>::unpack(v.z), make_float2(ex2(sgn * c1.x), ex2(sgn * c1.y)));
-  scaled.z = Fmt<T>::pack(f.x, f.y);
-  p = mul2(f, make_float2(u1.x, u1.y));
-  f = mul2(Fmt<T>::unpack(v.w), make_float2(ex2(sgn * c1.z), ex2(sgn * c1.w)));
-  scaled.w = Fmt<T>::pack(f.x, f.y);
-  q = mul2(f, make_float2(u1.z, u1.w));
-  upd.z = zero_u ? 0u : Fmt<T>::pack(p.x, p.y);
-  upd.w = zero_u ? 0u : Fmt<T>::pack(q.x, q.y);
+  if (zero) return make_uint4(0u, 0u, 0u, 0u);
+  float2 p;
+  uint4 o;
+  p = mul2(prod[0], make_float2(u0.x, u0.y)); o.x = Fmt<T>::pack(p.x, p.y);
+  p = mul2(prod[1], make_float2(u0.z, u0.w)); o.y = Fmt<T>::pack(p.x, p.y);
+  p = mul2(prod[2], make_float2(u1.x, u1.y)); o.z = Fmt<T>::pack(p.x, p.y);
+  p = mul2(prod[3], make_float2(u1.z, u1.w)); o.w = Fmt<T>::pack(p.x, p.y);
+  return o;
+}
+template <typename T, bool NEG>
+__device__ __forceinline__ void rescale_xy(uint8_t *gbase, const uint8_t *ck, const float *uvec, int i, int wg, int L) {
+  // X <- X 2^(+-ckc), Y <- Y 2^(-+ckc), U <- Y' uvec for this thread's row and 64 columns
+#pragma unroll 2
+  for (int pc = 0; pc < 8; ++pc) {
+    const int d0 = wg * 64 + pc * 8;
+    const uint32_t off = wg * kBoxBytes + sw128_offset(i, pc);
+    float fx[8], fy[8];
+    decay_factors<NEG>(ck, i, d0, fx);
+    decay_factors<!NEG>(ck, i, d0, fy);
+    float2 prod[4];
+    uint4 *px = reinterpret_cast<uint4 *>(gbase + kOffX + off);
+    *px = scale8<T>(*px, fx, prod);
+    uint4 *py = reinterpret_cast<uint4 *>(gbase + kOffY + off);
+    *py = scale8<T>(*py, fy, prod);
+    *reinterpret_cast<uint4 *>(gbase + kOffU + off) = update8<T>(prod, uvec, d0, i >= L);
+  }
+}
+template <typename T, bool NEG>
+__device__ __forceinline__ void rescale_z(uint8_t *gbase, const uint8_t *ck, const float *uvec, int i, int wg, int L) {
+#pragma unroll 2
+  for (int pc = 0; pc < 8; ++pc) {
+    const int d0 = wg * 64 + pc * 8;
+    const uint32_t off = wg * kBoxBytes + sw128_offset(i, pc);
+    float fz[8];
+    decay_factors<NEG>(ck, i, d0, fz);
+    float2 prod[4];
+    uint4 *pz = reinterpret_cast<uint4 *>(gbase + kOffZ + off);
+    *pz = scale8<T>(*pz, fz, prod);
+    *reinterpret_cast<uint4 *>(gbase + kOffU + off) = update8<T>(prod, uvec, d0, i >= L);
+  }
 }
 
 template <typename T, bool TMODE>
@@ -299,81 +342,66 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       mbar_wait(bar_full, par, abort_flag, a.status, kStFull);
 
       // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
-      // Thread (d = tid % 128, half = tid / 128) scans rows [64 half, 64 half + 64) as four
-      // interleaved 16-row segments.
+      // Thread (dg = tid % 32, seg = tid / 32) scans the four features [4 dg, 4 dg + 4) over the
+      // sixteen rows of segment seg with 128-bit accesses; segment totals meet in shared memory.
       {
-        const int d = tid & 127, half = tid >> 7;
-        float run[4];
+        const int dg = tid & 31, seg = tid >> 5, d0 = dg * 4;
+        const uint32_t colbase = (uint32_t)(d0 >> 5) * kBoxBytes;
+        const uint32_t c4 = (uint32_t)((d0 & 31) >> 2);
+        float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int sg = 0; sg < 4; ++sg) run[sg] = 0.f;
-#pragma unroll 4
         for (int r = 0; r < 16; ++r) {
-#pragma unroll
-          for (int sg = 0; sg < 4; ++sg) {
-            const int row = half * 64 + sg * 16 + r;
-            float *p = reinterpret_cast<float *>(ck + ck_off(row, d)) + (d & 3);
-            const float v = (row < L) ? *p * kLog2e : 0.f;
-            run[sg] += v;
-            *p = run[sg];
+          const int row = seg * 16 + r;  // row & 7 == r & 7
+          float4 *p = reinterpret_cast<float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
+          if (row < L) {
+            const float4 v = *p;
+            run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
+            run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
           }
+          *p = run;
         }
-#pragma unroll
-        for (int sg = 0; sg < 4; ++sg) segtot[(half * 4 + sg) * 128 + d] = run[sg];
+        *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = run;
         named_bar_sync(1, kComputeThreads);
-        float pre[8];
-        float acc = 0.f;
+        float4 pre = make_float4(0.f, 0.f, 0.f, 0.f), m = pre, acc = pre;
 #pragma unroll
         for (int sgl = 0; sgl < 8; ++sgl) {
-          pre[sgl] = acc;
-          acc += segtot[sgl * 128 + d];
+          if (sgl == seg) pre = acc;
+          if (sgl == 4) m = acc;
+          const float4 t = *reinterpret_cast<const float4 *>(&segtot[sgl * 128 + d0]);
+          acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
         }
-        const float m = pre[4], g = acc;  // ck at row 63 and at row 127
-#pragma unroll 4
-        for (int r = 0; r < 16; ++r) {
+        const float4 g = acc;  // m: ck at row 63, g: ck at row 127
+        const float4 sh = make_float4(pre.x - m.x, pre.y - m.y, pre.z - m.z, pre.w - m.w);
 #pragma unroll
-          for (int sg = 0; sg < 4; ++sg) {
-            const int row = half * 64 + sg * 16 + r;
-            float *p = reinterpret_cast<float *>(ck + ck_off(row, d)) + (d & 3);
-            *p = *p + (pre[half * 4 + sg] - m);
-          }
+        for (int r = 0; r < 16; ++r) {
+          const int row = seg * 16 + r;
+          float4 *p = reinterpret_cast<float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
+          float4 v = *p;
+          v.x += sh.x; v.y += sh.y; v.z += sh.z; v.w += sh.w;
+          *p = v;
         }
-        if (half == 0) {
-          sm->uvec[d] = rev ? ex2(m) : ex2(g - m);
-          sm->cvec[d] = rev ? ex2(g - m) : ex2(m);
-          sm->gfac[d] = ex2(g);
-          if (-m > SafeBits<T>::value || -(g - m) > SafeBits<T>::value) atomicExch(a.unsafe, 1);
+        if (seg == 0) {
+          const float mm[4] = {m.x, m.y, m.z, m.w}, gg[4] = {g.x, g.y, g.z, g.w};
+          bool bad = false;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            sm->uvec[d0 + c] = rev ? ex2(mm[c]) : ex2(gg[c] - mm[c]);
+            sm->cvec[d0 + c] = rev ? ex2(gg[c] - mm[c]) : ex2(mm[c]);
+            sm->gfac[d0 + c] = ex2(gg[c]);
+            bad = bad || (-mm[c] > SafeBits<T>::value) || (-(gg[c] - mm[c]) > SafeBits<T>::value);
+          }
+          if (bad) atomicExch(a.unsafe, 1);
         }
         named_bar_sync(1, kComputeThreads);
       }
 
       // ---- R: rescale operands in place, build the state-update operand U
       if (!TMODE) {
-        const float sx = rev ? -1.f : 1.f;
-#pragma unroll 2
-        for (int pc = 0; pc < 8; ++pc) {  // X
-          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffX + wg * kBoxBytes + sw128_offset(i, pc));
-          uint4 sc, up;
-          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, sx, true, sm->uvec, sc, up);
-          *p = sc;
-        }
-#pragma unroll 2
-        for (int pc = 0; pc < 8; ++pc) {  // Y and U
-          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffY + wg * kBoxBytes + sw128_offset(i, pc));
-          uint4 sc, up;
-          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, -sx, i >= L, sm->uvec, sc, up);
-          *p = sc;
-          *reinterpret_cast<uint4 *>(gbase + kOffU + wg * kBoxBytes + sw128_offset(i, pc)) = up;
-        }
+        if (rev) rescale_xy<T, true>(gbase, ck, sm->uvec, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
+        else rescale_xy<T, false>(gbase, ck, sm->uvec, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
       } else {
-        const float sz = rev ? 1.f : -1.f;
-#pragma unroll 2
-        for (int pc = 0; pc < 8; ++pc) {  // Z and U
-          uint4 *p = reinterpret_cast<uint4 *>(gbase + kOffZ + wg * kBoxBytes + sw128_offset(i, pc));
-          uint4 sc, up;
-          scale_piece<T>(*p, ck, i, wg * 64 + pc * 8, sz, i >= L, sm->uvec, sc, up);
-          *p = sc;
-          *reinterpret_cast<uint4 *>(gbase + kOffU + wg * kBoxBytes + sw128_offset(i, pc)) = up;
-        }
+        if (rev) rescale_z<T, false>(gbase, ck, sm->uvec, i, wg, L);   // dk: Z = q 2^(ck-m)
+        else rescale_z<T, true>(gbase, ck, sm->uvec, i, wg, L);        // dq: Z = k 2^(m-ck)
       }
       fence_proxy_async();
       mbar_arrive(bar_r);
