@@ -50,7 +50,7 @@ constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
 
 // status codes written to the device status word
 constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104, kStD = 105, kStF = 106, kStH = 107,
-              kStT = 108, kStY = 109;
+              kStT = 108, kStY = 109, kStX = 110, kStL = 111;
 
 struct Small {
   unsigned long long full[kStages];
@@ -62,6 +62,8 @@ struct Small {
   unsigned long long bar_y;   // rescaled Y written                        (compute -> MMA warp)
   unsigned long long bar_f;   // masked P~ written                         (compute -> MMA warp)
   unsigned long long bar_h;   // output tile staged, W1/W2 consumed        (compute -> store and MMA warps)
+  unsigned long long bar_x;   // X T_in with the high half of the state copy complete (MMA warp -> compute)
+  unsigned long long bar_l;   // low half of the state copy written, T rescaled (compute -> MMA warp)
   uint32_t tmem_base;
   int abort_flag;
   int issued;
@@ -173,6 +175,11 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w);
   const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
   const uint32_t bar_t = smem_u32(&sm->bar_t), bar_y = smem_u32(&sm->bar_y);
+  const uint32_t bar_x = smem_u32(&sm->bar_x), bar_l = smem_u32(&sm->bar_l);
+  // With a log-decay gradient requested the 16-bit state copy is split into a high and a low
+  // half (two passes of X T_in over the same buffer): the gradient is a long cumulative sum of
+  // nearly cancelling terms and the rounding of a single 16-bit copy dominates its error.
+  const bool split = a.rowdot != nullptr;
   volatile int *abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -183,6 +190,8 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     mbar_init(bar_p, 1);
     mbar_init(bar_w, 1);
     mbar_init(bar_t, 1);
+    mbar_init(bar_x, 1);
+    mbar_init(bar_l, kComputeThreads);
     mbar_init(bar_d, kComputeThreads);
     mbar_init(bar_y, kComputeThreads);
     mbar_init(bar_f, kComputeThreads);
@@ -258,6 +267,16 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
           mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
+        }
+        if (split) {
+          mma_commit(bar_x);  // the compute warps may now overwrite the copy with its low half
+          mbar_wait(bar_l, par, abort_flag, a.status, kStL);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+            mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, 1);
+          }
         }
         // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
         // next chunk's state copy while P~ Z still runs
@@ -368,6 +387,45 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       return d;
     };
     // D: state in -> 16-bit copy in shared memory (B operand of X T_in); T <- e^g T
+    // low half of the split copy: T - round16(T), written over the high half once X T_hi is done;
+    // the rescaling of T that state_copy skipped in split mode happens here
+    auto state_copy_low = [&](float eg, uint32_t par) {
+      mbar_wait(bar_x, par, abort_flag, a.status, kStX);
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
+      tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
+      tmem_wait_ld();
+      uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t(&r)[32] = hf ? r1 : r0;
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x0 = __uint_as_float(r[pc * 8 + 2 * j]), x1 = __uint_as_float(r[pc * 8 + 2 * j + 1]);
+            const float2 hi = Fmt<T>::unpack(Fmt<T>::pack(x0, x1));
+            w[j] = Fmt<T>::pack(x0 - hi.x, x1 - hi.y);
+          }
+          *reinterpret_cast<uint4 *>(box + sw128_offset(i, hf * 4 + pc)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      const float2 eg2 = make_float2(eg, eg);
+#pragma unroll
+      for (int k = 0; k < 32; k += 2) {
+        const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
+        r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
+        r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
+      }
+      tmem_st32(tl + kColT + (2 * wg) * 32, r0);
+      tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
+      tmem_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar_l);
+    };
     auto state_copy = [&](float eg) {
       uint32_t r0[32], r1[32];
       tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
@@ -392,16 +450,18 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
         *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
       }
-      const float2 eg2 = make_float2(eg, eg);
+      if (!split) {
+        const float2 eg2 = make_float2(eg, eg);
 #pragma unroll
-      for (int k = 0; k < 32; k += 2) {
-        const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
-        r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
-        r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
+        for (int k = 0; k < 32; k += 2) {
+          const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
+          r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
+          r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
+        }
+        tmem_st32(tl + kColT + (2 * wg) * 32, r0);
+        tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
+        tmem_wait_st();
       }
-      tmem_st32(tl + kColT + (2 * wg) * 32, r0);
-      tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
-      tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_d);
@@ -425,6 +485,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const float c_i = cur.c;
 
       LA_TRACE(0);
+      if (split) state_copy_low(cur.eg, par);
       // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
       mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
       mbar_wait(bar_p, par, abort_flag, a.status, kStP);
