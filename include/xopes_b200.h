@@ -183,6 +183,13 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
  * q, o are (1,N,H,D) / (1,N,H,E); cum is fp32 (T1,H), the inclusive cumulative log decay from the
  * rank's first token; s_in is fp32 (H,D,E), the document's true incoming state.
  * ------------------------------------------------------------------------------------------- */
+/* The true state entering `rank` from the all-gathered per-rank summaries, each a row of
+ * H*D*E + H + 2 floats [S_loc | G | open_end | spans]:
+ *     S_in(r+1) = open_end(r) * (S_loc(r) + spans(r) * exp(G(r)) * S_in(r)),  S_in(0) = 0.
+ * gathered is (world, H*D*E + H + 2) fp32, s_in (H,D,E) fp32.  No counterpart in the reference. */
+LA_API int la_seqpar_fold(const float *gathered, float *s_in, int64_t rank, int64_t H, int64_t D,
+                          int64_t E, void *stream);
+
 LA_API int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int64_t T1,
                              int64_t N, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
 

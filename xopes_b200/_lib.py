@@ -43,6 +43,7 @@ SIGNATURES = {
     "la_lavd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64]),
     "la_lavd_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_seqpar_fold": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_correct": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_decode_scalar": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp,
                                 _i64, _i64, _i64, _i64, _i32, _vp]),

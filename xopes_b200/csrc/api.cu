@@ -441,6 +441,14 @@ int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_i
                                static_cast<cudaStream_t>(stream));
 }
 
+int la_seqpar_fold(const float *gathered, float *s_in, int64_t rank, int64_t H, int64_t D, int64_t E,
+                   void *stream) {
+  if (gathered == nullptr || s_in == nullptr) return LA_ERR_NULL_POINTER;
+  if (rank < 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  if (rank > 4096 || H * D * E > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  return launch_seqpar_fold(gathered, s_in, (int)rank, (int)H, (int)(D * E), static_cast<cudaStream_t>(stream));
+}
+
 // ------------------------------------------------------------------------------------------------
 // decode
 // ------------------------------------------------------------------------------------------------

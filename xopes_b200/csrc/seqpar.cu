@@ -217,7 +217,31 @@ int launch_generic(const void *q, void *o, const float *cum, const float *s_in, 
   return launch_status();
 }
 
+// S_in of `rank` from the gathered per-rank summaries [S_loc (HDE) | G (H) | open_end | spans]:
+//   S_in(r+1) = open_end(r) * (S_loc(r) + spans(r) * exp(G(r)) * S_in(r)),  S_in(0) = 0.
+__global__ void seqpar_fold_kernel(const float *__restrict__ gathered, float *__restrict__ s_in, int rank, int H,
+                                   int DE) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long hde = (long long)H * DE;
+  if (idx >= hde) return;
+  const int h = (int)(idx / DE);
+  const long long row = hde + H + 2;
+  float s = 0.f;
+  for (int r = 0; r < rank; ++r) {
+    const float *g = gathered + r * row;
+    s = g[hde + H] * (g[idx] + g[hde + H + 1] * expf(g[hde + h]) * s);
+  }
+  s_in[idx] = s;
+}
+
 }  // namespace
+
+int launch_seqpar_fold(const float *gathered, float *s_in, int rank, int H, int DE, cudaStream_t st) {
+  const long long hde = (long long)H * DE;
+  const int threads = 256;
+  seqpar_fold_kernel<<<(unsigned)((hde + threads - 1) / threads), threads, 0, st>>>(gathered, s_in, rank, H, DE);
+  return launch_status();
+}
 
 int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,
                           int D, int E, int dtype, cudaStream_t st) {

@@ -96,22 +96,30 @@ def local_phase(q, k, v, ld, plan: ShardPlan, local_forward: Optional[Callable] 
     o, states = fwd(q, k, v, ld, plan.local_cu)
     e = o.shape[-1]
     dev = q.device
-    summary = torch.zeros(h * d * e + h + 2, dtype=torch.float32, device=dev)
-    if plan.open_end:
-        last0 = plan.local_cu[-2]
-        summary[: h * d * e] = states[-1].reshape(-1)
-        if ld.dim() == 1:
-            summary[h * d * e: h * d * e + h] = ld.float() * float(t - last0)
-        else:
-            summary[h * d * e: h * d * e + h] = _ld_local(ld, t, h)[last0:].sum(0)
-        summary[-2] = 1.0
-        summary[-1] = 1.0 if (plan.open_start and len(plan.doc_ids) == 1) else 0.0
+    if not plan.open_end:
+        return o, states, torch.zeros(h * d * e + h + 2, dtype=torch.float32, device=dev)
+    last0 = plan.local_cu[-2]
+    if ld.dim() == 1:
+        g = ld.float() * float(t - last0)
+    else:
+        g = _ld_local(ld, t, h)[last0:].sum(0)
+    spans = 1.0 if (plan.open_start and len(plan.doc_ids) == 1) else 0.0
+    flags = torch.tensor([1.0, spans], dtype=torch.float32).to(dev, non_blocking=True)
+    summary = torch.cat([states[-1].reshape(-1), g, flags])
     return o, states, summary
 
 
 def fold_incoming_state(gathered: torch.Tensor, rank: int, h: int, d: int, e: int) -> torch.Tensor:
     """Phase 2, after the all-gather: the true state entering `rank`, from the summaries of the
     ranks before it (gathered is (world, H*D*E + H + 2)).  No host synchronisation."""
+    if gathered.is_cuda:  # one kernel instead of half a dozen small ones per preceding rank
+        lib = _lib.load()
+        g = gathered.contiguous()
+        s_in = torch.empty(h, d, e, dtype=torch.float32, device=g.device)
+        with torch.cuda.device(g.device):
+            rc = lib.la_seqpar_fold(_lib.ptr(g), _lib.ptr(s_in), rank, h, d, e, _lib.stream_of(g))
+        _lib.check(rc, "la_seqpar_fold")
+        return s_in
     s_in = torch.zeros(h, d, e, dtype=torch.float32, device=gathered.device)
     for r in range(rank):
         row = gathered[r]
