@@ -190,6 +190,23 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
 LA_API int la_seqpar_fold(const float *gathered, float *s_in, int64_t rank, int64_t H, int64_t D,
                           int64_t E, void *stream);
 
+/* Segmented forward inside one GPU: long sequences are cut into segments that run as independent
+ * "documents" of la_lasd_fwd (zero incoming state), then stitched.  seg_table is int32 (nseg, 4):
+ * {first token, length, index of the segment's first 128-token tile among all corrected tiles,
+ * 1 if the segment starts a document}.  la_seqpar_fold_segments turns the segments' end states
+ * (nseg,H,D,E) into true end states in place and writes each segment's incoming state to s_in,
+ * given seg_decay (nseg,H) = the summed log decay of each segment.  la_seqpar_correct_multi then
+ * adds exp(cum[t] - cum[start-1]) q_t^T s_in[seg] to every token of the listed segments (pass only
+ * the segments that continue a document; their tile indices run from 0 to total_tiles), cum being
+ * the inclusive cumulative log decay (N,H) of the whole stream.  16-bit, D = E = 128 only.
+ * No counterpart in the reference. */
+LA_API int la_seqpar_fold_segments(float *states, const float *seg_decay, const int32_t *seg_table,
+                                   float *s_in, int64_t nseg, int64_t H, int64_t D, int64_t E,
+                                   void *stream);
+LA_API int la_seqpar_correct_multi(const void *q, void *o, const float *cum, const float *s_in,
+                                   const int32_t *seg_table, int64_t nseg, int64_t total_tiles,
+                                   int64_t N, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
+
 LA_API int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int64_t T1,
                              int64_t N, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
 

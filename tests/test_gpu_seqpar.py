@@ -49,3 +49,38 @@ def test_emulated_ranks_match_whole_stream(world, lens, h, d, e, dtype, tol, per
         for j, doc in enumerate(plan.doc_ids):
             if cu[doc + 1] <= b:
                 assert_close(f"state doc {doc}", rs[doc], states[j], tol)
+
+
+@pytest.mark.parametrize("per_head", [True, False])
+@pytest.mark.parametrize("b,n,h", [(1, 8192, 2), (2, 3000, 1)])
+def test_segmented_forward_inside_one_gpu(b, n, h, per_head):
+    """Few long sequences: lasd_fn cuts them into segments that run concurrently and stitches them
+    (xopes_b200/lightning_attn/segmented.py).  Output, final state and the gradients that follow
+    must match the oracle on the whole sequences."""
+    import xopes_b200 as xb
+    from xopes_b200.lightning_attn import segmented as sg
+    d = e = 128
+    dtype = torch.bfloat16
+    assert sg.worth_segmenting([(i * n, (i + 1) * n) for i in range(b)], h, sg.auto_cap(b * n, h))
+    g = torch.Generator().manual_seed(3)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    q = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    k = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(b, n, h, e, generator=g))
+    if per_head:
+        ld = torch.log(1 - 2.0 ** (-6 - torch.arange(h, dtype=torch.float32)))
+        ld_full = ld.view(1, 1, h).expand(b, n, h)
+    else:
+        ld = ld_full = torch.nn.functional.logsigmoid(torch.randn(b, n, h, generator=g) + 4)
+    s0 = 0.1 * torch.randn(b, h, d, e, generator=g)
+    do = cast(torch.randn(b, n, h, e, generator=g))
+    qc, kc, vc = (t.to(dtype).cuda().requires_grad_() for t in (q, k, v))
+    o, sf = xb.lasd_fn(qc, kc, vc, ld.cuda(), initial_state=s0.cuda())
+    ro, rsf = orc.lasd_forward(q, k, v, ld_full, s0)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    (o.float() * do.cuda()).sum().backward()
+    rq, rk, rv, _, _ = orc.lasd_backward(q, k, v, ld_full, do, s0)
+    assert_close("dq", rq, qc.grad.float(), TOL_BF16)
+    assert_close("dk", rk, kc.grad.float(), TOL_BF16)
+    assert_close("dv", rv, vc.grad.float(), TOL_BF16)

@@ -441,6 +441,27 @@ int la_seqpar_correct(const void *q, void *o, const float *cum, const float *s_i
                                static_cast<cudaStream_t>(stream));
 }
 
+int la_seqpar_fold_segments(float *states, const float *seg_decay, const int32_t *seg_table, float *s_in,
+                            int64_t nseg, int64_t H, int64_t D, int64_t E, void *stream) {
+  if (states == nullptr || seg_decay == nullptr || seg_table == nullptr || s_in == nullptr) return LA_ERR_NULL_POINTER;
+  if (nseg <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  if (nseg > 65535 || H * D * E > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  return launch_seqpar_fold_segments(states, seg_decay, seg_table, s_in, (int)nseg, (int)H, (int)(D * E),
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int la_seqpar_correct_multi(const void *q, void *o, const float *cum, const float *s_in, const int32_t *seg_table,
+                            int64_t nseg, int64_t total_tiles, int64_t N, int64_t H, int64_t D, int64_t E, int dtype,
+                            void *stream) {
+  if (q == nullptr || o == nullptr || cum == nullptr || s_in == nullptr || seg_table == nullptr)
+    return LA_ERR_NULL_POINTER;
+  if (nseg < 0 || total_tiles < 0 || N <= 0 || H <= 0) return LA_ERR_BAD_SHAPE;
+  if (D != 128 || E != 128 || N < 128 || !(dtype == LA_BF16 || dtype == LA_F16)) return LA_ERR_UNSUPPORTED;
+  if (N > (int64_t)1 << 30 || H > 65535 || total_tiles > 0x7fffffff || nseg > 65535) return LA_ERR_TOO_LARGE;
+  return launch_seqpar_correct_multi(q, o, cum, s_in, seg_table, (int)nseg, (int)total_tiles, (int)N, (int)H, dtype,
+                                     static_cast<cudaStream_t>(stream));
+}
+
 int la_seqpar_fold(const float *gathered, float *s_in, int64_t rank, int64_t H, int64_t D, int64_t E,
                    void *stream) {
   if (gathered == nullptr || s_in == nullptr) return LA_ERR_NULL_POINTER;

@@ -57,6 +57,10 @@ int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream);
 int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,
                           int D, int E, int dtype, cudaStream_t st);
 int launch_seqpar_fold(const float *gathered, float *s_in, int rank, int H, int DE, cudaStream_t st);
+int launch_seqpar_fold_segments(float *states, const float *G, const int *seg, float *s_in, int nseg, int H, int DE,
+                                cudaStream_t st);
+int launch_seqpar_correct_multi(const void *q, void *o, const float *cum, const float *s_in, const int *seg,
+                                int nseg, int total_tiles, int N, int H, int dtype, cudaStream_t st);
 // phase timestamps of CTA 0 (2 x 4096 x 16 int64) are written to buf by later passes; null disables
 void chunk_set_trace(long long *buf);
 // one 128x128x128 product through one operand staging variant (see chunk_sm100.cu)

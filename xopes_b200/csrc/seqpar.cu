@@ -73,19 +73,32 @@ template <> struct FmtC<__half> {
   }
 };
 
-// grid (tiles, H); 128 threads.  q is (1, N, H, 128); tokens [0, T1) are corrected.
+// grid (tiles, H); 128 threads.  q is (1, N, H, 128).  Without a segment table tokens [0, T1) are
+// corrected with one S_in and cum[t]; with a table (nseg rows of {start, length, first tile,
+// flag}) segment s covers tokens [start, start + length), uses s_in[s] and the weight
+// exp(cum[t] - cum[start - 1]), cum being the inclusive cumulative log decay of the whole stream.
 template <typename T>
 __global__ void __launch_bounds__(128, 1)
 seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *__restrict__ cum,
-                  const float *__restrict__ s_in, int T1, int H, int *status) {
+                  const float *__restrict__ s_in, int T1, int H, const int *__restrict__ seg, int nseg,
+                  int *status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *gbase = smem_raw + (base - raw);
   SmallC *sm = reinterpret_cast<SmallC *>(gbase + 2 * kTile);
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int tile = blockIdx.x, h = blockIdx.y;
-  const int tok0 = tile * 128;
+  const int h = blockIdx.y;
+  int tile = blockIdx.x, start = 0, slen = T1;
+  if (seg != nullptr) {
+    int sidx = 0;
+    while (sidx + 1 < nseg && tile >= seg[4 * (sidx + 1) + 2]) ++sidx;
+    start = seg[4 * sidx];
+    slen = seg[4 * sidx + 1];
+    tile -= seg[4 * sidx + 2];
+    s_in += (long long)sidx * H * 128 * 128;
+  }
+  const int tok0 = start + tile * 128;
   const uint32_t bar_full = smem_u32(&sm->full), bar_done = smem_u32(&sm->done);
   volatile int *abort_flag = &sm->abort_flag;
   if (tid == 0) {
@@ -136,14 +149,19 @@ seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *
   mbar_wait(bar_done, 0, abort_flag, status, 202);
   tc_fence_after();
   const int t = tok0 + tid;
+  const bool valid = tile * 128 + tid < slen;
   const uint32_t tl = tmem + ((uint32_t)(32 * warp) << 16);
-  const float w = (t < T1) ? expf(cum[(long long)t * H + h]) : 0.f;
+  float w = 0.f;
+  if (valid) {
+    const float c0 = start > 0 ? cum[(long long)(start - 1) * H + h] : 0.f;
+    w = expf(cum[(long long)t * H + h] - c0);
+  }
   T *orow = o + ((long long)t * H + h) * 128;
   for (int bt = 0; bt < 4; ++bt) {
     uint32_t r[32];
     tmem_ld32(tl + bt * 32, r);
     tmem_wait_ld();
-    if (t < T1) {
+    if (valid) {
       uint4 *op = reinterpret_cast<uint4 *>(orow + bt * 32);
 #pragma unroll
       for (int pc = 0; pc < 4; ++pc) {
@@ -190,7 +208,7 @@ int make_q_map(CUtensorMap *m, const void *ptr, int dtype, int N, int H) {
 
 template <typename T>
 int launch_tc(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H, int dtype,
-              cudaStream_t st) {
+              cudaStream_t st, const int *seg = nullptr, int nseg = 0, int total_tiles = 0) {
   alignas(64) CUtensorMap mq;
   int rc = make_q_map(&mq, q, dtype, N, H);
   if (rc != LA_OK) return rc;
@@ -200,8 +218,8 @@ int launch_tc(const void *q, void *o, const float *cum, const float *s_in, int T
   const int smem = 2 * kTile + 64 + 1024;
   auto kern = seqpar_correct_tc<T>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return LA_ERR_CUDA;
-  dim3 grid((T1 + 127) / 128, H);
-  kern<<<grid, 128, smem, st>>>(mq, static_cast<T *>(o), cum, s_in, T1, H, status);
+  dim3 grid(seg != nullptr ? total_tiles : (T1 + 127) / 128, H);
+  kern<<<grid, 128, smem, st>>>(mq, static_cast<T *>(o), cum, s_in, T1, H, seg, nseg, status);
   return launch_status();
 }
 
@@ -235,6 +253,43 @@ __global__ void seqpar_fold_kernel(const float *__restrict__ gathered, float *__
 }
 
 }  // namespace
+
+// Stitch consecutive segments of the same document, all run with a zero incoming state:
+//   s_in(k) = 0 if segment k starts a document, else the true end state of segment k-1;
+//   states(k) <- states(k) + exp(G(k)) s_in(k)        (its true end state).
+// seg rows are {start, length, first tile, starts-a-document}.
+__global__ void seqpar_fold_segments_kernel(float *__restrict__ states, const float *__restrict__ G,
+                                            const int *__restrict__ seg, float *__restrict__ s_in, int nseg, int H,
+                                            int DE) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long hde = (long long)H * DE;
+  if (idx >= hde) return;
+  const int h = (int)(idx / DE);
+  float s = 0.f;
+  for (int k = 0; k < nseg; ++k) {
+    if (seg[4 * k + 3] != 0) s = 0.f;
+    s_in[k * hde + idx] = s;
+    s = states[k * hde + idx] + expf(G[(long long)k * H + h]) * s;
+    states[k * hde + idx] = s;
+  }
+}
+
+int launch_seqpar_fold_segments(float *states, const float *G, const int *seg, float *s_in, int nseg, int H, int DE,
+                                cudaStream_t st) {
+  const long long hde = (long long)H * DE;
+  const int threads = 256;
+  seqpar_fold_segments_kernel<<<(unsigned)((hde + threads - 1) / threads), threads, 0, st>>>(states, G, seg, s_in,
+                                                                                            nseg, H, DE);
+  return launch_status();
+}
+
+int launch_seqpar_correct_multi(const void *q, void *o, const float *cum, const float *s_in, const int *seg,
+                                int nseg, int total_tiles, int N, int H, int dtype, cudaStream_t st) {
+  if (nseg <= 0 || total_tiles <= 0) return LA_OK;
+  if (dtype == LA_BF16) return launch_tc<__nv_bfloat16>(q, o, cum, s_in, 0, N, H, dtype, st, seg, nseg, total_tiles);
+  if (dtype == LA_F16) return launch_tc<__half>(q, o, cum, s_in, 0, N, H, dtype, st, seg, nseg, total_tiles);
+  return LA_ERR_UNSUPPORTED;
+}
 
 int launch_seqpar_fold(const float *gathered, float *s_in, int rank, int H, int DE, cudaStream_t st) {
   const long long hde = (long long)H * DE;

@@ -57,6 +57,28 @@ def _cu(cu_seqlens, device):
     return cu, cu.numel() - 1
 
 
+def _segmentation(lib, q, ld32, strides, cu, b, n, h, d, e, flags):
+    """Decide whether the forward should run segmented (few long sequences on the tensor path,
+    xopes_b200/lightning_attn/segmented.py).  Returns (doc bounds, cap, ld over the flattened
+    stream, its strides) or None.  Only for calls without cu_seqlens: the bounds must be known on
+    the host without a device round trip."""
+    from . import segmented as sg
+    if cu is not None or (flags & _lib.FLAG_FORCE_RECURRENCE):
+        return None
+    if lib.la_lasd_path(n, d, e, _lib.dtype_code(q), flags) != 1:
+        return None
+    cap = sg.auto_cap(b * n, h)
+    bounds = [(i * n, (i + 1) * n) for i in range(b)]
+    if not sg.worth_segmenting(bounds, h, cap):
+        return None
+    sb, sn, sh = strides
+    if sn == 0 and sb == 0:            # per-head constant
+        return bounds, cap, ld32, (0, 0, sh)
+    if sb == n * sn or b == 1:          # batch and sequence strides collapse into one stream stride
+        return bounds, cap, ld32, (0, sn, sh)
+    return None
+
+
 class LasdFunction(torch.autograd.Function):
     """forward(q, k, v, ld, initial_state, cu_seqlens, flags) -> (o, final_state)."""
 
@@ -75,6 +97,18 @@ class LasdFunction(torch.autograd.Function):
         s0 = None
         if initial_state is not None:
             s0 = initial_state.detach().to(torch.float32).contiguous()
+        seg = _segmentation(lib, q, ld32, (sb, sn, sh), cu, b, n, h, d, e, flags)
+        if seg is not None:
+            from .segmented import lasd_forward_segmented
+            bounds, cap, ld_flat, strides = seg
+            o, sf = lasd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e),
+                                           ld_flat, strides, s0, bounds, cap)
+            o = o.view(b, n, h, e)
+            ctx.save_for_backward(q, k, v, ld, s0, cu)
+            ctx.flags = flags
+            ctx.state_dtype = None if initial_state is None else initial_state.dtype
+            ctx.set_materialize_grads(False)
+            return o, sf
         o = torch.empty(b, n, h, e, dtype=q.dtype, device=q.device)
         sf = torch.empty(nb, h, d, e, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):

@@ -1,0 +1,126 @@
+"""Segmented scalar-decay forward: sequence parallelism inside one GPU.
+
+The chunk kernel gives one CTA to every (sequence, head) and walks the sequence chunk by chunk, so
+a call with few, long sequences (B*H well below the 148 SMs) is bound by that serial walk.  Here
+long sequences are cut into segments that run as independent "documents" with a zero incoming
+state, all at once; the segments of a sequence are then stitched exactly as ranks are in the
+sequence-parallel forward: the segments' end states are folded front to back
+(la_seqpar_fold_segments) and every segment that continues a sequence receives the missing term
+o_t += exp(cum_t) q_t^T S_in (la_seqpar_correct_multi).  The price is one more pass over the
+corrected tokens (768 B per token and head instead of 1,024), so segments are made no shorter than
+needed to occupy the GPU.  Forward only; 16-bit inputs with D = E = 128.
+"""
+from typing import List, Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+NUM_SMS = 148
+
+
+def auto_cap(total_tokens: int, h: int) -> int:
+    """Segment length (a multiple of the 128-token chunk) that yields about one CTA per SM."""
+    segs = max(1, NUM_SMS // max(1, h))
+    cap = -(-total_tokens // segs)
+    return max(1024, -(-cap // 128) * 128)
+
+
+def plan_segments(doc_bounds: List[Tuple[int, int]], cap: int):
+    """Cut every document [a, b) into ceil(len / cap) nearly equal segments whose boundaries fall on
+    128-token chunk boundaries of the document.  Returns (seg_cu, first, last_of_doc)."""
+    seg_cu, first, last_of_doc = [doc_bounds[0][0]], [], []
+    for a, b in doc_bounds:
+        n = b - a
+        parts = max(1, -(-n // cap))
+        per = -(-(-(-n // parts)) // 128) * 128
+        t = a
+        k = 0
+        while t < b:
+            e = min(b, t + per)
+            seg_cu.append(e)
+            first.append(1 if k == 0 else 0)
+            t = e
+            k += 1
+        last_of_doc.append(len(first) - 1)
+    return seg_cu, first, last_of_doc
+
+
+def worth_segmenting(doc_bounds, h: int, cap: int) -> bool:
+    """Segmenting pays an extra pass over the continued segments plus a few small launches
+    (measured: ~0.15 ms), so it is used only when the plain launch would leave most SMs idle or
+    one sequence would run at least three times longer than a balanced share."""
+    ctas = len(doc_bounds) * h
+    longest = max(b - a for a, b in doc_bounds)
+    if ctas <= NUM_SMS // 4:
+        return longest > cap + cap // 2
+    return ctas < NUM_SMS and longest >= 3 * cap
+
+
+def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds, cap):
+    """q, k, v: (1, T, H, 128) contiguous 16-bit CUDA tensors (a batch flattened to one stream);
+    ld32 fp32 with element strides over (stream token, head) = ld_strides[1:]; doc_bounds the
+    sequences [(a, b), ...] in stream order; initial_state (ndocs, H, 128, 128) fp32 or None.
+    Returns (o (1,T,H,128), final states (ndocs,H,128,128) fp32)."""
+    lib = _lib.load()
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    seg_cu, first, last_of_doc = plan_segments(doc_bounds, cap)
+    nseg = len(first)
+    lens = [seg_cu[i + 1] - seg_cu[i] for i in range(nseg)]
+    cont = [i for i in range(nseg) if not first[i]]
+    tiles, tile0 = 0, []
+    for i in cont:
+        tile0.append(tiles)
+        tiles += -(-lens[i] // 128)
+    # one host->device copy for every table: cu (int64) | all segments (int32 x4) | continuing ones
+    table_all = [[seg_cu[i], lens[i], 0, first[i]] for i in range(nseg)]
+    table_cont = [[seg_cu[i], lens[i], tile0[j], 0] for j, i in enumerate(cont)]
+    cu_dev = torch.tensor(seg_cu, dtype=torch.int64).to(dev, non_blocking=True)
+    tab = torch.tensor(table_all + table_cont, dtype=torch.int32).to(dev, non_blocking=True)
+    tab_all, tab_cont = tab[:nseg], tab[nseg:]
+
+    s0 = None
+    if initial_state is not None:
+        s0 = torch.zeros(nseg, h, d, e, dtype=torch.float32, device=dev)
+        idx = torch.tensor([i for i in range(nseg) if first[i]], dtype=torch.int64).to(dev, non_blocking=True)
+        s0.index_copy_(0, idx, initial_state)
+    o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
+    st = torch.empty(nseg, h, d, e, dtype=torch.float32, device=dev)
+    _, sn, sh = ld_strides
+    stream = _lib.stream_of(q)
+    with torch.cuda.device(dev):
+        rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s0),
+                             _lib.ptr(cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, nseg,
+                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, stream)
+        _lib.check(rc, "la_lasd_fwd (segmented)")
+        # inclusive cumulative log decay of the stream, (T, H), and each segment's total
+        if sn == 0:  # constant per head
+            steps = torch.arange(1, t + 1, dtype=torch.float32, device=dev)
+            cum = steps.view(t, 1) * ld32.view(1, h)
+            seg_decay = torch.tensor(lens, dtype=torch.float32).to(dev, non_blocking=True).view(nseg, 1) * ld32.view(1, h)
+        else:
+            ldt = torch.as_strided(ld32, (h, t), (sh, sn))
+            cum = torch.cumsum(ldt.contiguous(), dim=1).t().contiguous()
+            ends = cu_dev[1:] - 1
+            total = cum.index_select(0, ends)
+            prev = torch.cat([torch.zeros(1, h, device=dev), total[:-1]])
+            # a segment's decay = cum at its end minus cum just before its start
+            starts = cu_dev[:-1]
+            before = torch.where((starts > 0).view(-1, 1), cum.index_select(0, (starts - 1).clamp(min=0)),
+                                 torch.zeros(1, h, device=dev))
+            seg_decay = total - before
+            del prev
+        s_in = torch.empty(nseg, h, d, e, dtype=torch.float32, device=dev)
+        rc = lib.la_seqpar_fold_segments(_lib.ptr(st), _lib.ptr(seg_decay.contiguous()), _lib.ptr(tab_all),
+                                         _lib.ptr(s_in), nseg, h, d, e, stream)
+        _lib.check(rc, "la_seqpar_fold_segments")
+        if cont:
+            s_in_cont = s_in.index_select(0, torch.tensor(cont, dtype=torch.int64).to(dev, non_blocking=True))
+            rc = lib.la_seqpar_correct_multi(_lib.ptr(q), _lib.ptr(o), _lib.ptr(cum), _lib.ptr(s_in_cont),
+                                             _lib.ptr(tab_cont), len(cont), tiles, t, h, d, e,
+                                             _lib.dtype_code(q), stream)
+            _lib.check(rc, "la_seqpar_correct_multi")
+    final = st.index_select(0, torch.tensor(last_of_doc, dtype=torch.int64).to(dev, non_blocking=True))
+    return o, final

@@ -69,7 +69,20 @@ def _ld_local(ld: torch.Tensor, t: int, h: int) -> torch.Tensor:
 
 
 def _cuda_local_forward(q, k, v, ld, local_cu):
-    from .scalar_decay import lasd_fn
+    from . import segmented as sg
+    from .scalar_decay import _prep_ld, lasd_fn
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    bounds = [(local_cu[i], local_cu[i + 1]) for i in range(len(local_cu) - 1)]
+    cap = sg.auto_cap(t, h)
+    lib = _lib.load()
+    if (q.is_cuda and lib.la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1
+            and sg.worth_segmenting(bounds, h, cap)):
+        # few long documents on this rank: cut them further so that every SM has a segment
+        ld32, strides = _prep_ld(ld, 1, t, h)
+        with torch.no_grad():
+            return sg.lasd_forward_segmented(q.contiguous(), k.contiguous(), v.contiguous(), ld32, strides,
+                                             None, bounds, cap)
     cu = torch.tensor(local_cu, dtype=torch.int64, device=q.device)
     with torch.no_grad():
         return lasd_fn(q, k, v, ld, cu_seqlens=cu)
