@@ -66,7 +66,8 @@ LA_API int la_debug_lavd_unsafe(void *stream, int *flag_out);
 
 /* Phase tracing of the chunk kernel (no counterpart in the reference): while buf is non-NULL,
  * every chunk pass writes clock64() stamps of CTA 0, threads 0 and 32, at 15 phase boundaries
- * per chunk into buf (device memory, 2 x 4096 x 16 int64).  NULL switches it off. */
+ * per chunk into buf (device memory, 2 x 4096 x 16 int64).  NULL switches it off.  The stamps are
+ * compiled in only when the library is built with -DLA_CHUNK_TRACE; otherwise this is a no-op. */
 LA_API int la_debug_chunk_trace(void *buf);
 
 /* Self-test of the tensor-core building blocks (no counterpart in the reference): one

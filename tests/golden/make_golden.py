@@ -1,8 +1,9 @@
 """Generate the golden vectors under tests/golden/ from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference, or pass its path):
+Run where a checkout of the reference project (Doraemonzzz/xopes) is available and pass its path
+(or set XOPES_REFERENCE_ROOT):
 
-    python tests/golden/make_golden.py [reference_root]
+    python tests/golden/make_golden.py <reference_root>
 
 The reference's torch operators are loaded BY FILE PATH (importing the `xopes` package needs a
 GPU because it queries the Triton driver at import time).  For every case this script
@@ -152,7 +153,9 @@ def lavd_case(ref, name, seed, b, n, h, d, e, use_ldv, use_init, use_dfinal, sha
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XOPES_REFERENCE_ROOT")
+    if not ref_root:
+        raise SystemExit("usage: make_golden.py <path to a checkout of Doraemonzzz/xopes>")
     lasd = load(ref_root, "xopes/ops/lightning_attn/scalar_decay/lasd_torch.py", "ref_lasd_torch")
     lavd = load(ref_root, "xopes/ops/lightning_attn/vector_decay/lavd_torch.py", "ref_lavd_torch")
     torch.set_num_threads(max(1, os.cpu_count() or 1))

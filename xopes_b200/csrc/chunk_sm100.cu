@@ -725,11 +725,13 @@ int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
   if (a.status == nullptr) return LA_ERR_CUDA;
   a.trace = g_trace;
   auto kern = chunk_pass_kernel<T>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};  // the attribute is per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LA_ERR_CUDA;
+  if (!attr_set[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return LA_ERR_CUDA;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   const int nb = p.cu ? p.M : p.B;
   kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, mo, a);
