@@ -340,7 +340,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
         lens = W.varlen_doc_lengths(cfg["N"], cfg["docs"], 0)
         cu = [0] + [int(x) for x in torch.cumsum(lens, 0)]
         # sample: the shortest document and as many leading documents as fit ~24K tokens
-        picks, budget = [int(torch.argmin(lens))], 24000
+        picks, budget = [int(torch.argmin(lens))], 200000
         for i in range(cfg["docs"]):
             if i not in picks and int(lens[i]) <= budget:
                 picks.append(i)
@@ -358,7 +358,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
                   f"{dt:.1f} s; documents are independent, cost is linear in tokens")
         return val, sample, threads
     if name == "C2":
-        bs, hs, n = 2, 32, cfg["N"]
+        bs, hs, n = cfg["B"], cfg["H"], cfg["N"]  # the whole configuration (about 10-15 s on 16 cores)
         w = W.lasd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
         f = {k: v.float() for k, v in w.items()}
         ld = f["ld"]
@@ -371,7 +371,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
         sample = (f"oracle lasd fwd+bwd on a (B={bs},H={hs},N={n}) slice, {dt:.1f} s; scaled by "
                   f"B*H/{bs * hs}={scale:.0f} (independent (b,h) recurrences)")
     elif name == "C3":
-        bs, hs, n = 1, 2, 4096
+        bs, hs, n = cfg["B"], cfg["H"], 4096
         w = W.lavd_inputs(bs, n, hs, cfg["D"], cfg["E"], torch.bfloat16, seed)
         f = {k: v.float() for k, v in w.items()}
         t0 = time.perf_counter()
@@ -383,7 +383,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
         sample = (f"oracle lavd fwd+bwd on a (B={bs},H={hs},N={n}) slice, {dt:.1f} s; scaled by "
                   f"{scale:.0f} (pairs x sequence length; cost is linear in N)")
     else:  # C4
-        steps = 8
+        steps = cfg["steps"]
         w = W.decode_inputs(cfg["B"], cfg["H"], cfg["D"], cfg["E"], steps, False, seed=seed)
         st = w["state"]
         t0 = time.perf_counter()
