@@ -3,6 +3,8 @@ C ABI) against the committed reference vectors and against the CPU oracle on see
 
 Tolerances: relative L2 <= 1e-5 for fp32 outputs, <= 1e-2 for 16-bit outputs, gradients and
 final states."""
+import ctypes
+
 import pytest
 import torch
 
@@ -315,6 +317,49 @@ def test_lasd_varlen_documents_are_independent(dtype, tol):
     assert_close("dv", rv, v.grad.float(), tol)
     assert_close("dld", rld, ldc.grad, dld_tol(dtype, tol))
     assert_close("dinitial_state", rs0, s0c.grad, tol)
+
+
+@pytest.mark.parametrize("shape", [(5, 400, 32, 128, 128), (3, 513, 30, 128, 128), (40, 256, 4, 128, 128)])
+def test_lasd_more_pairs_than_sms(shape):
+    """More (sequence, head) pairs than SMs: the chunk passes split the chunk space evenly over
+    one CTA per SM and hand the running state of a cut sequence from one CTA to the next; with
+    more than half as many, the merged dk/dv launch does."""
+    import xopes_b200 as xb
+    _run_lasd_case(xb.lasd_fn, *shape, seed=11, dtype=torch.bfloat16, use_state=True, use_dfinal=True,
+                   weak_decay=False, tol=TOL_BF16)
+
+
+@pytest.mark.parametrize("want_dld", [False, True])
+def test_lasd_varlen_many_documents(want_dld):
+    """Ragged documents (empty, one token, several times a CTA's share of the chunk space) with
+    more (document, head) pairs than SMs."""
+    import xopes_b200 as xb
+    g = torch.Generator().manual_seed(21)
+    lens = [3000, 0, 1, 128] + [int(x) for x in torch.randint(0, 400, (44,), generator=g)] + [0, 700]
+    n, h, d, e = sum(lens), 4, 128, 128
+    dtype = torch.bfloat16
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    qf, kf, vf, ld, _, dof, _ = _lasd_seeded(1, n, h, d, e, 5, dtype, False, False, False)
+    s0 = 0.1 * torch.randn(len(lens), h, d, e, generator=g)
+    dsf = torch.randn(len(lens), h, d, e, generator=g)
+    q, k, v, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(s0)
+    ldc = leaf(ld) if want_dld else ld.to(DEV)
+    o, sf = xb.lasd_fn(q, k, v, ldc, initial_state=s0c, cu_seqlens=cu.to(DEV))
+    ro, rsf = orc.lasd_forward(qf, kf, vf, ld, s0, cu)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rld, rs0 = orc.lasd_backward(qf, kf, vf, ld, dof, s0, dsf, cu)
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    if want_dld:
+        assert_close("dld", rld, ldc.grad, dld_tol(dtype, TOL_BF16))
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+    st = ctypes.c_int(-1)
+    lib = xb._lib.load()
+    assert lib.la_device_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(st)) == 0
+    assert st.value == 0, f"a bounded wait ran out (code {st.value})"
 
 
 # ------------------------------------------------------------------------------------------------

@@ -182,12 +182,13 @@ int64_t la_lasd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, 
   return ((int64_t)2 * nt * B * N * H + nb * H * D * E) * (int64_t)sizeof(float);
 }
 
-int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
-                int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
-                const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
-                void *dv, float *dld, float *dinitial_state, void *workspace,
-                int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
-                int64_t M, int dtype, unsigned flags, void *stream) {
+// no_scratch: the chunk passes may not take hand-off scratch from the library's pool
+static int lasd_bwd_impl(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                         int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
+                         const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
+                         void *dv, float *dld, float *dinitial_state, void *workspace,
+                         int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                         int64_t M, int dtype, unsigned flags, void *stream, int no_scratch) {
   int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc != LA_OK) return rc;
   if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr || ld == nullptr)
@@ -213,7 +214,7 @@ int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, in
   if (path == 1) {
     ChunkPass c;
     c.ld = ld; c.ld_sb = ld_sb; c.ld_sn = ld_sn; c.ld_sh = ld_sh;
-    c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens;
+    c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.no_scratch = no_scratch;
     // dq: (X,Y,Z) = (do, v, k), state S^T, forward direction
     c.x = d_o; c.y = v; c.z = k; c.out = dq; c.t0 = initial_state; c.state_transposed = 1;
     c.tfinal = state_term ? ws_state : nullptr; c.reverse = 0;
@@ -223,11 +224,12 @@ int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, in
     c.x = v; c.y = d_o; c.z = q; c.out = dk; c.t0 = dfinal_state; c.state_transposed = 1;
     c.tfinal = nullptr; c.reverse = 1;
     c.xrow = want_dld ? k : nullptr; c.rowdot = slots_k;
-    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
-    // dv: (k, q, do), state dS, reverse direction; its end state is d initial_state
-    c.x = k; c.y = q; c.z = d_o; c.out = dv; c.t0 = dfinal_state; c.state_transposed = 0;
-    c.tfinal = dinitial_state; c.reverse = 1; c.xrow = nullptr; c.rowdot = nullptr;
-    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
+    // dv: (k, q, do), state dS, reverse direction; its end state is d initial_state.  Both walk
+    // the tokens last to first and both read q and do: one launch, neighbouring CTAs.
+    ChunkPass c2 = c;
+    c2.x = k; c2.y = q; c2.z = d_o; c2.out = dv; c2.t0 = dfinal_state; c2.state_transposed = 0;
+    c2.tfinal = dinitial_state; c2.reverse = 1; c2.xrow = nullptr; c2.rowdot = nullptr;
+    if ((rc = launch_chunk_pass_pair(c, c2, dtype, st)) != LA_OK) return rc;
   } else {
     // dq: T = S (rows D): a = k, b = v, w = do
     ScanParams p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
@@ -256,6 +258,17 @@ int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, in
     if (rc != LA_OK) return rc;
   }
   return LA_OK;
+}
+
+int la_lasd_bwd(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
+                int64_t ld_sn, int64_t ld_sh, const float *initial_state, const void *d_o,
+                const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
+                void *dv, float *dld, float *dinitial_state, void *workspace,
+                int64_t workspace_bytes, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                int64_t M, int dtype, unsigned flags, void *stream) {
+  return lasd_bwd_impl(q, k, v, ld, ld_sb, ld_sn, ld_sh, initial_state, d_o, dfinal_state, cu_seqlens, dq, dk,
+                       dv, dld, dinitial_state, workspace, workspace_bytes, B, N, H, D, E, M, dtype, flags,
+                       stream, 0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -290,9 +303,9 @@ int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, const float
   if (scratch == nullptr) return LA_ERR_CUDA;
   // Nothing in the scratch has to start at zero: the row-dot slots and the recomputed final state
   // are written in full by the dq / dk passes of this call before the reduction reads them.
-  return la_lasd_bwd(q, k, v, ld, ld_sb, ld_sn, ld_sh, initial_state, d_o, dfinal_state, cu_seqlens, dq,
-                     dk, dv, dld, dinitial_state, scratch, (int64_t)LA_NOALLOC_SCRATCH_BYTES, B, N, H, D, E,
-                     M, dtype, flags, stream);
+  return lasd_bwd_impl(q, k, v, ld, ld_sb, ld_sn, ld_sh, initial_state, d_o, dfinal_state, cu_seqlens, dq,
+                       dk, dv, dld, dinitial_state, scratch, (int64_t)LA_NOALLOC_SCRATCH_BYTES, B, N, H, D, E,
+                       M, dtype, flags, stream, 1);
 }
 
 // ------------------------------------------------------------------------------------------------

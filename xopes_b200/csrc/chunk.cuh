@@ -27,10 +27,17 @@ struct ChunkPass {
   int reverse = 0;
   const int64_t *cu = nullptr;
   int B = 0, N = 0, H = 0, M = 0;
+  int no_scratch = 0;  // 1: never take hand-off scratch from the library's pool (one CTA per pair)
 };
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype);
+// With more (sequence, head) pairs than SMs the launch runs one CTA per SM on an even split of
+// the chunk space; the running state of a pair cut by a split crosses through scratch taken from
+// a stream-ordered pool the library owns (and returned to it in stream order).
 int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream);
+// Two passes over the same tokens in one launch (even CTAs: p, odd CTAs: q), so that operand
+// tiles both passes read are fetched from HBM once.  Sizes and cu_seqlens must be the same.
+int launch_chunk_pass_pair(const ChunkPass &p, const ChunkPass &q, int dtype, cudaStream_t stream);
 // One directional vector-decay (ldk) pass on tcgen05 (lavd_chunk_sm100.cu).  tmode = 0: the decay
 // acts on the contraction dimension of X Y^T (o and dv passes); tmode = 1: on the output dimension
 // (dq and dk passes, state transposed), with the optional log-decay-gradient accumulation

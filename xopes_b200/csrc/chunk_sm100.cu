@@ -20,14 +20,18 @@
 #include <cuda.h>
 
 #include <cstddef>
+#include <cstdlib>
+#include <mutex>
 
 #include "chunk.cuh"
 #include "sm100_ptx.cuh"
+#include "tile_common.cuh"
 
 namespace la {
 namespace {
 
 using namespace ptx;
+using namespace tile;
 
 constexpr int kChunk = 128;
 constexpr int kTileBytes = 32768;  // [128][128] 16-bit = two TMA boxes of [128][64]
@@ -68,6 +72,7 @@ struct Small {
   int abort_flag;
   int issued;
   int pad;
+  int rg[4];                  // this CTA's range of the chunk space (Range), written once at start
   alignas(16) float wsum[4];
   alignas(16) float cs[kChunk];   // inclusive cumulative log2 decay of each row of the chunk
   alignas(16) float bs[kChunk];   // per-column factor of the factorised decay mask (read as float4)
@@ -92,52 +97,132 @@ struct ChunkArgs {
   long long *trace;  // optional: clock64() at phase boundaries of CTA 0 (threads 0 and 32)
 };
 
+// How the (sequence, head) pairs of a launch are spread over its CTAs.
+//
+// balanced = 0: CTA r owns pair r whole.
+// balanced = 1: every pair is a run of w = max(chunks, 1) units in processing order; the pairs'
+//   runs are laid end to end (pair = sequence * H + head) and CTA r of R owns units
+//   [total r / R, total (r+1) / R).  A pair cut by a boundary is worked on by two neighbouring
+//   CTAs: the one that owns its first part publishes the running state to its hand-off slot, the
+//   one that owns the rest picks it up there.  A CTA works on the part it publishes first and on
+//   the part it has to wait for last, so with pairs shorter than a CTA's share nobody waits.
+// npass = 2: two passes over the same tokens share the launch (even CTAs run pass 0, odd CTAs
+//   pass 1, both on range blockIdx.x / 2), so that the operand tiles they have in common are
+//   fetched from HBM once and found in L2 by the other.
+struct Sched {
+  int balanced, npass;
+  long long total;           // sum of w over all pairs (fixed-length launches; else H * wprefix[M])
+  const long long *wprefix;  // cu_seqlens launches: exclusive prefix sum of w over sequences (M + 1)
+  float *handoff;            // [gridDim.x][128 * 128] fp32, element (i, c) of T at c * 128 + i
+  int *flags;                // [gridDim.x], zero before the launch; 1 = slot written
+};
+
+struct Launch {
+  ChunkArgs a[2];
+  Sched sc;
+};
+struct PassMaps {
+  CUtensorMap x, y, z, o;
+};
+struct Maps {
+  PassMaps p[2];
+};
+
+constexpr int kStHandoff = 112;
+
+// first and last pair of a CTA's range, chunk offset inside the first, end offset inside the last
+struct Range {
+  int p_a, p_b, off_a, end_b;
+};
+struct Task {
+  int seq, h, bidx;
+  long long t_begin;
+  int len, nc;   // tokens and chunks of the whole sequence
+  int it0, cnt;  // this task covers processing steps [it0, it0 + cnt) of the sequence
+  bool waits, publishes;
+};
+
+__device__ __forceinline__ void locate(const ChunkArgs &a, const Sched &sc, long long x, int &p, int &off) {
+  if (a.cu == nullptr) {
+    const int w = (a.N + kChunk - 1) / kChunk;
+    p = (int)(x / w);
+    off = (int)(x - (long long)p * w);
+    return;
+  }
+  int lo = 0, hi = a.M - 1;  // largest seq with H * wprefix[seq] <= x
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if ((long long)a.H * sc.wprefix[mid] <= x) lo = mid; else hi = mid - 1;
+  }
+  const long long rem = x - (long long)a.H * sc.wprefix[lo];
+  const long long w = sc.wprefix[lo + 1] - sc.wprefix[lo];
+  const int h = (int)(rem / w);
+  p = lo * a.H + h;
+  off = (int)(rem - (long long)h * w);
+}
+
+__device__ __forceinline__ Range cta_range(const ChunkArgs &a, const Sched &sc, int r, int R) {
+  Range g;
+  if (!sc.balanced) {
+    g.p_a = g.p_b = r;
+    g.off_a = 0;
+    g.end_b = 0x7fffffff;
+    return g;
+  }
+  const long long total = a.cu != nullptr ? (long long)a.H * sc.wprefix[a.M] : sc.total;
+  const long long lo = total * r / R, hi = total * (r + 1) / R;
+  locate(a, sc, lo, g.p_a, g.off_a);
+  locate(a, sc, hi - 1, g.p_b, g.end_b);
+  g.end_b += 1;
+  return g;
+}
+
+__device__ __forceinline__ Task task_of(const ChunkArgs &a, const Range &g, int k, int ntasks) {
+  Task t;
+  const int p = (ntasks == 1) ? g.p_a : (k == 0 ? g.p_b : (k == ntasks - 1 ? g.p_a : g.p_a + k));
+  t.seq = p / a.H;
+  t.h = p - t.seq * a.H;
+  if (a.cu != nullptr) {
+    t.t_begin = a.cu[t.seq];
+    t.len = (int)(a.cu[t.seq + 1] - t.t_begin);
+    t.bidx = 0;
+  } else {
+    t.t_begin = 0;
+    t.len = a.N;
+    t.bidx = t.seq;
+  }
+  t.nc = (t.len + kChunk - 1) / kChunk;
+  const int w = max(t.nc, 1);
+  t.it0 = (p == g.p_a) ? g.off_a : 0;
+  const int it1 = (p == g.p_b) ? min(g.end_b, w) : w;
+  t.waits = t.it0 > 0;
+  t.publishes = it1 < w;
+  t.cnt = min(it1, t.nc) - t.it0;
+  return t;
+}
+
+__device__ __forceinline__ int ld_acquire(const int *p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int *p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // trace[thread slot][chunk][point]: 16 points per chunk, 2 thread slots of 4096 chunks at most
 #ifdef LA_CHUNK_TRACE
 #define LA_TRACE(point)                                                                   \
   do {                                                                                    \
-    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32) && it < 4096)      \
-      a.trace[((tid >> 5) * 4096 + it) * 16 + (point)] = clock64();                       \
+    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32) && gi < 4096)      \
+      a.trace[((tid >> 5) * 4096 + gi) * 16 + (point)] = clock64();                       \
   } while (0)
 #else
 #define LA_TRACE(point) do { } while (0)
 #endif
 
-template <typename T> struct Fmt;
-template <> struct Fmt<__nv_bfloat16> {
-  static constexpr uint32_t kAB = 1;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-  }
-  static __device__ __forceinline__ float2 unpack(uint32_t u) {
-    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
-  }
-};
-template <> struct Fmt<__half> {
-  static constexpr uint32_t kAB = 0;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-  }
-  static __device__ __forceinline__ float2 unpack(uint32_t u) {
-    return __half22float2(*reinterpret_cast<__half2 *>(&u));
-  }
-};
-
 // byte offset of the k-th 16-element slice of a K-major [128][128] tile (two boxes of 64 columns)
 __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
-
-// two fp32 lanes per instruction (sm_100 packed fp32 pipe)
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) { return make_float2(__uint_as_float(lo), __uint_as_float(hi)); }
-
-__device__ __forceinline__ float ex2(float x) {  // 2^x, single MUFU
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // Thread layout of the compute warps: warpgroup wg = warp / 4 owns columns [64 wg, 64 wg + 64) of
 // every 128-column row, quadrant q4 = warp % 4 owns rows (= tensor-memory lanes) [32 q4, 32 q4 + 32).
@@ -147,11 +232,13 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x, single MUFU
 // batch that lies wholly on the allowed side of the diagonal the weight factorises as
 // A_i(batch) * B_j with both exponents <= 0 (reference point: the batch edge nearest the diagonal),
 // so only the diagonal batch pays one exponential per element.
+//
+// Every role walks the CTA's tasks in the same order and numbers the chunks it has handled with
+// one running counter; pipeline stages and mbarrier parities follow that counter, so the
+// pipeline never drains between tasks.
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_o,
-                  const ChunkArgs a) {
+chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Launch lp) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -159,16 +246,22 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   Small *sm = reinterpret_cast<Small *>(gbase + kOffSmall);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int seq = blockIdx.x / a.H, h = blockIdx.x - seq * a.H;
-  long long t_begin = 0, t_end = a.N;
-  int bidx = seq;
-  if (a.cu != nullptr) {
-    t_begin = a.cu[seq];
-    t_end = a.cu[seq + 1];
-    bidx = 0;
-  }
-  const int len = (int)(t_end - t_begin);
-  const int nc = (len + kChunk - 1) / kChunk;
+  // Arguments both passes of a merged launch share (sizes, strides, decay, direction) are read
+  // from slot 0 as direct constant-bank operands; only the few that differ (`ap`: row-dot
+  // operand, output, states) are indexed by the pass, and none of those is touched per chunk
+  // unless a log-decay gradient was asked for.
+  const Sched &sc = lp.sc;
+  const int sh = sc.npass == 2 ? 1 : 0;
+  const int pass = (int)(blockIdx.x & (unsigned)sh);
+  const int r_cta = (int)(blockIdx.x >> sh), r_cnt = (int)(gridDim.x >> sh);
+  const ChunkArgs &a = lp.a[0];
+  const ChunkArgs &ap = lp.a[pass];
+  const CUtensorMap *map_x = &maps.p[pass].x, *map_y = &maps.p[pass].y, *map_z = &maps.p[pass].z,
+                    *map_o = &maps.p[pass].o;
+  // The range lives in shared memory and every role re-reads it per task: it must not occupy
+  // registers across the chunk loop of the compute warps.
+  volatile int *rg_s = sm->rg;
+  auto range = [&]() -> Range { return Range{rg_s[0], rg_s[1], rg_s[2], rg_s[3]}; };
   const bool rev = a.reverse != 0;
 
   const uint32_t bar_full = smem_u32(&sm->full[0]), bar_empty = smem_u32(&sm->empty[0]);
@@ -179,7 +272,7 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   // With a log-decay gradient requested the 16-bit state copy is split into a high and a low
   // half (two passes of X T_in over the same buffer): the gradient is a long cumulative sum of
   // nearly cancelling terms and the rounding of a single 16-bit copy dominates its error.
-  const bool split = a.rowdot != nullptr;
+  const bool split = ap.rowdot != nullptr;
   volatile int *abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -198,6 +291,8 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     mbar_init(bar_h, kComputeThreads);
     sm->abort_flag = 0;
     sm->issued = 0;
+    const Range g = cta_range(a, sc, r_cta, r_cnt);
+    sm->rg[0] = g.p_a; sm->rg[1] = g.p_b; sm->rg[2] = g.off_a; sm->rg[3] = g.end_b;
     fence_barrier_init();
   }
   if (warp == kProducerWarp) {
@@ -208,32 +303,39 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
+  const int ntasks = rg_s[1] - rg_s[0] + 1;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA loads
     if (lane == 0) {
-      prefetch_tmap(&map_x);
-      prefetch_tmap(&map_y);
-      prefetch_tmap(&map_z);
-      int it = 0;
-      for (; it < nc; ++it) {
-        const int n = rev ? (nc - 1 - it) : it;
-        const int s = it & 1;
-        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
-        mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
-        if (*abort_flag) break;
-        const uint32_t fb = bar_full + 8 * s;
-        mbar_arrive_expect_tx(fb, 3 * kTileBytes);
-        const uint32_t dst = base + (uint32_t)s * kStageBytes;
-        const int tok0 = (int)t_begin + n * kChunk;
-        tma_load_4d(dst, &map_x, fb, 0, h, tok0, bidx);
-        tma_load_4d(dst + kBoxBytes, &map_x, fb, 64, h, tok0, bidx);
-        tma_load_4d(dst + kTileBytes, &map_y, fb, 0, h, tok0, bidx);
-        tma_load_4d(dst + kTileBytes + kBoxBytes, &map_y, fb, 64, h, tok0, bidx);
-        tma_load_4d(dst + 2 * kTileBytes, &map_z, fb, 0, h, tok0, bidx);
-        tma_load_4d(dst + 2 * kTileBytes + kBoxBytes, &map_z, fb, 64, h, tok0, bidx);
+      prefetch_tmap(map_x);
+      prefetch_tmap(map_y);
+      prefetch_tmap(map_z);
+      int g0 = 0;
+      for (int k = 0; k < ntasks && !*abort_flag; ++k) {
+        const Task tk = task_of(a, range(), k, ntasks);
+        int it = 0;
+        for (; it < tk.cnt; ++it) {
+          const int gi = g0 + it;
+          const int n = rev ? (tk.nc - 1 - (tk.it0 + it)) : (tk.it0 + it);
+          const int s = gi & 1;
+          const uint32_t ph = (uint32_t)(gi >> 1) & 1u;
+          mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
+          if (*abort_flag) break;
+          const uint32_t fb = bar_full + 8 * s;
+          mbar_arrive_expect_tx(fb, 3 * kTileBytes);
+          const uint32_t dst = base + (uint32_t)s * kStageBytes;
+          const int tok0 = (int)tk.t_begin + n * kChunk;
+          tma_load_4d(dst, map_x, fb, 0, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + kBoxBytes, map_x, fb, 64, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + kTileBytes, map_y, fb, 0, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + kTileBytes + kBoxBytes, map_y, fb, 64, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + 2 * kTileBytes, map_z, fb, 0, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + 2 * kTileBytes + kBoxBytes, map_z, fb, 64, tk.h, tok0, tk.bidx);
+        }
+        g0 += it;
       }
-      sm->issued = it;
+      sm->issued = g0;
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
@@ -243,79 +345,91 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
       const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
       const uint64_t d_tb = desc_mnmajor(base + kOffTb, kBoxBytes);
-      for (int it = 0; it < nc; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
-        const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
-        const uint64_t d_xk = desc_kmajor(xs), d_yk = desc_kmajor(ys);
-        const uint64_t d_ymn = desc_mnmajor(ys, kBoxBytes), d_zmn = desc_mnmajor(zs, kBoxBytes);
-        // descriptor advance per 16-element K slice, in 16-byte units: K-major tiles step 32 B
-        // inside a 128 B row and jump to the second box after 4 slices; MN-major tiles step 16 rows
-        mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
-          mma_ss(tmem + kColP, d_xk + ko, d_yk + ko, idesc_kk, ks > 0);
-        }
-        mma_commit(bar_p);
-        // W2 = X T_in: needs the state copy of this chunk and the previous epilogue's reads of W2
-        mbar_wait(bar_d, par, abort_flag, a.status, kStD);
-        if (it > 0) mbar_wait(bar_h, par ^ 1u, abort_flag, a.status, kStH);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
-          mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
-        }
-        if (split) {
-          mma_commit(bar_x);  // the compute warps may now overwrite the copy with its low half
-          mbar_wait(bar_l, par, abort_flag, a.status, kStL);
+      int g0 = 0;
+      for (int k = 0; k < ntasks; ++k) {
+        const Task tk = task_of(a, range(), k, ntasks);
+        for (int it = 0; it < tk.cnt; ++it) {
+          const int gi = g0 + it;
+          const int s = gi & 1;
+          const uint32_t ph = (uint32_t)(gi >> 1) & 1u, par = (uint32_t)gi & 1u;
+          const uint32_t xs = base + (uint32_t)s * kStageBytes, ys = xs + kTileBytes, zs = ys + kTileBytes;
+          const uint64_t d_xk = desc_kmajor(xs), d_yk = desc_kmajor(ys);
+          const uint64_t d_ymn = desc_mnmajor(ys, kBoxBytes), d_zmn = desc_mnmajor(zs, kBoxBytes);
+          // descriptor advance per 16-element K slice, in 16-byte units: K-major tiles step 32 B
+          // inside a 128 B row and jump to the second box after 4 slices; MN-major tiles step 16 rows
+          mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
-            mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, 1);
+            mma_ss(tmem + kColP, d_xk + ko, d_yk + ko, idesc_kk, ks > 0);
           }
+          mma_commit(bar_p);
+          // W2 = X T_in: needs the state copy of this chunk and the previous epilogue's reads of W2
+          mbar_wait(bar_d, par, abort_flag, a.status, kStD);
+          if (gi > 0) mbar_wait(bar_h, par ^ 1u, abort_flag, a.status, kStH);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+            mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
+          }
+          if (split) {
+            mma_commit(bar_x);  // the compute warps may now overwrite the copy with its low half
+            mbar_wait(bar_l, par, abort_flag, a.status, kStL);
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
+              mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, 1);
+            }
+          }
+          // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
+          // next chunk's state copy while P~ Z still runs
+          mbar_wait(bar_y, par, abort_flag, a.status, kStY);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+          mma_commit(bar_t);
+          mbar_wait(bar_f, par, abort_flag, a.status, kStF);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
+                   idesc_kmn, ks > 0);
+          mma_commit(bar_w);
+          // the next chunk's X Y^T overwrites P, which the product above reads as P~
+          mbar_wait(bar_w, par, abort_flag, a.status, kStW);
         }
-        // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
-        // next chunk's state copy while P~ Z still runs
-        mbar_wait(bar_y, par, abort_flag, a.status, kStY);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
-        mma_commit(bar_t);
-        mbar_wait(bar_f, par, abort_flag, a.status, kStF);
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
-                 idesc_kmn, ks > 0);
-        mma_commit(bar_w);
-        // the next chunk's X Y^T overwrites P, which the product above reads as P~
-        mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+        g0 += tk.cnt;
       }
     }
     __syncwarp();
   } else if (warp == kStoreWarp) {
     // ------------------------------------------------------------------ TMA stores
     if (lane == 0) {
-      for (int it = 0; it < nc; ++it) {
-        const int n = rev ? (nc - 1 - it) : it;
-        const int s = it & 1;
-        const uint32_t par = (uint32_t)it & 1u;
-        const int L = min(kChunk, len - n * kChunk);
-        mbar_wait(bar_h, par, abort_flag, a.status, kStH);
-        if (L == kChunk) {
-          const uint32_t xs = base + (uint32_t)s * kStageBytes;
-          const int tok0 = (int)t_begin + n * kChunk;
-          tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
-          tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
-          tma_store_commit();
-          tma_store_wait_read();
+      int g0 = 0;
+      for (int k = 0; k < ntasks; ++k) {
+        const Task tk = task_of(a, range(), k, ntasks);
+        for (int it = 0; it < tk.cnt; ++it) {
+          const int gi = g0 + it;
+          const int n = rev ? (tk.nc - 1 - (tk.it0 + it)) : (tk.it0 + it);
+          const int s = gi & 1;
+          const uint32_t par = (uint32_t)gi & 1u;
+          const int L = min(kChunk, tk.len - n * kChunk);
+          mbar_wait(bar_h, par, abort_flag, a.status, kStH);
+          if (L == kChunk) {
+            const uint32_t xs = base + (uint32_t)s * kStageBytes;
+            const int tok0 = (int)tk.t_begin + n * kChunk;
+            tma_store_4d(map_o, xs, 0, tk.h, tok0, tk.bidx);
+            tma_store_4d(map_o, xs + kBoxBytes, 64, tk.h, tok0, tk.bidx);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+          mbar_arrive(bar_empty + 8 * s);
         }
-        mbar_arrive(bar_empty + 8 * s);
+        g0 += tk.cnt;
       }
       tma_store_wait_all();
     }
@@ -325,44 +439,31 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int wg = warp >> 2, q4 = warp & 3;
     const int i = q4 * 32 + lane;  // row of every 128-row tile this thread works on
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
-    const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
+    // per-task quantities (kept few: they stay live across the chunk loop)
+    int n_first = 0, t_len = 0, t_cnt = 0;  // first chunk index, tokens of the sequence, chunks of the task
+    const float *ld_row = a.ld;             // &ld[b, t_begin + i, h]
+    long long row_base = 0;                 // element offset of row (b, t_begin + i, h, 0)
 
-    // starting state -> tensor memory (this warpgroup's 64 columns)
-    for (int b2 = 0; b2 < 2; ++b2) {
-      const int bt = 2 * wg + b2;
-      uint32_t r[32];
-#pragma unroll
-      for (int k = 0; k < 32; ++k) {
-        const int c = bt * 32 + k;
-        float v = 0.f;
-        if (a.t0 != nullptr) v = a.t0[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))];
-        r[k] = __float_as_uint(v);
-      }
-      tmem_st32(tl + kColT + bt * 32, r);
-    }
-    tmem_wait_st();
-
+    auto chunk_of = [&](int it) -> int { return rev ? n_first - it : n_first + it; };
     auto load_ld = [&](int it) -> float {
-      if (it >= nc) return 0.f;
-      const int n = rev ? (nc - 1 - it) : it;
-      const int L = min(kChunk, len - n * kChunk);
-      if (i >= L) return 0.f;
-      const long long tok = t_begin + (long long)n * kChunk + i;
-      return a.ld[bidx * a.ld_sb + tok * a.ld_sn + h * a.ld_sh] * kLog2e;
+      if (it >= t_cnt) return 0.f;
+      const int n = chunk_of(it);
+      if (i >= t_len - n * kChunk) return 0.f;
+      return ld_row[(long long)n * kChunk * a.ld_sn] * kLog2e;
     };
 
     // Per-chunk decay quantities of this thread's row.
     struct Decay {
-      float c;        // inclusive in-chunk cumulative log2 decay of row i
-      float wend[5];  // wend[b]: cumulative decay at the end of row batch b-1 (wend[4] = chunk total)
-      float eg, s, u; // e^g, output-row scale, Y-row scale
+      float c;         // inclusive in-chunk cumulative log2 decay of row i
+      float a0, a1;    // row factors of the factorised mask for this thread's two column batches
+      float eg, s, u;  // e^g, output-row scale, Y-row scale
     };
-    // A: cumulative decays of chunk `it`.  Contains a named barrier; cs/bs are overwritten only
-    // after it, i.e. after every thread has finished reading the previous chunk's values.
+    // A: cumulative decays of step `it` of the task.  Contains a named barrier; cs/bs are
+    // overwritten only after it, i.e. after every thread has finished reading the previous
+    // chunk's values.
     auto decay_of = [&](int it, float ldv) -> Decay {
       Decay d;
-      const int n = rev ? (nc - 1 - it) : it;
-      const int L = min(kChunk, len - n * kChunk);
+      const int L = t_len - chunk_of(it) * kChunk;  // rows >= L are padding
       float c = ldv;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -371,18 +472,29 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
       if (wg == 0 && lane == 31) sm->wsum[q4] = c;
       named_bar_sync(1, kComputeThreads);
-      d.wend[0] = 0.f;
+      // cumulative decay at the start (w_lo) / end (w_hi) of this thread's 32-row batch, over the
+      // chunk (g), and at the reference edge of its two column batches wg and wg + 2
+      const int e0 = rev ? wg : wg + 1, e1 = e0 + 2;
+      float w_lo = 0.f, w_hi = 0.f, g = 0.f, r0 = 0.f, r1 = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) d.wend[w + 1] = d.wend[w] + sm->wsum[w];
-      c += d.wend[q4];
-      const float g = d.wend[4];
+      for (int w = 0; w < 4; ++w) {
+        const float ws = sm->wsum[w];
+        g += ws;
+        if (w < q4) w_lo += ws;
+        if (w <= q4) w_hi += ws;
+        if (w < e0) r0 += ws;
+        if (w < e1) r1 += ws;
+      }
+      c += w_lo;
       d.c = c;
+      d.a0 = rev ? ex2(r0 - c) : ex2(c - r0);
+      d.a1 = rev ? ex2(r1 - c) : ex2(c - r1);
       d.eg = ex2(g);
       d.s = rev ? ex2(g - c) : ex2(c);
       d.u = (i < L) ? (rev ? ex2(c) : ex2(g - c)) : 0.f;
       if (wg == 0) {
         sm->cs[i] = c;
-        sm->bs[i] = rev ? ((i < L) ? ex2(c - d.wend[q4]) : 0.f) : ex2(d.wend[q4 + 1] - c);
+        sm->bs[i] = rev ? ((i < L) ? ex2(c - w_lo) : 0.f) : ex2(w_hi - c);
       }
       return d;
     };
@@ -392,14 +504,13 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     auto state_copy_low = [&](float eg, uint32_t par) {
       mbar_wait(bar_x, par, abort_flag, a.status, kStX);
       tc_fence_after();
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
-      tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
-      tmem_wait_ld();
       uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        uint32_t(&r)[32] = hf ? r1 : r0;
+      const float2 eg2 = make_float2(eg, eg);
+#pragma unroll 1
+      for (int hf = 0; hf < 2; ++hf) {  // 32 columns at a time keeps the register peak low
+        uint32_t r[32];
+        tmem_ld32(tl + kColT + (2 * wg + hf) * 32, r);
+        tmem_wait_ld();
 #pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint32_t w[4];
@@ -411,242 +522,292 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
           *reinterpret_cast<uint4 *>(box + sw128_offset(i, hf * 4 + pc)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-      }
-      const float2 eg2 = make_float2(eg, eg);
 #pragma unroll
-      for (int k = 0; k < 32; k += 2) {
-        const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
-        r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
-        r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
+        for (int k = 0; k < 32; k += 2) {
+          const float2 a0 = mul2(f2(r[k], r[k + 1]), eg2);
+          r[k] = __float_as_uint(a0.x); r[k + 1] = __float_as_uint(a0.y);
+        }
+        tmem_st32(tl + kColT + (2 * wg + hf) * 32, r);
       }
-      tmem_st32(tl + kColT + (2 * wg) * 32, r0);
-      tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_l);
     };
     auto state_copy = [&](float eg) {
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tl + kColT + (2 * wg) * 32, r0);
-      tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
-      tmem_wait_ld();
       uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
+      const float2 eg2 = make_float2(eg, eg);
+#pragma unroll 1
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t r[32];
+        tmem_ld32(tl + kColT + (2 * wg + hf) * 32, r);
+        tmem_wait_ld();
 #pragma unroll
-      for (int pc = 0; pc < 4; ++pc) {
-        uint4 v;
-        v.x = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 0]), __uint_as_float(r0[pc * 8 + 1]));
-        v.y = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 2]), __uint_as_float(r0[pc * 8 + 3]));
-        v.z = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 4]), __uint_as_float(r0[pc * 8 + 5]));
-        v.w = Fmt<T>::pack(__uint_as_float(r0[pc * 8 + 6]), __uint_as_float(r0[pc * 8 + 7]));
-        *reinterpret_cast<uint4 *>(box + sw128_offset(i, pc)) = v;
-      }
-#pragma unroll
-      for (int pc = 0; pc < 4; ++pc) {
-        uint4 v;
-        v.x = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 0]), __uint_as_float(r1[pc * 8 + 1]));
-        v.y = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 2]), __uint_as_float(r1[pc * 8 + 3]));
-        v.z = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 4]), __uint_as_float(r1[pc * 8 + 5]));
-        v.w = Fmt<T>::pack(__uint_as_float(r1[pc * 8 + 6]), __uint_as_float(r1[pc * 8 + 7]));
-        *reinterpret_cast<uint4 *>(box + sw128_offset(i, 4 + pc)) = v;
-      }
-      if (!split) {
-        const float2 eg2 = make_float2(eg, eg);
-#pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float2 a0 = mul2(f2(r0[k], r0[k + 1]), eg2), a1 = mul2(f2(r1[k], r1[k + 1]), eg2);
-          r0[k] = __float_as_uint(a0.x); r0[k + 1] = __float_as_uint(a0.y);
-          r1[k] = __float_as_uint(a1.x); r1[k + 1] = __float_as_uint(a1.y);
+        for (int pc = 0; pc < 4; ++pc) {
+          uint4 v;
+          v.x = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 0]), __uint_as_float(r[pc * 8 + 1]));
+          v.y = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 2]), __uint_as_float(r[pc * 8 + 3]));
+          v.z = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 4]), __uint_as_float(r[pc * 8 + 5]));
+          v.w = Fmt<T>::pack(__uint_as_float(r[pc * 8 + 6]), __uint_as_float(r[pc * 8 + 7]));
+          *reinterpret_cast<uint4 *>(box + sw128_offset(i, hf * 4 + pc)) = v;
         }
-        tmem_st32(tl + kColT + (2 * wg) * 32, r0);
-        tmem_st32(tl + kColT + (2 * wg + 1) * 32, r1);
-        tmem_wait_st();
+        if (!split) {
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            const float2 a0 = mul2(f2(r[k], r[k + 1]), eg2);
+            r[k] = __float_as_uint(a0.x); r[k + 1] = __float_as_uint(a0.y);
+          }
+          tmem_st32(tl + kColT + (2 * wg + hf) * 32, r);
+        }
       }
+      if (!split) tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_d);
     };
 
-    Decay cur{};
-    float ld_next = 0.f;
-    if (nc > 0) {
-      cur = decay_of(0, load_ld(0));
-      ld_next = load_ld(1);
-      state_copy(cur.eg);
-    }
-
-    for (int it = 0; it < nc; ++it) {
-      const int n = rev ? (nc - 1 - it) : it;
-      const int s = it & 1;
-      const uint32_t ph = (uint32_t)(it >> 1) & 1u, par = (uint32_t)it & 1u;
-      const int L = min(kChunk, len - n * kChunk);
-      const long long tok = t_begin + (long long)n * kChunk + i;
-      uint8_t *stage = gbase + (size_t)s * kStageBytes;
-      const float c_i = cur.c;
-
-      LA_TRACE(0);
-      if (split) state_copy_low(cur.eg, par);
-      // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
-      mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
-      mbar_wait(bar_p, par, abort_flag, a.status, kStP);
-      tc_fence_after();
-      LA_TRACE(1);
+    int g0 = 0;
+    for (int k = 0; k < ntasks; ++k) {
       {
-        uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
-        uint4 v[8];
-#pragma unroll
-        for (int pc = 0; pc < 8; ++pc) v[pc] = *reinterpret_cast<const uint4 *>(ybox + sw128_offset(i, pc));
-        const float2 u2 = make_float2(cur.u, cur.u);
-#pragma unroll
-        for (int pc = 0; pc < 8; ++pc) {
-          float2 f;
-          f = mul2(Fmt<T>::unpack(v[pc].x), u2); v[pc].x = Fmt<T>::pack(f.x, f.y);
-          f = mul2(Fmt<T>::unpack(v[pc].y), u2); v[pc].y = Fmt<T>::pack(f.x, f.y);
-          f = mul2(Fmt<T>::unpack(v[pc].z), u2); v[pc].z = Fmt<T>::pack(f.x, f.y);
-          f = mul2(Fmt<T>::unpack(v[pc].w), u2); v[pc].w = Fmt<T>::pack(f.x, f.y);
-        }
-#pragma unroll
-        for (int pc = 0; pc < 8; ++pc) *reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc)) = v[pc];
-      }
-      fence_proxy_async();
-      mbar_arrive(bar_y);
-      LA_TRACE(2);
+        const Task tk = task_of(a, range(), k, ntasks);
+        n_first = rev ? (tk.nc - 1 - tk.it0) : tk.it0;
+        t_len = tk.len;
+        t_cnt = tk.cnt;
+        ld_row = a.ld + tk.bidx * a.ld_sb + tk.h * a.ld_sh + (tk.t_begin + i) * a.ld_sn;
+        row_base = ((tk.bidx * (long long)a.N + tk.t_begin + i) * a.H + tk.h) * (long long)kChunk;
 
-      // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P)
-#pragma unroll 1
-      for (int b2 = 0; b2 < 2; ++b2) {
-        const int bt = wg + 2 * b2;  // batches {0,2} / {1,3}: balances the triangular work
-        uint32_t pk[16];
-        const bool dead = rev ? (bt < q4) : (bt > q4);  // warp-uniform
-        if (dead) {
-#pragma unroll
-          for (int k = 0; k < 16; ++k) pk[k] = 0u;
-        } else {
-          uint32_t r[32];
-          tmem_ld32(tl + kColP + bt * 32, r);
-          tmem_wait_ld();
-          if (bt != q4) {
-            const float ai = rev ? ex2(cur.wend[bt] - c_i) : ex2(c_i - cur.wend[bt + 1]);
-#pragma unroll
-            const float2 ai2 = make_float2(ai, ai);
-            for (int k = 0; k < 32; k += 4) {
-              const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + k]);
-              const float2 p0 = mul2(f2(r[k + 0], r[k + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
-              const float2 p1 = mul2(f2(r[k + 2], r[k + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
-              pk[(k >> 1) + 0] = Fmt<T>::pack(p0.x, p0.y);
-              pk[(k >> 1) + 1] = Fmt<T>::pack(p1.x, p1.y);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < 32; k += 2) {
-              const int j = bt * 32 + k;
-              const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
-              float m0, m1;
-              if (!rev) {
-                m0 = (j <= i) ? ex2(c_i - cj.x) : 0.f;
-                m1 = (j + 1 <= i) ? ex2(c_i - cj.y) : 0.f;
-              } else {
-                m0 = (j >= i && j < L) ? ex2(cj.x - c_i) : 0.f;
-                m1 = (j + 1 >= i && j + 1 < L) ? ex2(cj.y - c_i) : 0.f;
+        // starting state -> tensor memory (this warpgroup's 64 columns): the caller's state, or
+        // what the neighbouring CTA left in its hand-off slot
+        const float *src = nullptr;
+        bool src_tr = true;
+        if (tk.waits) {
+          if (tid == 0) {
+            const int *flag = sc.flags + (blockIdx.x - sc.npass);
+            uint32_t polls = 0;
+            while (ld_acquire(flag) == 0 && *abort_flag == 0) {
+              __nanosleep(200);
+              if (++polls > (1u << 22)) {
+                *abort_flag = 1;
+                atomicCAS(a.status, 0, kStHandoff);
               }
-              pk[k >> 1] = Fmt<T>::pack(__uint_as_float(r[k]) * m0, __uint_as_float(r[k + 1]) * m1);
             }
           }
+          named_bar_sync(3, kComputeThreads);
+          src = sc.handoff + (size_t)(blockIdx.x - sc.npass) * (kChunk * kChunk);
+        } else if (ap.t0 != nullptr) {
+          src = ap.t0 + ((long long)tk.seq * a.H + tk.h) * (long long)(kChunk * kChunk);
+          src_tr = ap.state_transposed != 0;
         }
-        tmem_st16(tl + kColP + bt * 32, pk);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_f);
-      LA_TRACE(3);
-
-      // ---- while the tensor cores finish this chunk: decays and state copy of the next one
-      Decay nxt{};
-      if (it + 1 < nc) {  // uniform over the CTA
-        nxt = decay_of(it + 1, ld_next);
-        ld_next = load_ld(it + 2);
-        LA_TRACE(4);
-        mbar_wait(bar_t, par, abort_flag, a.status, kStT);  // T holds this chunk's final state
-        tc_fence_after();
-        LA_TRACE(5);
-        state_copy(nxt.eg);
-      }
-      LA_TRACE(6);
-
-      // ---- epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
-      mbar_wait(bar_w, par, abort_flag, a.status, kStW);
-      tc_fence_after();
-      LA_TRACE(7);
-      const bool full_chunk = (L == kChunk);
-      const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
-      const float s_i = cur.s;
-      float rd = 0.f;
-#pragma unroll 1
-      for (int b2 = 0; b2 < 2; ++b2) {
-        const int bt = 2 * wg + b2;
-        uint32_t w1[32], w2[32];
-        tmem_ld32(tl + kColW1 + bt * 32, w1);
-        tmem_ld32(tl + kColW2 + bt * 32, w2);
-        tmem_wait_ld();
-        float w[32];
-        const float2 s2 = make_float2(s_i, s_i);
+        for (int b2 = 0; b2 < 2; ++b2) {
+          const int bt = 2 * wg + b2;
+          uint32_t r[32];
 #pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float2 t2 = fma2(s2, f2(w2[k], w2[k + 1]), f2(w1[k], w1[k + 1]));
-          w[k] = t2.x;
-          w[k + 1] = t2.y;
+          for (int kk = 0; kk < 32; ++kk) {
+            const int c = bt * 32 + kk;
+            float v = 0.f;
+            if (src != nullptr) v = __ldcg(src + (src_tr ? (c * kChunk + i) : (i * kChunk + c)));
+            r[kk] = __float_as_uint(v);
+          }
+          tmem_st32(tl + kColT + bt * 32, r);
         }
-        if (a.xrow != nullptr && i < L) {
-          const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
+        tmem_wait_st();
+      }
+      const int nc = t_cnt;
+
+      Decay cur{};
+      float ld_next = 0.f;
+      if (nc > 0) {
+        cur = decay_of(0, load_ld(0));
+        ld_next = load_ld(1);
+        state_copy(cur.eg);
+      }
+
+      for (int it = 0; it < nc; ++it) {
+        const int gi = g0 + it;
+        const int n = chunk_of(it);
+        const int s = gi & 1;
+        const uint32_t ph = (uint32_t)(gi >> 1) & 1u, par = (uint32_t)gi & 1u;
+        const int L = min(kChunk, t_len - n * kChunk);
+        uint8_t *stage = gbase + (size_t)s * kStageBytes;
+        const float c_i = cur.c;
+
+        LA_TRACE(0);
+        if (split) state_copy_low(cur.eg, par);
+        // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
+        mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
+        mbar_wait(bar_p, par, abort_flag, a.status, kStP);
+        tc_fence_after();
+        LA_TRACE(1);
+        {
+          uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
+          uint4 v[8];
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) v[pc] = *reinterpret_cast<const uint4 *>(ybox + sw128_offset(i, pc));
+          const float2 u2 = make_float2(cur.u, cur.u);
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) {
+            float2 f;
+            f = mul2(Fmt<T>::unpack(v[pc].x), u2); v[pc].x = Fmt<T>::pack(f.x, f.y);
+            f = mul2(Fmt<T>::unpack(v[pc].y), u2); v[pc].y = Fmt<T>::pack(f.x, f.y);
+            f = mul2(Fmt<T>::unpack(v[pc].z), u2); v[pc].z = Fmt<T>::pack(f.x, f.y);
+            f = mul2(Fmt<T>::unpack(v[pc].w), u2); v[pc].w = Fmt<T>::pack(f.x, f.y);
+          }
+#pragma unroll
+          for (int pc = 0; pc < 8; ++pc) *reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc)) = v[pc];
+        }
+        fence_proxy_async();
+        mbar_arrive(bar_y);
+        LA_TRACE(2);
+
+        // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P)
+#pragma unroll 1
+        for (int b2 = 0; b2 < 2; ++b2) {
+          const int bt = wg + 2 * b2;  // batches {0,2} / {1,3}: balances the triangular work
+          uint32_t pk[16];
+          const bool dead = rev ? (bt < q4) : (bt > q4);  // warp-uniform
+          if (dead) {
+#pragma unroll
+            for (int kk = 0; kk < 16; ++kk) pk[kk] = 0u;
+          } else {
+            uint32_t r[32];
+            tmem_ld32(tl + kColP + bt * 32, r);
+            tmem_wait_ld();
+            if (bt != q4) {
+              const float ai = b2 ? cur.a1 : cur.a0;
+              const float2 ai2 = make_float2(ai, ai);
+#pragma unroll
+              for (int kk = 0; kk < 32; kk += 4) {
+                const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + kk]);
+                const float2 p0 = mul2(f2(r[kk + 0], r[kk + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
+                const float2 p1 = mul2(f2(r[kk + 2], r[kk + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
+                pk[(kk >> 1) + 0] = Fmt<T>::pack(p0.x, p0.y);
+                pk[(kk >> 1) + 1] = Fmt<T>::pack(p1.x, p1.y);
+              }
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < 32; kk += 2) {
+                const int j = bt * 32 + kk;
+                const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
+                float m0, m1;
+                if (!rev) {
+                  m0 = (j <= i) ? ex2(c_i - cj.x) : 0.f;
+                  m1 = (j + 1 <= i) ? ex2(c_i - cj.y) : 0.f;
+                } else {
+                  m0 = (j >= i && j < L) ? ex2(cj.x - c_i) : 0.f;
+                  m1 = (j + 1 >= i && j + 1 < L) ? ex2(cj.y - c_i) : 0.f;
+                }
+                pk[kk >> 1] = Fmt<T>::pack(__uint_as_float(r[kk]) * m0, __uint_as_float(r[kk + 1]) * m1);
+              }
+            }
+          }
+          tmem_st16(tl + kColP + bt * 32, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_f);
+        LA_TRACE(3);
+
+        // ---- while the tensor cores finish this chunk: decays and state copy of the next one
+        Decay nxt{};
+        if (it + 1 < nc) {  // uniform over the CTA
+          nxt = decay_of(it + 1, ld_next);
+          ld_next = load_ld(it + 2);
+          LA_TRACE(4);
+          mbar_wait(bar_t, par, abort_flag, a.status, kStT);  // T holds this chunk's final state
+          tc_fence_after();
+          LA_TRACE(5);
+          state_copy(nxt.eg);
+        }
+        LA_TRACE(6);
+
+        // ---- epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
+        mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+        tc_fence_after();
+        LA_TRACE(7);
+        const bool full_chunk = (L == kChunk);
+        const long long row_off = row_base + (long long)n * kChunk * a.H * kChunk;
+        const float s_i = cur.s;
+        float rd = 0.f;
+#pragma unroll 1
+        for (int b2 = 0; b2 < 2; ++b2) {
+          const int c0 = 64 * wg + 32 * b2;
+          uint32_t w1[32], w2[32];
+          tmem_ld32(tl + kColW1 + c0, w1);
+          tmem_ld32(tl + kColW2 + c0, w2);
+          tmem_wait_ld();
+          float w[32];
+          const float2 s2 = make_float2(s_i, s_i);
+#pragma unroll
+          for (int kk = 0; kk < 32; kk += 2) {
+            const float2 t2 = fma2(s2, f2(w2[kk], w2[kk + 1]), f2(w1[kk], w1[kk + 1]));
+            w[kk] = t2.x;
+            w[kk + 1] = t2.y;
+          }
+          if (split && i < L) {  // row-dot operand present (uniform over the CTA)
+            const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(ap.xrow) + row_off + c0);
+#pragma unroll
+            for (int pc = 0; pc < 4; ++pc) {
+              const uint4 xv = xp[pc];
+              float2 f;
+              f = Fmt<T>::unpack(xv.x); rd = fmaf(f.x, w[pc * 8 + 0], rd); rd = fmaf(f.y, w[pc * 8 + 1], rd);
+              f = Fmt<T>::unpack(xv.y); rd = fmaf(f.x, w[pc * 8 + 2], rd); rd = fmaf(f.y, w[pc * 8 + 3], rd);
+              f = Fmt<T>::unpack(xv.z); rd = fmaf(f.x, w[pc * 8 + 4], rd); rd = fmaf(f.y, w[pc * 8 + 5], rd);
+              f = Fmt<T>::unpack(xv.w); rd = fmaf(f.x, w[pc * 8 + 6], rd); rd = fmaf(f.y, w[pc * 8 + 7], rd);
+            }
+          }
 #pragma unroll
           for (int pc = 0; pc < 4; ++pc) {
-            const uint4 xv = xp[pc];
-            float2 f;
-            f = Fmt<T>::unpack(xv.x); rd = fmaf(f.x, w[pc * 8 + 0], rd); rd = fmaf(f.y, w[pc * 8 + 1], rd);
-            f = Fmt<T>::unpack(xv.y); rd = fmaf(f.x, w[pc * 8 + 2], rd); rd = fmaf(f.y, w[pc * 8 + 3], rd);
-            f = Fmt<T>::unpack(xv.z); rd = fmaf(f.x, w[pc * 8 + 4], rd); rd = fmaf(f.y, w[pc * 8 + 5], rd);
-            f = Fmt<T>::unpack(xv.w); rd = fmaf(f.x, w[pc * 8 + 6], rd); rd = fmaf(f.y, w[pc * 8 + 7], rd);
+            uint4 v;
+            v.x = Fmt<T>::pack(w[pc * 8 + 0], w[pc * 8 + 1]);
+            v.y = Fmt<T>::pack(w[pc * 8 + 2], w[pc * 8 + 3]);
+            v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
+            v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
+            if (full_chunk) {
+              // staging = this stage's X tile (dead once the MMAs above have completed)
+              *reinterpret_cast<uint4 *>(stage + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
+            } else if (i < L) {
+              reinterpret_cast<uint4 *>(static_cast<T *>(ap.out) + row_off + c0)[pc] = v;
+            }
           }
         }
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          uint4 v;
-          v.x = Fmt<T>::pack(w[pc * 8 + 0], w[pc * 8 + 1]);
-          v.y = Fmt<T>::pack(w[pc * 8 + 2], w[pc * 8 + 3]);
-          v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
-          v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
-          if (full_chunk) {
-            // staging = this stage's X tile (dead once the MMAs above have completed)
-            *reinterpret_cast<uint4 *>(stage + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
-          } else if (i < L) {
-            reinterpret_cast<uint4 *>(static_cast<T *>(a.out) + row_off + bt * 32)[pc] = v;
-          }
+        if (split) {  // uniform over the CTA
+          if (wg == 1) sm->rd[i] = rd;
+          named_bar_sync(2, kComputeThreads);
+          if (wg == 0 && i < L) ap.rowdot[row_off >> 7] = rd + sm->rd[i];
         }
+        if (full_chunk) fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(bar_h);
+        LA_TRACE(8);
+        cur = nxt;
       }
-      if (a.rowdot != nullptr) {  // uniform over the CTA
-        if (wg == 1) sm->rd[i] = rd;
-        named_bar_sync(2, kComputeThreads);
-        if (wg == 0 && i < L) a.rowdot[(bidx * (long long)a.N + tok) * a.H + h] = rd + sm->rd[i];
-      }
-      if (full_chunk) fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(bar_h);
-      LA_TRACE(8);
-      cur = nxt;
-    }
+      g0 += nc;
 
-    // end state -> global
-    if (a.tfinal != nullptr) {
-      tc_fence_after();
-      for (int b2 = 0; b2 < 2; ++b2) {
-        const int bt = 2 * wg + b2;
-        uint32_t r[32];
-        tmem_ld32(tl + kColT + bt * 32, r);
-        tmem_wait_ld();
+      // end state -> the caller's buffer, or the hand-off slot when the sequence continues on
+      // the next CTA
+      {
+        const Task tk = task_of(a, range(), k, ntasks);
+        if (tk.publishes || ap.tfinal != nullptr) {
+          tc_fence_after();
+          float *dst = tk.publishes ? sc.handoff + (size_t)blockIdx.x * (kChunk * kChunk)
+                                    : ap.tfinal + ((long long)tk.seq * a.H + tk.h) * (long long)(kChunk * kChunk);
+          const bool dst_tr = tk.publishes || ap.state_transposed != 0;
+          for (int b2 = 0; b2 < 2; ++b2) {
+            const int bt = 2 * wg + b2;
+            uint32_t r[32];
+            tmem_ld32(tl + kColT + bt * 32, r);
+            tmem_wait_ld();
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int c = bt * 32 + k;
-          a.tfinal[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))] = __uint_as_float(r[k]);
+            for (int kk = 0; kk < 32; ++kk) {
+              const int c = bt * 32 + kk;
+              dst[dst_tr ? (c * kChunk + i) : (i * kChunk + c)] = __uint_as_float(r[kk]);
+            }
+          }
+          if (tk.publishes) {
+            __threadfence();
+            named_bar_sync(3, kComputeThreads);
+            if (tid == 0) st_release(sc.flags + blockIdx.x, 1);
+          }
         }
       }
     }
@@ -670,52 +831,89 @@ chunk_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// (B, N, H, 128) 16-bit tensor; one box = 128 tokens x 64 features of one head, 128-byte swizzle
-int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
-  EncodeTiledFn enc = encode_fn();
-  if (enc == nullptr) return LA_ERR_CUDA;
-  if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
-  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
-  const cuuint64_t strides[3] = {256, (cuuint64_t)H * 256, (cuuint64_t)N * H * 256};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapDataType dt = dtype == LA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
-}
-
 long long *g_trace = nullptr;
 
+// wprefix[s] = sum over sequences before s of max(chunks, 1); one block
+__global__ void weight_prefix_kernel(const long long *cu, int M, long long *wprefix) {
+  __shared__ long long part[1024];
+  const int tid = threadIdx.x, per = (M + 1023) / 1024;
+  const int lo = min(M, tid * per), hi = min(M, lo + per);
+  long long sum = 0;
+  for (int s = lo; s < hi; ++s) {
+    const long long len = cu[s + 1] - cu[s];
+    sum += max((len + kChunk - 1) / kChunk, 1LL);
+  }
+  part[tid] = sum;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const long long v = tid >= off ? part[tid - off] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  long long run = part[tid] - sum;
+  for (int s = lo; s < hi; ++s) {
+    wprefix[s] = run;
+    const long long len = cu[s + 1] - cu[s];
+    run += max((len + kChunk - 1) / kChunk, 1LL);
+  }
+  if (tid == 1023) wprefix[M] = part[1023];
+}
+
+struct DeviceInfo {
+  bool ready = false, attr_bf16 = false, attr_f16 = false;
+  int sms = 0;
+  cudaMemPool_t pool = nullptr;  // hand-off scratch; null if the pool could not be made
+};
+
+// per-device facts and the stream-ordered pool the hand-off scratch comes from
+DeviceInfo *device_info() {
+  static DeviceInfo info[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo &d = info[dev];
+  if (!d.ready) {
+    if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    if (cudaMemPoolCreate(&d.pool, &props) == cudaSuccess) {
+      uint64_t keep = ~0ull;  // freed scratch stays in the pool for the next launch
+      cudaMemPoolSetAttribute(d.pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    } else {
+      d.pool = nullptr;
+      cudaGetLastError();
+    }
+    d.ready = true;
+  }
+  return &d;
+}
+
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// XOPES_B200_CHUNK_SCHED (read once): bit 0 set = never split the chunk space evenly (one CTA per
+// pair), bit 1 set = never merge two passes into one launch.  For measurements.
+int sched_knob() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("XOPES_B200_CHUNK_SCHED");
+    v = e ? atoi(e) & 3 : 0;
+  }
+  return v;
+}
+
 template <typename T>
-int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
-  alignas(64) CUtensorMap mx, my, mz, mo;
+int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   int rc;
-  if ((rc = make_map(&mx, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&mz, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&mo, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&m.x, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&m.y, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&m.z, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&m.o, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if (p.xrow != nullptr && (reinterpret_cast<uintptr_t>(p.xrow) & 15u)) return LA_ERR_MISALIGNED;
-  ChunkArgs a;
   a.xrow = p.xrow; a.rowdot = p.xrow ? p.rowdot : nullptr; a.out = p.out;
   a.ld = p.ld; a.ld_sb = p.ld_sb; a.ld_sn = p.ld_sn; a.ld_sh = p.ld_sh;
   a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
@@ -724,20 +922,77 @@ int launch_t(const ChunkPass &p, int dtype, cudaStream_t stream) {
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   a.trace = g_trace;
-  auto kern = chunk_pass_kernel<T>;
-  static bool attr_set[64] = {false};  // the attribute is per device
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LA_ERR_CUDA;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return LA_ERR_CUDA;
-    attr_set[dev] = true;
-  }
-  const int nb = p.cu ? p.M : p.B;
-  kern<<<nb * p.H, kThreads, kSmemBytes, stream>>>(mx, my, mz, mo, a);
-  return launch_status();
+  return LA_OK;
 }
 
+// One launch for one pass (q == nullptr) or for two passes over the same tokens.
+template <typename T>
+int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t stream) {
+  alignas(64) Maps maps;
+  Launch lp;
+  int rc;
+  if ((rc = fill_pass<T>(p, dtype, maps.p[0], lp.a[0])) != LA_OK) return rc;
+  if ((rc = fill_pass<T>(q ? *q : p, dtype, maps.p[1], lp.a[1])) != LA_OK) return rc;
+  DeviceInfo *di = device_info();
+  if (di == nullptr) return LA_ERR_CUDA;
+  auto kern = chunk_pass_kernel<T>;
+  bool &attr = (dtype == LA_BF16) ? di->attr_bf16 : di->attr_f16;  // the attribute is per device
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return LA_ERR_CUDA;
+    attr = true;
+  }
+  const int npass = q ? 2 : 1;
+  const long long pairs = (long long)(p.cu ? p.M : p.B) * p.H;
+  const int ranges = di->sms / npass;
+  Sched &sc = lp.sc;
+  sc.npass = npass;
+  sc.balanced = 0;
+  sc.total = 0;
+  sc.wprefix = nullptr;
+  sc.handoff = nullptr;
+  sc.flags = nullptr;
+  long long grid = pairs * npass;
+  void *scratch = nullptr;
+  // Worth it when whole pairs per CTA would leave SMs idle in the last round.  Many ragged
+  // documents spread well enough by themselves (CTAs start as SMs free up) and keep neighbouring
+  // heads in step, which the even split does not.
+  const bool uneven = p.cu ? pairs <= 2LL * ranges : true;
+  if (!p.no_scratch && !(sched_knob() & 1) && g_trace == nullptr && di->pool != nullptr && ranges > 0 &&
+      pairs > ranges && pairs % ranges != 0 && uneven) {
+    // even split of the chunk space over one CTA per SM
+    grid = (long long)ranges * npass;
+    const size_t flag_bytes = round_up((size_t)grid * sizeof(int), 256);
+    const size_t prefix_bytes = p.cu ? round_up(((size_t)p.M + 1) * sizeof(long long), 256) : 0;
+    const size_t bytes = flag_bytes + prefix_bytes + (size_t)grid * kChunk * kChunk * sizeof(float);
+    if (cudaMallocFromPoolAsync(&scratch, bytes, di->pool, stream) != cudaSuccess) {
+      cudaGetLastError();
+      scratch = nullptr;
+      grid = pairs * npass;
+    } else {
+      uint8_t *base = static_cast<uint8_t *>(scratch);
+      sc.balanced = 1;
+      sc.flags = reinterpret_cast<int *>(base);
+      sc.handoff = reinterpret_cast<float *>(base + flag_bytes + prefix_bytes);
+      sc.total = pairs * (((long long)p.N + kChunk - 1) / kChunk);
+      bool ok = cudaMemsetAsync(sc.flags, 0, flag_bytes, stream) == cudaSuccess;
+      if (ok && p.cu) {
+        long long *wp = reinterpret_cast<long long *>(base + flag_bytes);
+        sc.wprefix = wp;
+        weight_prefix_kernel<<<1, 1024, 0, stream>>>(reinterpret_cast<const long long *>(p.cu), p.M, wp);
+        ok = cudaGetLastError() == cudaSuccess;
+      }
+      if (!ok) {
+        cudaFreeAsync(scratch, stream);
+        return LA_ERR_CUDA;
+      }
+    }
+  }
+  kern<<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(maps, lp);
+  rc = launch_status();
+  if (scratch != nullptr && cudaFreeAsync(scratch, stream) != cudaSuccess && rc == LA_OK) rc = LA_ERR_CUDA;
+  return rc;
+}
 
 // ------------------------------------------------------------------------------------------------
 // Self-test of the tensor-core building blocks: one 128x128x128 product per variant, operands
@@ -866,14 +1121,38 @@ bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
   return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
 }
 
-int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream) {
+namespace {
+int check_pass(const ChunkPass &p) {
   if (p.x == nullptr || p.y == nullptr || p.z == nullptr || p.out == nullptr || p.ld == nullptr)
     return LA_ERR_NULL_POINTER;
   const int nb = p.cu ? p.M : p.B;
   if (nb <= 0 || p.H <= 0 || p.N <= 0) return LA_ERR_BAD_SHAPE;
-  if ((int64_t)nb * p.H > 0x7fffffff) return LA_ERR_TOO_LARGE;
-  if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, dtype, stream);
-  if (dtype == LA_F16) return launch_t<__half>(p, dtype, stream);
+  if ((int64_t)nb * p.H * 2 > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  return LA_OK;
+}
+}  // namespace
+
+int launch_chunk_pass(const ChunkPass &p, int dtype, cudaStream_t stream) {
+  const int rc = check_pass(p);
+  if (rc != LA_OK) return rc;
+  if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, nullptr, dtype, stream);
+  if (dtype == LA_F16) return launch_t<__half>(p, nullptr, dtype, stream);
+  return LA_ERR_UNSUPPORTED;
+}
+
+int launch_chunk_pass_pair(const ChunkPass &p, const ChunkPass &q, int dtype, cudaStream_t stream) {
+  int rc = check_pass(p);
+  if (rc == LA_OK) rc = check_pass(q);
+  if (rc != LA_OK) return rc;
+  if (p.B != q.B || p.N != q.N || p.H != q.H || p.M != q.M || p.cu != q.cu || p.reverse != q.reverse ||
+      p.ld != q.ld || p.ld_sb != q.ld_sb || p.ld_sn != q.ld_sn || p.ld_sh != q.ld_sh)
+    return LA_ERR_BAD_SHAPE;
+  if (sched_knob() & 2) {
+    rc = launch_chunk_pass(p, dtype, stream);
+    return rc != LA_OK ? rc : launch_chunk_pass(q, dtype, stream);
+  }
+  if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, &q, dtype, stream);
+  if (dtype == LA_F16) return launch_t<__half>(p, &q, dtype, stream);
   return LA_ERR_UNSUPPORTED;
 }
 
