@@ -330,12 +330,13 @@ def test_lasd_more_pairs_than_sms(shape):
 
 
 @pytest.mark.parametrize("want_dld", [False, True])
-def test_lasd_varlen_many_documents(want_dld):
+@pytest.mark.parametrize("ndocs", [44, 19])  # 200 and 100 (document, head) pairs
+def test_lasd_varlen_many_documents(want_dld, ndocs):
     """Ragged documents (empty, one token, several times a CTA's share of the chunk space) with
     more (document, head) pairs than SMs."""
     import xopes_b200 as xb
     g = torch.Generator().manual_seed(21)
-    lens = [3000, 0, 1, 128] + [int(x) for x in torch.randint(0, 400, (44,), generator=g)] + [0, 700]
+    lens = [3000, 0, 1, 128] + [int(x) for x in torch.randint(0, 400, (ndocs,), generator=g)] + [0, 700]
     n, h, d, e = sum(lens), 4, 128, 128
     dtype = torch.bfloat16
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)

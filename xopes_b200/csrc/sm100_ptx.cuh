@@ -37,17 +37,39 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// The same with a suspend-time hint: the hardware may park the thread for up to `hint_ns`
+// nanoseconds (or until the phase completes) before it answers, so a waiting warp takes no
+// issue slots from the warps that do the work.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
-// Bounded wait.  Gives up after `limit` polls (or as soon as another thread of the CTA has given
-// up), raises the CTA's abort flag and records `code` in the device status word.  The caller
-// carries on as if the wait had succeeded: control flow stays convergent, every later wait
-// returns at once, and the kernel ends by itself with a non-zero status instead of hanging.
+// Bounded wait.  Gives up after `limit_us` microseconds (or as soon as another thread of the CTA
+// has given up), raises the CTA's abort flag and records `code` in the device status word.  The
+// caller carries on as if the wait had succeeded: control flow stays convergent, every later
+// wait returns at once, and the kernel ends by itself with a non-zero status instead of hanging.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int code, uint32_t limit = (1u << 22)) {
-  for (uint32_t it = 0; it < limit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag != 0) return false;
-  }
+                                          int *status, int code, uint32_t limit_us = (1u << 22)) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag != 0) return false;
+  const uint64_t t0 = globaltimer_ns();
+  do {
+    if (mbar_try_wait_parked(bar, parity, 50000u)) return true;
+    if (*abort_flag != 0) return false;
+  } while (globaltimer_ns() - t0 < (uint64_t)limit_us * 1000ull);
   *abort_flag = 1;
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
