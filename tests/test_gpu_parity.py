@@ -319,6 +319,35 @@ def test_lasd_varlen_documents_are_independent(dtype, tol):
     assert_close("dinitial_state", rs0, s0c.grad, tol)
 
 
+@pytest.mark.parametrize("reverse_heavy", [False, True])
+def test_lasd_extreme_decay(reverse_heavy):
+    """Log decays of -2 to -8 per token: a 32-token batch decays by hundreds of bits, beyond what
+    the factorised decay mask of the tensor-core path may represent, so its diagonal batches take
+    the per-element path; mixed with mild heads that stay factorised."""
+    import xopes_b200 as xb
+    b, n, h, d, e = 2, 300, 4, 128, 128
+    dtype = torch.bfloat16
+    qf, kf, vf, ld, s0, dof, dsf = _lasd_seeded(b, n, h, d, e, 31, dtype, True, True, False)
+    g = torch.Generator().manual_seed(32)
+    ld = -(2.0 + 6.0 * torch.rand(b, n, h, generator=g))
+    ld[:, :, 0] = -0.01 * torch.rand(b, n, generator=g)      # one mild head
+    if reverse_heavy:
+        ld[:, ::7, 1] = -40.0                                 # isolated near-resets
+    q, k, v, ldc, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ld), leaf(s0)
+    o, sf = xb.lasd_fn(q, k, v, ldc, initial_state=s0c)
+    ro, rsf = orc.lasd_forward(qf, kf, vf, ld, s0)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rld, rs0 = orc.lasd_backward(qf, kf, vf, ld, dof, s0, dsf)
+    assert torch.isfinite(q.grad).all() and torch.isfinite(k.grad).all() and torch.isfinite(v.grad).all()
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    assert_close("dld", rld, ldc.grad, dld_tol(dtype, TOL_BF16))
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
 @pytest.mark.parametrize("shape", [(5, 400, 32, 128, 128), (3, 513, 30, 128, 128), (40, 256, 4, 128, 128)])
 def test_lasd_more_pairs_than_sms(shape):
     """More (sequence, head) pairs than SMs: the chunk passes split the chunk space evenly over

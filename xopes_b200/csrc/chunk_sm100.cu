@@ -457,6 +457,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       float c;         // inclusive in-chunk cumulative log2 decay of row i
       float a0, a1;    // row factors of the factorised mask for this thread's two column batches
       float eg, s, u;  // e^g, output-row scale, Y-row scale
+      bool wide;       // this row batch decays by more than 2^-64 end to end (warp-uniform)
     };
     // A: cumulative decays of step `it` of the task.  Contains a named barrier; cs/bs are
     // overwritten only after it, i.e. after every thread has finished reading the previous
@@ -487,6 +488,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       }
       c += w_lo;
       d.c = c;
+      d.wide = (w_lo - w_hi) > 64.f;
       d.a0 = rev ? ex2(r0 - c) : ex2(c - r0);
       d.a1 = rev ? ex2(r1 - c) : ex2(c - r1);
       d.eg = ex2(g);
@@ -643,14 +645,17 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           uint4 v[8];
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) v[pc] = *reinterpret_cast<const uint4 *>(ybox + sw128_offset(i, pc));
-          const float2 u2 = make_float2(cur.u, cur.u);
+          // u as a 16-bit value plus its 16-bit remainder: two packed 16-bit operations per
+          // pair of elements instead of unpack, fp32 multiply and pack
+          const uint32_t uh = Fmt<T>::pack(cur.u, cur.u);
+          const float urem = cur.u - Fmt<T>::unpack(uh).x;
+          const uint32_t ul = Fmt<T>::pack(urem, urem);
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) {
-            float2 f;
-            f = mul2(Fmt<T>::unpack(v[pc].x), u2); v[pc].x = Fmt<T>::pack(f.x, f.y);
-            f = mul2(Fmt<T>::unpack(v[pc].y), u2); v[pc].y = Fmt<T>::pack(f.x, f.y);
-            f = mul2(Fmt<T>::unpack(v[pc].z), u2); v[pc].z = Fmt<T>::pack(f.x, f.y);
-            f = mul2(Fmt<T>::unpack(v[pc].w), u2); v[pc].w = Fmt<T>::pack(f.x, f.y);
+            v[pc].x = Fmt<T>::scale(v[pc].x, uh, ul);
+            v[pc].y = Fmt<T>::scale(v[pc].y, uh, ul);
+            v[pc].z = Fmt<T>::scale(v[pc].z, uh, ul);
+            v[pc].w = Fmt<T>::scale(v[pc].w, uh, ul);
           }
 #pragma unroll
           for (int pc = 0; pc < 8; ++pc) *reinterpret_cast<uint4 *>(ybox + sw128_offset(i, pc)) = v[pc];
@@ -659,31 +664,24 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         mbar_arrive(bar_y);
         LA_TRACE(2);
 
-        // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P)
-#pragma unroll 1
-        for (int b2 = 0; b2 < 2; ++b2) {
-          const int bt = wg + 2 * b2;  // batches {0,2} / {1,3}: balances the triangular work
-          uint32_t pk[16];
-          const bool dead = rev ? (bt < q4) : (bt > q4);  // warp-uniform
-          if (dead) {
+        // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P).  This thread's
+        // batches are wg and wg + 2 ({0,2} / {1,3} balances the triangular work); both loads
+        // are issued before the one wait.
+        {
+          const bool dead0 = rev ? (wg < q4) : (wg > q4);          // warp-uniform
+          const bool dead1 = rev ? (wg + 2 < q4) : (wg + 2 > q4);
+          uint32_t r0[32], r1[32];
+          if (!dead0) tmem_ld32(tl + kColP + wg * 32, r0);
+          if (!dead1) tmem_ld32(tl + kColP + (wg + 2) * 32, r1);
+          tmem_wait_ld();
+          auto mask_batch = [&](const int b2, uint32_t(&r)[32], const bool dead) {
+            const int bt = wg + 2 * b2;
+            uint32_t pk[16];
+            if (dead) {
 #pragma unroll
-            for (int kk = 0; kk < 16; ++kk) pk[kk] = 0u;
-          } else {
-            uint32_t r[32];
-            tmem_ld32(tl + kColP + bt * 32, r);
-            tmem_wait_ld();
-            if (bt != q4) {
-              const float ai = b2 ? cur.a1 : cur.a0;
-              const float2 ai2 = make_float2(ai, ai);
-#pragma unroll
-              for (int kk = 0; kk < 32; kk += 4) {
-                const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + kk]);
-                const float2 p0 = mul2(f2(r[kk + 0], r[kk + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
-                const float2 p1 = mul2(f2(r[kk + 2], r[kk + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
-                pk[(kk >> 1) + 0] = Fmt<T>::pack(p0.x, p0.y);
-                pk[(kk >> 1) + 1] = Fmt<T>::pack(p1.x, p1.y);
-              }
-            } else {
+              for (int kk = 0; kk < 16; ++kk) pk[kk] = 0u;
+            } else if (bt == q4 && cur.wide) {
+              // diagonal batch whose decay range is too wide to factorise: one exponential per element
 #pragma unroll
               for (int kk = 0; kk < 32; kk += 2) {
                 const int j = bt * 32 + kk;
@@ -698,9 +696,32 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
                 }
                 pk[kk >> 1] = Fmt<T>::pack(__uint_as_float(r[kk]) * m0, __uint_as_float(r[kk + 1]) * m1);
               }
+            } else {
+              // weight = (row factor) x (column factor), both relative to the batch edge next to
+              // the diagonal; on the diagonal batch the entries beyond the diagonal are dropped
+              const float ai = b2 ? cur.a1 : cur.a0;
+              const float2 ai2 = make_float2(ai, ai);
+#pragma unroll
+              for (int kk = 0; kk < 32; kk += 4) {
+                const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + kk]);
+                const float2 p0 = mul2(f2(r[kk + 0], r[kk + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
+                const float2 p1 = mul2(f2(r[kk + 2], r[kk + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
+                r[kk + 0] = __float_as_uint(p0.x); r[kk + 1] = __float_as_uint(p0.y);
+                r[kk + 2] = __float_as_uint(p1.x); r[kk + 3] = __float_as_uint(p1.y);
+              }
+              if (bt == q4) {
+                const uint32_t keep = rev ? (0xffffffffu << lane) : (0xffffffffu >> (31 - lane));
+#pragma unroll
+                for (int kk = 0; kk < 32; ++kk) r[kk] = ((keep >> kk) & 1u) ? r[kk] : 0u;
+              }
+#pragma unroll
+              for (int kk = 0; kk < 32; kk += 2)
+                pk[kk >> 1] = Fmt<T>::pack(__uint_as_float(r[kk]), __uint_as_float(r[kk + 1]));
             }
-          }
-          tmem_st16(tl + kColP + bt * 32, pk);
+            tmem_st16(tl + kColP + bt * 32, pk);
+          };
+          mask_batch(0, r0, dead0);
+          mask_batch(1, r1, dead1);
         }
         tmem_wait_st();
         tc_fence_before();

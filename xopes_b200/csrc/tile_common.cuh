@@ -20,6 +20,14 @@ template <> struct Fmt<__nv_bfloat16> {
   static __device__ __forceinline__ float2 unpack(uint32_t u) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
   }
+  // y * (hi + lo) on a packed pair, rounded once more than the exact product: the factor is
+  // carried as a 16-bit value plus its 16-bit remainder, so no unpacking to fp32 is needed
+  static __device__ __forceinline__ uint32_t scale(uint32_t y, uint32_t hi, uint32_t lo) {
+    const __nv_bfloat162 yy = *reinterpret_cast<__nv_bfloat162 *>(&y);
+    const __nv_bfloat162 r = __hfma2(yy, *reinterpret_cast<__nv_bfloat162 *>(&hi),
+                                     __hmul2(yy, *reinterpret_cast<__nv_bfloat162 *>(&lo)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
 };
 template <> struct Fmt<__half> {
   static constexpr uint32_t kAB = 0;
@@ -29,6 +37,11 @@ template <> struct Fmt<__half> {
   }
   static __device__ __forceinline__ float2 unpack(uint32_t u) {
     return __half22float2(*reinterpret_cast<__half2 *>(&u));
+  }
+  static __device__ __forceinline__ uint32_t scale(uint32_t y, uint32_t hi, uint32_t lo) {
+    const __half2 yy = *reinterpret_cast<__half2 *>(&y);
+    const __half2 r = __hfma2(yy, *reinterpret_cast<__half2 *>(&hi), __hmul2(yy, *reinterpret_cast<__half2 *>(&lo)));
+    return *reinterpret_cast<const uint32_t *>(&r);
   }
 };
 
