@@ -1,4 +1,6 @@
 // extern "C" entry points: argument checks, choice of kernel family, pass orchestration.
+#include <mutex>
+
 #include "chunk.cuh"
 #include "scan.cuh"
 
@@ -34,6 +36,52 @@ static int *lavd_unsafe_ptr() {
 }
 
 namespace {
+
+// A second stream per device for passes of one call that do not depend on each other (a gradient
+// pass that would leave SMs idle runs beside the next one).  fork() makes the side stream wait for
+// everything already queued on the caller's stream, join() makes the caller's stream wait for the
+// side stream.  One caller at a time per device: the lock is held from fork to join.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  std::mutex mu;
+  bool ready = false, failed = false;
+};
+
+SideStream *side_stream() {
+  static SideStream side[64];
+  static std::mutex init_mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(init_mu);
+  SideStream &s = side[dev];
+  if (!s.ready && !s.failed) {
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join_ev, cudaEventDisableTiming) != cudaSuccess) {
+      s.failed = true;
+      cudaGetLastError();
+    } else {
+      s.ready = true;
+    }
+  }
+  return s.ready ? &s : nullptr;
+}
+
+bool side_fork(SideStream *s, cudaStream_t st) {
+  return cudaEventRecord(s->fork_ev, st) == cudaSuccess && cudaStreamWaitEvent(s->stream, s->fork_ev, 0) == cudaSuccess;
+}
+bool side_join(SideStream *s, cudaStream_t st) {
+  return cudaEventRecord(s->join_ev, s->stream) == cudaSuccess && cudaStreamWaitEvent(st, s->join_ev, 0) == cudaSuccess;
+}
+
+int sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (sms[dev] == 0 && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return sms[dev];
+}
 
 bool dtype_ok(int dtype) { return dtype == LA_F32 || dtype == LA_BF16 || dtype == LA_F16; }
 
@@ -219,7 +267,17 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     c.x = d_o; c.y = v; c.z = k; c.out = dq; c.t0 = initial_state; c.state_transposed = 1;
     c.tfinal = state_term ? ws_state : nullptr; c.reverse = 0;
     c.xrow = want_dld ? q : nullptr; c.rowdot = slots_q;
-    if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) return rc;
+    // With few (sequence, head) pairs the dq pass runs beside the merged dk/dv launch.
+    SideStream *side = (!no_scratch && 3 * (int64_t)s.nb() * s.H <= sm_count() + sm_count() / 2) ? side_stream() : nullptr;
+    std::unique_lock<std::mutex> side_lock;
+    if (side != nullptr) {
+      side_lock = std::unique_lock<std::mutex>(side->mu);
+      if (!side_fork(side, st)) return LA_ERR_CUDA;
+      rc = launch_chunk_pass(c, dtype, side->stream);
+      if (rc != LA_OK) { side_join(side, st); return rc; }
+    } else if ((rc = launch_chunk_pass(c, dtype, st)) != LA_OK) {
+      return rc;
+    }
     // dk: (v, do, q), state dS^T, reverse direction
     c.x = v; c.y = d_o; c.z = q; c.out = dk; c.t0 = dfinal_state; c.state_transposed = 1;
     c.tfinal = nullptr; c.reverse = 1;
@@ -229,7 +287,12 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     ChunkPass c2 = c;
     c2.x = k; c2.y = q; c2.z = d_o; c2.out = dv; c2.t0 = dfinal_state; c2.state_transposed = 0;
     c2.tfinal = dinitial_state; c2.reverse = 1; c2.xrow = nullptr; c2.rowdot = nullptr;
-    if ((rc = launch_chunk_pass_pair(c, c2, dtype, st)) != LA_OK) return rc;
+    rc = launch_chunk_pass_pair(c, c2, dtype, st);
+    if (side != nullptr) {
+      if (!side_join(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
+      side_lock.unlock();
+    }
+    if (rc != LA_OK) return rc;
   } else {
     // dq: T = S (rows D): a = k, b = v, w = do
     ScanParams p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
@@ -380,18 +443,35 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     if (cudaMemsetAsync(unsafe, 0, sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
+    // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
+    // with the other two passes, so while one CTA per (sequence, head) leaves SMs idle it runs
+    // beside them on the side stream.
+    LavdPass cv = c;
+    cv.x = k; cv.y = q; cv.z = d_o; cv.out = dv; cv.tmode = 0; cv.state_transposed = 0; cv.reverse = 1;
+    cv.t0 = dfinal_state; cv.tfinal = dinitial_state; cv.xrow = nullptr; cv.dld = nullptr;
+    SideStream *side = (2 * (int64_t)s.nb() * s.H <= sm_count() + sm_count() / 2) ? side_stream() : nullptr;
+    std::unique_lock<std::mutex> side_lock;
+    if (side != nullptr) {
+      side_lock = std::unique_lock<std::mutex>(side->mu);
+      if (!side_fork(side, st)) return LA_ERR_CUDA;
+      rc = launch_lavd_pass(cv, dtype, side->stream);
+      if (rc != LA_OK) { side_join(side, st); return rc; }
+    }
     // dq: (do, v, k), state S^T, forward; dldk = q * dq
     c.x = d_o; c.y = v; c.z = k; c.out = dq; c.tmode = 1; c.state_transposed = 1; c.reverse = 0;
     c.t0 = initial_state; c.tfinal = ws_state; c.xrow = q; c.dld = dldk; c.dld_sub = 0;
-    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    rc = launch_lavd_pass(c, dtype, st);
     // dk: (v, do, q), state dS^T, reverse; dldk -= k * dk
     c.x = v; c.y = d_o; c.z = q; c.out = dk; c.reverse = 1;
     c.t0 = dfinal_state; c.tfinal = nullptr; c.xrow = k; c.dld_sub = 1;
-    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
-    // dv: (k, q, do), state dS, reverse; its end state is d initial_state
-    c.x = k; c.y = q; c.z = d_o; c.out = dv; c.tmode = 0; c.state_transposed = 0; c.reverse = 1;
-    c.t0 = dfinal_state; c.tfinal = dinitial_state; c.xrow = nullptr; c.dld = nullptr;
-    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    if (rc == LA_OK) rc = launch_lavd_pass(c, dtype, st);
+    if (side != nullptr) {
+      if (!side_join(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
+      side_lock.unlock();
+    } else if (rc == LA_OK) {
+      rc = launch_lavd_pass(cv, dtype, st);
+    }
+    if (rc != LA_OK) return rc;
     enable = unsafe;
   }
   ScanParams p;

@@ -210,12 +210,13 @@ __device__ __forceinline__ void st_release(int *p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// trace[thread slot][chunk][point]: 16 points per chunk, 2 thread slots of 4096 chunks at most
+// trace[thread slot][chunk][point]: 16 points per chunk, 3 thread slots (threads 0 and 32 of the
+// compute warps, the tensor-core issue thread) of 4096 chunks at most
 #ifdef LA_CHUNK_TRACE
 #define LA_TRACE(point)                                                                   \
   do {                                                                                    \
-    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32) && gi < 4096)      \
-      a.trace[((tid >> 5) * 4096 + gi) * 16 + (point)] = clock64();                       \
+    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32 || tid == kMmaWarp * 32) && gi < 4096) \
+      a.trace[((tid == 0 ? 0 : (tid == 32 ? 1 : 2)) * 4096 + gi) * 16 + (point)] = clock64(); \
   } while (0)
 #else
 #define LA_TRACE(point) do { } while (0)
@@ -357,8 +358,10 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           const uint64_t d_ymn = desc_mnmajor(ys, kBoxBytes), d_zmn = desc_mnmajor(zs, kBoxBytes);
           // descriptor advance per 16-element K slice, in 16-byte units: K-major tiles step 32 B
           // inside a 128 B row and jump to the second box after 4 slices; MN-major tiles step 16 rows
+          LA_TRACE(0);
           mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
           tc_fence_after();
+          LA_TRACE(1);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
@@ -369,6 +372,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mbar_wait(bar_d, par, abort_flag, a.status, kStD);
           if (gi > 0) mbar_wait(bar_h, par ^ 1u, abort_flag, a.status, kStH);
           tc_fence_after();
+          LA_TRACE(2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
@@ -388,12 +392,14 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           // next chunk's state copy while P~ Z still runs
           mbar_wait(bar_y, par, abort_flag, a.status, kStY);
           tc_fence_after();
+          LA_TRACE(3);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
           mma_commit(bar_t);
           mbar_wait(bar_f, par, abort_flag, a.status, kStF);
           tc_fence_after();
+          LA_TRACE(4);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
@@ -401,6 +407,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mma_commit(bar_w);
           // the next chunk's X Y^T overwrites P, which the product above reads as P~
           mbar_wait(bar_w, par, abort_flag, a.status, kStW);
+          LA_TRACE(5);
         }
         g0 += tk.cnt;
       }
