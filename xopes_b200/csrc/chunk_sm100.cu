@@ -40,8 +40,11 @@ constexpr int kStages = 2;
 constexpr int kStageBytes = 3 * kTileBytes;
 constexpr int kOffTb = kStages * kStageBytes;
 constexpr int kOffSmall = kOffTb + kTileBytes;
-constexpr int kSmallBytes = 2048;
-constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;  // + slack to align the base to 1024 B
+constexpr int kSmallBytes = 3072;
+// All of the 227 KB a CTA may have.  There is no slack to round the base up: the kernel declares its
+// dynamic shared memory 1024-byte aligned (the 128-byte swizzle needs that) and checks it.
+constexpr int kSmemBytes = kOffSmall + kSmallBytes;
+constexpr int kStAlign = 113;
 constexpr int kComputeThreads = 256;                        // two warpgroups, each owns 64 columns
 constexpr int kProducerWarp = 8;                            // TMA loads
 constexpr int kMmaWarp = 9;                                 // tcgen05.mma issue
@@ -73,9 +76,11 @@ struct Small {
   int issued;
   int pad;
   int rg[4];                  // this CTA's range of the chunk space (Range), written once at start
-  alignas(16) float wsum[4];
-  alignas(16) float cs[kChunk];   // inclusive cumulative log2 decay of each row of the chunk
-  alignas(16) float bs[kChunk];   // per-column factor of the factorised decay mask (read as float4)
+  alignas(16) float wsum[2][4];     // per-quadrant decay sums, by chunk parity like cs/bs
+  // double-buffered by chunk parity: the next chunk's values are computed while the tensor cores
+  // still work on X Y^T of the current one
+  alignas(16) float cs[2][kChunk];  // inclusive cumulative log2 decay of each row of the chunk
+  alignas(16) float bs[2][kChunk];  // per-column factor of the factorised decay mask (read as float4)
   alignas(16) float rd[kChunk];   // row-dot partial of the second warpgroup
 };
 static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
@@ -240,13 +245,16 @@ __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Launch lp) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t *gbase = smem_raw + (base - raw);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t *gbase = smem_raw;
   Small *sm = reinterpret_cast<Small *>(gbase + kOffSmall);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (base & 1023u) {  // uniform over the CTA; nothing has been set up yet
+    if (tid == 0) atomicCAS(lp.a[0].status, 0, kStAlign);
+    return;
+  }
   // Arguments both passes of a merged launch share (sizes, strides, decay, direction) are read
   // from slot 0 as direct constant-bank operands; only the few that differ (`ap`: row-dot
   // operand, output, states) are indexed by the pass, and none of those is touched per chunk
@@ -466,10 +474,11 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       float eg, s, u;  // e^g, output-row scale, Y-row scale
       bool wide;       // this row batch decays by more than 2^-64 end to end (warp-uniform)
     };
-    // A: cumulative decays of step `it` of the task.  Contains a named barrier; cs/bs are
-    // overwritten only after it, i.e. after every thread has finished reading the previous
-    // chunk's values.
-    auto decay_of = [&](int it, float ldv) -> Decay {
+    // A: cumulative decays of step `it` of the task, cs/bs into buffer `buf`.  Contains a named
+    // barrier.  A buffer is rewritten two chunks after it was filled; by then every thread has
+    // arrived on bar_f of the chunk that read it (the tensor cores, and so the epilogue every
+    // thread has since passed, wait for that).
+    auto decay_of = [&](int it, float ldv, int buf) -> Decay {
       Decay d;
       const int L = t_len - chunk_of(it) * kChunk;  // rows >= L are padding
       float c = ldv;
@@ -478,7 +487,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         const float nb = __shfl_up_sync(0xffffffffu, c, off);
         if (lane >= off) c += nb;
       }
-      if (wg == 0 && lane == 31) sm->wsum[q4] = c;
+      if (wg == 0 && lane == 31) sm->wsum[buf][q4] = c;
       named_bar_sync(1, kComputeThreads);
       // cumulative decay at the start (w_lo) / end (w_hi) of this thread's 32-row batch, over the
       // chunk (g), and at the reference edge of its two column batches wg and wg + 2
@@ -486,7 +495,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       float w_lo = 0.f, w_hi = 0.f, g = 0.f, r0 = 0.f, r1 = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const float ws = sm->wsum[w];
+        const float ws = sm->wsum[buf][w];
         g += ws;
         if (w < q4) w_lo += ws;
         if (w <= q4) w_hi += ws;
@@ -502,8 +511,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       d.s = rev ? ex2(g - c) : ex2(c);
       d.u = (i < L) ? (rev ? ex2(c) : ex2(g - c)) : 0.f;
       if (wg == 0) {
-        sm->cs[i] = c;
-        sm->bs[i] = rev ? ((i < L) ? ex2(c - w_lo) : 0.f) : ex2(w_hi - c);
+        sm->cs[buf][i] = c;
+        sm->bs[buf][i] = rev ? ((i < L) ? ex2(c - w_lo) : 0.f) : ex2(w_hi - c);
       }
       return d;
     };
@@ -626,7 +635,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       Decay cur{};
       float ld_next = 0.f;
       if (nc > 0) {
-        cur = decay_of(0, load_ld(0));
+        cur = decay_of(0, load_ld(0), g0 & 1);
         ld_next = load_ld(1);
         state_copy(cur.eg);
       }
@@ -641,12 +650,19 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         const float c_i = cur.c;
 
         LA_TRACE(0);
+        // ---- decays of the next chunk, while the tensor cores are still on this one's X Y^T
+        Decay nxt{};
+        if (it + 1 < nc) {  // uniform over the CTA
+          nxt = decay_of(it + 1, ld_next, (gi + 1) & 1);
+          ld_next = load_ld(it + 2);
+        }
+        LA_TRACE(1);
         if (split) state_copy_low(cur.eg, par);
         // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
         mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
         mbar_wait(bar_p, par, abort_flag, a.status, kStP);
         tc_fence_after();
-        LA_TRACE(1);
+        LA_TRACE(2);
         {
           uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
           uint4 v[8];
@@ -669,7 +685,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         }
         fence_proxy_async();
         mbar_arrive(bar_y);
-        LA_TRACE(2);
+        LA_TRACE(3);
 
         // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P).  This thread's
         // batches are wg and wg + 2 ({0,2} / {1,3} balances the triangular work); both loads
@@ -692,7 +708,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
 #pragma unroll
               for (int kk = 0; kk < 32; kk += 2) {
                 const int j = bt * 32 + kk;
-                const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[j]);
+                const float2 cj = *reinterpret_cast<const float2 *>(&sm->cs[gi & 1][j]);
                 float m0, m1;
                 if (!rev) {
                   m0 = (j <= i) ? ex2(c_i - cj.x) : 0.f;
@@ -710,7 +726,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
               const float2 ai2 = make_float2(ai, ai);
 #pragma unroll
               for (int kk = 0; kk < 32; kk += 4) {
-                const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[bt * 32 + kk]);
+                const float4 bj = *reinterpret_cast<const float4 *>(&sm->bs[gi & 1][bt * 32 + kk]);
                 const float2 p0 = mul2(f2(r[kk + 0], r[kk + 1]), mul2(ai2, make_float2(bj.x, bj.y)));
                 const float2 p1 = mul2(f2(r[kk + 2], r[kk + 3]), mul2(ai2, make_float2(bj.z, bj.w)));
                 r[kk + 0] = __float_as_uint(p0.x); r[kk + 1] = __float_as_uint(p0.y);
@@ -733,14 +749,10 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_f);
-        LA_TRACE(3);
+        LA_TRACE(4);
 
-        // ---- while the tensor cores finish this chunk: decays and state copy of the next one
-        Decay nxt{};
+        // ---- while the tensor cores finish this chunk: state copy of the next one
         if (it + 1 < nc) {  // uniform over the CTA
-          nxt = decay_of(it + 1, ld_next);
-          ld_next = load_ld(it + 2);
-          LA_TRACE(4);
           mbar_wait(bar_t, par, abort_flag, a.status, kStT);  // T holds this chunk's final state
           tc_fence_after();
           LA_TRACE(5);
