@@ -230,6 +230,20 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tma_load_4d(zs + kBoxBytes, &map_z, bar_full, 64, h, tok0, bidx);
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) tma_load_4d(cks + gq * kBoxBytes, &map_ld, bar_full, 32 * gq, h, tok0, bidx);
+        // The stage is single-buffered, so the next chunk's loads start only when this chunk is
+        // stored and the CTA then waits out their full latency; pulling that chunk into L2 now
+        // shortens the wait (the pass uses a fraction of the HBM bandwidth, so this costs nothing).
+        if (it + 1 < nc) {
+          const int tokp = (int)t_begin + (rev ? (n - 1) : (n + 1)) * kChunk;
+          tma_prefetch_4d(&map_x, 0, h, tokp, bidx);
+          tma_prefetch_4d(&map_x, 64, h, tokp, bidx);
+          tma_prefetch_4d(&map_y, 0, h, tokp, bidx);
+          tma_prefetch_4d(&map_y, 64, h, tokp, bidx);
+          tma_prefetch_4d(&map_z, 0, h, tokp, bidx);
+          tma_prefetch_4d(&map_z, 64, h, tokp, bidx);
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq) tma_prefetch_4d(&map_ld, 32 * gq, h, tokp, bidx);
+        }
       }
       sm->issued = it;
     }
