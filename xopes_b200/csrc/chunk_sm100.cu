@@ -11,8 +11,11 @@
 //
 // The 128x128 fp32 state T never leaves tensor memory between chunks, so HBM sees each operand
 // tile once per pass and the output once.  A producer warp keeps the next chunk's three tiles in
-// flight with plain (non-multicast) TMA loads while the four compute warps work on the current
-// one.  Shared memory: 2 stages x 3 tiles x 32 KB + 32 KB state copy = 224 KB; tensor memory:
+// flight with plain (non-multicast) TMA loads while the eight compute warps work on the current
+// one.  X and Y of a stage go back to the producer as soon as the products that read them are
+// done (mid-chunk); Z doubles as the staging buffer of the output tile, which a store warp writes
+// out with TMA, and goes back after that.  Shared memory: 2 stages x 3 tiles x 32 KB + 32 KB
+// state copy + 3 KB of barriers and per-row decay values = 227 KB; tensor memory:
 // T | P | W1 | W2 = 4 x 128 columns.
 //
 // Every mbarrier wait is bounded (sm100_ptx.cuh: mbar_wait); a wait that runs out sets the device
@@ -60,8 +63,12 @@ constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104, kStD = 105,
               kStT = 108, kStY = 109, kStX = 110, kStL = 111;
 
 struct Small {
-  unsigned long long full[kStages];
-  unsigned long long empty[kStages];
+  // X and Y of a stage are released as soon as the products that read them are done (mid-chunk);
+  // Z doubles as the staging buffer of the output tile and is released when that has been stored
+  unsigned long long full[kStages];    // X and Y landed
+  unsigned long long empty[kStages];   // X and Y free
+  unsigned long long fullz[kStages];   // Z landed
+  unsigned long long emptyz[kStages];  // Z free
   unsigned long long bar_p;   // P = X Y^T complete                       (MMA warp -> compute)
   unsigned long long bar_w;   // W1, W2 and the state update complete      (MMA warp -> compute)
   unsigned long long bar_t;   // state update complete (T final for the chunk) (MMA warp -> compute)
@@ -73,8 +80,8 @@ struct Small {
   unsigned long long bar_l;   // low half of the state copy written, T rescaled (compute -> MMA warp)
   uint32_t tmem_base;
   int abort_flag;
-  int issued;
-  int pad;
+  int issued;    // chunks whose X and Y loads were issued
+  int issuedz;   // chunks whose Z load was issued
   int rg[4];                  // this CTA's range of the chunk space (Range), written once at start
   alignas(16) float wsum[2][4];     // per-quadrant decay sums, by chunk parity like cs/bs
   // double-buffered by chunk parity: the next chunk's values are computed while the tensor cores
@@ -274,6 +281,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
   const bool rev = a.reverse != 0;
 
   const uint32_t bar_full = smem_u32(&sm->full[0]), bar_empty = smem_u32(&sm->empty[0]);
+  const uint32_t bar_fullz = smem_u32(&sm->fullz[0]), bar_emptyz = smem_u32(&sm->emptyz[0]);
   const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w);
   const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
   const uint32_t bar_t = smem_u32(&sm->bar_t), bar_y = smem_u32(&sm->bar_y);
@@ -288,6 +296,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_fullz + 8 * s, 1);
+      mbar_init(bar_emptyz + 8 * s, 1);
     }
     mbar_init(bar_p, 1);
     mbar_init(bar_w, 1);
@@ -300,6 +310,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
     mbar_init(bar_h, kComputeThreads);
     sm->abort_flag = 0;
     sm->issued = 0;
+    sm->issuedz = 0;
     const Range g = cta_range(a, sc, r_cta, r_cnt);
     sm->rg[0] = g.p_a; sm->rg[1] = g.p_b; sm->rg[2] = g.off_a; sm->rg[3] = g.end_b;
     fence_barrier_init();
@@ -320,7 +331,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       prefetch_tmap(map_x);
       prefetch_tmap(map_y);
       prefetch_tmap(map_z);
-      int g0 = 0;
+      int g0 = 0, nxy = 0, nz = 0;
       for (int k = 0; k < ntasks && !*abort_flag; ++k) {
         const Task tk = task_of(a, range(), k, ntasks);
         int it = 0;
@@ -329,22 +340,29 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           const int n = rev ? (tk.nc - 1 - (tk.it0 + it)) : (tk.it0 + it);
           const int s = gi & 1;
           const uint32_t ph = (uint32_t)(gi >> 1) & 1u;
+          const uint32_t dst = base + (uint32_t)s * kStageBytes;
+          const int tok0 = (int)tk.t_begin + n * kChunk;
           mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
           if (*abort_flag) break;
           const uint32_t fb = bar_full + 8 * s;
-          mbar_arrive_expect_tx(fb, 3 * kTileBytes);
-          const uint32_t dst = base + (uint32_t)s * kStageBytes;
-          const int tok0 = (int)tk.t_begin + n * kChunk;
+          mbar_arrive_expect_tx(fb, 2 * kTileBytes);
           tma_load_4d(dst, map_x, fb, 0, tk.h, tok0, tk.bidx);
           tma_load_4d(dst + kBoxBytes, map_x, fb, 64, tk.h, tok0, tk.bidx);
           tma_load_4d(dst + kTileBytes, map_y, fb, 0, tk.h, tok0, tk.bidx);
           tma_load_4d(dst + kTileBytes + kBoxBytes, map_y, fb, 64, tk.h, tok0, tk.bidx);
-          tma_load_4d(dst + 2 * kTileBytes, map_z, fb, 0, tk.h, tok0, tk.bidx);
-          tma_load_4d(dst + 2 * kTileBytes + kBoxBytes, map_z, fb, 64, tk.h, tok0, tk.bidx);
+          nxy = gi + 1;
+          mbar_wait(bar_emptyz + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmpty);
+          if (*abort_flag) break;
+          const uint32_t fz = bar_fullz + 8 * s;
+          mbar_arrive_expect_tx(fz, kTileBytes);
+          tma_load_4d(dst + 2 * kTileBytes, map_z, fz, 0, tk.h, tok0, tk.bidx);
+          tma_load_4d(dst + 2 * kTileBytes + kBoxBytes, map_z, fz, 64, tk.h, tok0, tk.bidx);
+          nz = gi + 1;
         }
         g0 += it;
       }
-      sm->issued = g0;
+      sm->issued = nxy;
+      sm->issuedz = nz;
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
@@ -399,12 +417,16 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
           // next chunk's state copy while P~ Z still runs
           mbar_wait(bar_y, par, abort_flag, a.status, kStY);
+          mbar_wait(bar_fullz + 8 * s, ph, abort_flag, a.status, kStFull);
           tc_fence_after();
           LA_TRACE(3);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
           mma_commit(bar_t);
+          // every product that reads this stage's X or Y has been issued: the producer may refill
+          // them (for the chunk after the next one) as soon as those products are done
+          mma_commit(bar_empty + 8 * s);
           mbar_wait(bar_f, par, abort_flag, a.status, kStF);
           tc_fence_after();
           LA_TRACE(4);
@@ -435,14 +457,14 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           const int L = min(kChunk, tk.len - n * kChunk);
           mbar_wait(bar_h, par, abort_flag, a.status, kStH);
           if (L == kChunk) {
-            const uint32_t xs = base + (uint32_t)s * kStageBytes;
+            const uint32_t zs = base + (uint32_t)s * kStageBytes + 2 * kTileBytes;
             const int tok0 = (int)tk.t_begin + n * kChunk;
-            tma_store_4d(map_o, xs, 0, tk.h, tok0, tk.bidx);
-            tma_store_4d(map_o, xs + kBoxBytes, 64, tk.h, tok0, tk.bidx);
+            tma_store_4d(map_o, zs, 0, tk.h, tok0, tk.bidx);
+            tma_store_4d(map_o, zs + kBoxBytes, 64, tk.h, tok0, tk.bidx);
             tma_store_commit();
             tma_store_wait_read();
           }
-          mbar_arrive(bar_empty + 8 * s);
+          mbar_arrive(bar_emptyz + 8 * s);
         }
         g0 += tk.cnt;
       }
@@ -803,8 +825,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
             v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
             if (full_chunk) {
-              // staging = this stage's X tile (dead once the MMAs above have completed)
-              *reinterpret_cast<uint4 *>(stage + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
+              // staging = this stage's Z tile (dead once the MMAs above have completed)
+              *reinterpret_cast<uint4 *>(stage + 2 * kTileBytes + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
             } else if (i < L) {
               reinterpret_cast<uint4 *>(static_cast<T *>(ap.out) + row_off + c0)[pc] = v;
             }
@@ -862,6 +884,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       int dummy = 0;
       for (int it = max(0, sm->issued - kStages); it < sm->issued; ++it)
         mbar_wait(bar_full + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, &dummy, nullptr, 0, 1u << 20);
+      for (int it = max(0, sm->issuedz - kStages); it < sm->issuedz; ++it)
+        mbar_wait(bar_fullz + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, &dummy, nullptr, 0, 1u << 20);
     }
     __syncwarp();
     tmem_dealloc(tmem, 512);
