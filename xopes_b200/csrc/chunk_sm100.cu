@@ -641,12 +641,20 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         for (int b2 = 0; b2 < 2; ++b2) {
           const int bt = 2 * wg + b2;
           uint32_t r[32];
+          if (src == nullptr) {
 #pragma unroll
-          for (int kk = 0; kk < 32; ++kk) {
-            const int c = bt * 32 + kk;
-            float v = 0.f;
-            if (src != nullptr) v = __ldcg(src + (src_tr ? (c * kChunk + i) : (i * kChunk + c)));
-            r[kk] = __float_as_uint(v);
+            for (int kk = 0; kk < 32; ++kk) r[kk] = 0u;
+          } else if (src_tr) {  // element (i, c) at c * 128 + i: a warp reads 128 contiguous bytes
+#pragma unroll
+            for (int kk = 0; kk < 32; ++kk) r[kk] = __float_as_uint(__ldcg(src + (bt * 32 + kk) * kChunk + i));
+          } else {              // row i contiguous: 16-byte loads
+            const float4 *row = reinterpret_cast<const float4 *>(src + i * kChunk + bt * 32);
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const float4 v = __ldcg(row + kk);
+              r[4 * kk + 0] = __float_as_uint(v.x); r[4 * kk + 1] = __float_as_uint(v.y);
+              r[4 * kk + 2] = __float_as_uint(v.z); r[4 * kk + 3] = __float_as_uint(v.w);
+            }
           }
           tmem_st32(tl + kColT + bt * 32, r);
         }
@@ -859,10 +867,15 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             uint32_t r[32];
             tmem_ld32(tl + kColT + bt * 32, r);
             tmem_wait_ld();
+            if (dst_tr) {
 #pragma unroll
-            for (int kk = 0; kk < 32; ++kk) {
-              const int c = bt * 32 + kk;
-              dst[dst_tr ? (c * kChunk + i) : (i * kChunk + c)] = __uint_as_float(r[kk]);
+              for (int kk = 0; kk < 32; ++kk) dst[(bt * 32 + kk) * kChunk + i] = __uint_as_float(r[kk]);
+            } else {
+              float4 *row = reinterpret_cast<float4 *>(dst + i * kChunk + bt * 32);
+#pragma unroll
+              for (int kk = 0; kk < 8; ++kk)
+                row[kk] = make_float4(__uint_as_float(r[4 * kk]), __uint_as_float(r[4 * kk + 1]),
+                                      __uint_as_float(r[4 * kk + 2]), __uint_as_float(r[4 * kk + 3]));
             }
           }
           if (tk.publishes) {
@@ -978,6 +991,7 @@ int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   if ((rc = make_map(&m.z, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&m.o, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if (p.xrow != nullptr && (reinterpret_cast<uintptr_t>(p.xrow) & 15u)) return LA_ERR_MISALIGNED;
+  if ((reinterpret_cast<uintptr_t>(p.t0) | reinterpret_cast<uintptr_t>(p.tfinal)) & 15u) return LA_ERR_MISALIGNED;
   a.xrow = p.xrow; a.rowdot = p.xrow ? p.rowdot : nullptr; a.out = p.out;
   a.ld = p.ld; a.ld_sb = p.ld_sb; a.ld_sn = p.ld_sn; a.ld_sh = p.ld_sh;
   a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
