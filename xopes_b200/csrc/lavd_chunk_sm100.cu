@@ -18,7 +18,10 @@
 // Structure as in chunk_sm100.cu (state resident in tensor memory, TMA producer / MMA issuer /
 // TMA store warps, bounded mbarrier waits, no multicast), but single-stage: the chunk's operands
 // are three 16-bit tiles plus the 64 KB fp32 decay tile, and two more tiles hold the 16-bit state
-// copy and the rescaled update operand, which fills shared memory.
+// copy and the rescaled update operand, which fills shared memory.  The stage goes back to the
+// producer piece by piece (decay tile, Y and Z, X), each when its last reader is done, and the
+// next chunk is pulled into L2 meanwhile, so that most of the load latency hides behind the rest
+// of the current chunk.
 #include <cuda.h>
 
 #include <cstddef>
@@ -40,7 +43,6 @@ constexpr int kCkBytes = 65536;
 constexpr int kOffTb = kOffCk + kCkBytes, kOffU = kOffTb + kTileBytes, kOffSmall = kOffU + kTileBytes;
 constexpr int kSmallBytes = 2048;
 constexpr int kSmemBytes = kOffSmall + kSmallBytes + 1024;
-constexpr int kLoadBytes = 3 * kTileBytes + kCkBytes;
 constexpr int kComputeThreads = 256;
 constexpr int kProducerWarp = 8, kMmaWarp = 9, kStoreWarp = 10;
 constexpr int kThreads = kComputeThreads + 96;
@@ -55,11 +57,15 @@ constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
 constexpr int kStFull = 301, kStEmpty = 302, kStP = 303, kStW = 304, kStD = 305, kStF = 306, kStH = 307, kStR = 308;
 
 struct Small {
-  unsigned long long full, empty, bar_p, bar_w, bar_r, bar_d, bar_f, bar_h;
+  // The single stage is handed back to the producer in three pieces, each as soon as its last
+  // reader is done: the decay tile (N mode: after the rescale; T mode: it stages the gradient
+  // terms and goes back with X), Y and Z (after the chunk's products), X (it stages the output
+  // tile and goes back once that has been stored).
+  unsigned long long full_ck, full_yz, full_x, empty_ck, empty_yz, empty_x;
+  unsigned long long bar_p, bar_w, bar_r, bar_d, bar_f, bar_h;
   uint32_t tmem_base;
   int abort_flag;
-  int issued;
-  int pad;
+  int issued[3];  // chunks whose decay tile / Y and Z / X loads were issued
   alignas(16) float uvec[kChunk];  // scale of the state-update operand per feature
   alignas(16) float cvec[kChunk];  // scale of the 16-bit state copy per feature
   alignas(16) float gfac[kChunk];  // e^g per feature: decay of the state over the chunk
@@ -182,14 +188,19 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const int nc = (len + kChunk - 1) / kChunk;
   const bool rev = a.reverse != 0;
 
-  const uint32_t bar_full = smem_u32(&sm->full), bar_empty = smem_u32(&sm->empty);
+  const uint32_t full_ck = smem_u32(&sm->full_ck), full_yz = smem_u32(&sm->full_yz), full_x = smem_u32(&sm->full_x);
+  const uint32_t empty_ck = smem_u32(&sm->empty_ck), empty_yz = smem_u32(&sm->empty_yz), empty_x = smem_u32(&sm->empty_x);
   const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w), bar_r = smem_u32(&sm->bar_r);
   const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
   volatile int *abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
-    mbar_init(bar_full, 1);
-    mbar_init(bar_empty, 1);
+    mbar_init(full_ck, 1);
+    mbar_init(full_yz, 1);
+    mbar_init(full_x, 1);
+    mbar_init(empty_ck, TMODE ? 1 : kComputeThreads);
+    mbar_init(empty_yz, 1);
+    mbar_init(empty_x, 1);
     mbar_init(bar_p, 1);
     mbar_init(bar_w, 1);
     mbar_init(bar_r, kComputeThreads);
@@ -197,7 +208,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     mbar_init(bar_f, kComputeThreads);
     mbar_init(bar_h, kComputeThreads);
     sm->abort_flag = 0;
-    sm->issued = 0;
+    sm->issued[0] = sm->issued[1] = sm->issued[2] = 0;
     fence_barrier_init();
   }
   if (warp == kProducerWarp) {
@@ -214,25 +225,40 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA loads (single stage)
     if (lane == 0) {
-      int it = 0;
-      for (; it < nc; ++it) {
+      int n_ck = 0, n_yz = 0, n_x = 0;
+      auto load_ck = [&](int tok0, uint32_t par) {
+        mbar_wait(empty_ck, par ^ 1u, abort_flag, a.status, kStEmpty);
+        if (*abort_flag) return false;
+        mbar_arrive_expect_tx(full_ck, kCkBytes);
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) tma_load_4d(cks + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+        ++n_ck;
+        return true;
+      };
+      for (int it = 0; it < nc; ++it) {
         const int n = rev ? (nc - 1 - it) : it;
         const uint32_t par = (uint32_t)it & 1u;
-        mbar_wait(bar_empty, par ^ 1u, abort_flag, a.status, kStEmpty);
-        if (*abort_flag) break;
-        mbar_arrive_expect_tx(bar_full, kLoadBytes);
         const int tok0 = (int)t_begin + n * kChunk;
-        tma_load_4d(xs, &map_x, bar_full, 0, h, tok0, bidx);
-        tma_load_4d(xs + kBoxBytes, &map_x, bar_full, 64, h, tok0, bidx);
-        tma_load_4d(ys, &map_y, bar_full, 0, h, tok0, bidx);
-        tma_load_4d(ys + kBoxBytes, &map_y, bar_full, 64, h, tok0, bidx);
-        tma_load_4d(zs, &map_z, bar_full, 0, h, tok0, bidx);
-        tma_load_4d(zs + kBoxBytes, &map_z, bar_full, 64, h, tok0, bidx);
-#pragma unroll
-        for (int gq = 0; gq < 4; ++gq) tma_load_4d(cks + gq * kBoxBytes, &map_ld, bar_full, 32 * gq, h, tok0, bidx);
-        // The stage is single-buffered, so the next chunk's loads start only when this chunk is
-        // stored and the CTA then waits out their full latency; pulling that chunk into L2 now
-        // shortens the wait (the pass uses a fraction of the HBM bandwidth, so this costs nothing).
+        // in the order in which the pieces come free
+        if (!TMODE && !load_ck(tok0, par)) break;
+        mbar_wait(empty_yz, par ^ 1u, abort_flag, a.status, kStEmpty);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(full_yz, 2 * kTileBytes);
+        tma_load_4d(ys, &map_y, full_yz, 0, h, tok0, bidx);
+        tma_load_4d(ys + kBoxBytes, &map_y, full_yz, 64, h, tok0, bidx);
+        tma_load_4d(zs, &map_z, full_yz, 0, h, tok0, bidx);
+        tma_load_4d(zs + kBoxBytes, &map_z, full_yz, 64, h, tok0, bidx);
+        ++n_yz;
+        mbar_wait(empty_x, par ^ 1u, abort_flag, a.status, kStEmpty);
+        if (*abort_flag) break;
+        mbar_arrive_expect_tx(full_x, kTileBytes);
+        tma_load_4d(xs, &map_x, full_x, 0, h, tok0, bidx);
+        tma_load_4d(xs + kBoxBytes, &map_x, full_x, 64, h, tok0, bidx);
+        ++n_x;
+        if (TMODE && !load_ck(tok0, par)) break;
+        // The stage is single-buffered, so the next chunk's loads start only as its pieces come
+        // free and the CTA then waits out their latency; pulling that chunk into L2 now shortens
+        // the wait (the pass uses a fraction of the HBM bandwidth, so this costs nothing).
         if (it + 1 < nc) {
           const int tokp = (int)t_begin + (rev ? (n - 1) : (n + 1)) * kChunk;
           tma_prefetch_4d(&map_x, 0, h, tokp, bidx);
@@ -245,7 +271,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           for (int gq = 0; gq < 4; ++gq) tma_prefetch_4d(&map_ld, 32 * gq, h, tokp, bidx);
         }
       }
-      sm->issued = it;
+      sm->issued[0] = n_ck;
+      sm->issued[1] = n_yz;
+      sm->issued[2] = n_x;
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
@@ -259,7 +287,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint64_t d_umn = desc_mnmajor(us, kBoxBytes);
       for (int it = 0; it < nc; ++it) {
         const uint32_t par = (uint32_t)it & 1u;
-        mbar_wait(bar_full, par, abort_flag, a.status, kStFull);
+        mbar_wait(full_x, par, abort_flag, a.status, kStFull);
+        mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
         // N mode multiplies the rescaled X and Y; T mode the tiles as loaded
         if (!TMODE) mbar_wait(bar_r, par, abort_flag, a.status, kStR);
         tc_fence_after();
@@ -291,6 +320,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
                  idesc_kmn, ks > 0);
         mma_commit(bar_w);
+        mma_commit(empty_yz);  // Y and Z have no reader left once the products above are done
         mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       }
     }
@@ -319,7 +349,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tma_store_commit();
           tma_store_wait_read();
         }
-        mbar_arrive(bar_empty);
+        mbar_arrive(empty_x);
+        if (TMODE) mbar_arrive(empty_ck);
       }
       tma_store_wait_all();
     }
@@ -353,7 +384,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
 
-      mbar_wait(bar_full, par, abort_flag, a.status, kStFull);
+      mbar_wait(full_ck, par, abort_flag, a.status, kStFull);
 
       // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
       // Thread (dg = tid % 32, seg = tid / 32) scans the four features [4 dg, 4 dg + 4) over the
@@ -362,17 +393,19 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int dg = tid & 31, seg = tid >> 5, d0 = dg * 4;
         const uint32_t colbase = (uint32_t)(d0 >> 5) * kBoxBytes;
         const uint32_t c4 = (uint32_t)((d0 & 31) >> 2);
+        // the sixteen running sums stay in registers between the two sweeps: one load and one
+        // store per row and no read-back
+        float4 acc16[16];
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
           const int row = seg * 16 + r;  // row & 7 == r & 7
-          float4 *p = reinterpret_cast<float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
           if (row < L) {
-            const float4 v = *p;
+            const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
             run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
             run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
           }
-          *p = run;
+          acc16[r] = run;
         }
         *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = run;
         named_bar_sync(1, kComputeThreads);
@@ -389,10 +422,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
           const int row = seg * 16 + r;
-          float4 *p = reinterpret_cast<float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-          float4 v = *p;
+          float4 v = acc16[r];
           v.x += sh.x; v.y += sh.y; v.z += sh.z; v.w += sh.w;
-          *p = v;
+          *reinterpret_cast<float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4)) = v;
         }
         if (seg == 0) {
           const float mm[4] = {m.x, m.y, m.z, m.w}, gg[4] = {g.x, g.y, g.z, g.w};
@@ -410,6 +442,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
 
       // ---- R: rescale operands in place, build the state-update operand U
+      mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
+      if (!TMODE) mbar_wait(full_x, par, abort_flag, a.status, kStFull);
       if (!TMODE) {
         if (rev) rescale_xy<T, true>(gbase, ck, sm->uvec, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
         else rescale_xy<T, false>(gbase, ck, sm->uvec, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
@@ -419,6 +453,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       fence_proxy_async();
       mbar_arrive(bar_r);
+      if (!TMODE) mbar_arrive(empty_ck);  // N mode reads the decay tile for the last time above
 
       // ---- D: scaled 16-bit state copy (B operand of X T), decay of the resident state
       {
@@ -607,8 +642,10 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (warp == kProducerWarp) {
     if (lane == 0 && sm->abort_flag != 0) {
       int dummy = 0;
-      if (sm->issued > 0)
-        mbar_wait(bar_full, (uint32_t)(sm->issued - 1) & 1u, &dummy, nullptr, 0, 1u << 20);
+      const uint32_t fulls[3] = {full_ck, full_yz, full_x};
+      for (int gq = 0; gq < 3; ++gq)
+        if (sm->issued[gq] > 0)
+          mbar_wait(fulls[gq], (uint32_t)(sm->issued[gq] - 1) & 1u, &dummy, nullptr, 0, 1u << 20);
     }
     __syncwarp();
     tmem_dealloc(tmem, 512);
