@@ -58,9 +58,10 @@ constexpr int kStFull = 301, kStEmpty = 302, kStP = 303, kStW = 304, kStD = 305,
 
 struct Small {
   // The single stage is handed back to the producer in three pieces, each as soon as its last
-  // reader is done: the decay tile (N mode: after the rescale; T mode: it stages the gradient
-  // terms and goes back with X), Y and Z (after the chunk's products), X (it stages the output
-  // tile and goes back once that has been stored).
+  // reader is done: the decay tile (N mode: after the rescale; T mode: after the epilogue, which
+  // scales by it), Y and Z (N mode: after the chunk's products; T mode: they stage the gradient
+  // terms and go back once those have been stored), X (it stages the output tile and goes back
+  // once that has been stored).
   unsigned long long full_ck, full_yz, full_x, empty_ck, empty_yz, empty_x;
   unsigned long long bar_p, bar_w, bar_r, bar_d, bar_f, bar_h;
   uint32_t tmem_base;
@@ -198,7 +199,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     mbar_init(full_ck, 1);
     mbar_init(full_yz, 1);
     mbar_init(full_x, 1);
-    mbar_init(empty_ck, TMODE ? 1 : kComputeThreads);
+    mbar_init(empty_ck, kComputeThreads);
     mbar_init(empty_yz, 1);
     mbar_init(empty_x, 1);
     mbar_init(bar_p, 1);
@@ -240,7 +241,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t par = (uint32_t)it & 1u;
         const int tok0 = (int)t_begin + n * kChunk;
         // in the order in which the pieces come free
-        if (!TMODE && !load_ck(tok0, par)) break;
+        if (!load_ck(tok0, par)) break;
         mbar_wait(empty_yz, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(full_yz, 2 * kTileBytes);
@@ -255,7 +256,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tma_load_4d(xs, &map_x, full_x, 0, h, tok0, bidx);
         tma_load_4d(xs + kBoxBytes, &map_x, full_x, 64, h, tok0, bidx);
         ++n_x;
-        if (TMODE && !load_ck(tok0, par)) break;
         // The stage is single-buffered, so the next chunk's loads start only as its pieces come
         // free and the CTA then waits out their latency; pulling that chunk into L2 now shortens
         // the wait (the pass uses a fraction of the HBM bandwidth, so this costs nothing).
@@ -320,7 +320,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
                  idesc_kmn, ks > 0);
         mma_commit(bar_w);
-        mma_commit(empty_yz);  // Y and Z have no reader left once the products above are done
+        // N mode: Y and Z have no reader left once the products above are done (in T mode they
+        // go on to stage the gradient terms and the store warp hands them back)
+        if (!TMODE) mma_commit(empty_yz);
         mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       }
     }
@@ -338,19 +340,19 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
           tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
           if (TMODE && a.dld != nullptr) {
-            // the decay tile now holds this chunk's log-decay-gradient terms: store (dq pass) or
+            // the Y and Z tiles now hold this chunk's log-decay-gradient terms: store (dq pass) or
             // add the negated terms (dk pass) as four fp32 boxes
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
-              if (a.dld_sub) tma_reduce_add_4d(&map_dld, cks + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
-              else tma_store_4d(&map_dld, cks + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              if (a.dld_sub) tma_reduce_add_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              else tma_store_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
             }
           }
           tma_store_commit();
           tma_store_wait_read();
         }
         mbar_arrive(empty_x);
-        if (TMODE) mbar_arrive(empty_ck);
+        if (TMODE) mbar_arrive(empty_yz);
       }
       tma_store_wait_all();
     }
@@ -583,12 +585,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             float4 lo = make_float4(xs[0] * w[pc * 8 + 0], xs[1] * w[pc * 8 + 1], xs[2] * w[pc * 8 + 2], xs[3] * w[pc * 8 + 3]);
             float4 hi = make_float4(xs[4] * w[pc * 8 + 4], xs[5] * w[pc * 8 + 5], xs[6] * w[pc * 8 + 6], xs[7] * w[pc * 8 + 7]);
             if (full_chunk) {
-              // stage in the decay tile (this thread's row, columns already consumed above); the
-              // store warp writes the tile out with TMA
+              // stage in the Y and Z tiles (64 KB, free once the chunk's products are done) in
+              // the layout of the decay tile; the store warp writes them out with TMA
               const float sg = a.dld_sub ? -1.f : 1.f;
               const int d0 = bt * 32 + pc * 8;
-              *reinterpret_cast<float4 *>(ck + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
-              *reinterpret_cast<float4 *>(ck + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
+              uint8_t *stg = gbase + kOffY;
+              *reinterpret_cast<float4 *>(stg + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
+              *reinterpret_cast<float4 *>(stg + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
               continue;
             }
             if (a.dld_sub) {
@@ -618,6 +621,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       if (full_chunk) fence_proxy_async();
       tc_fence_before();
+      if (TMODE) mbar_arrive(empty_ck);  // T mode reads the decay tile for the last time above
       mbar_arrive(bar_h);
     }
 
