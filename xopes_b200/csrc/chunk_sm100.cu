@@ -1032,12 +1032,10 @@ int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t str
   sc.flags = nullptr;
   long long grid = pairs * npass;
   void *scratch = nullptr;
-  // Worth it when whole pairs per CTA would leave SMs idle in the last round.  Many ragged
-  // documents spread well enough by themselves (CTAs start as SMs free up) and keep neighbouring
-  // heads in step, which the even split does not.
-  const bool uneven = p.cu ? pairs <= 2LL * ranges : true;
+  // Worth it when whole pairs per CTA would leave SMs idle in the last round (always the case
+  // with ragged documents).
   if (!p.no_scratch && !(sched_knob() & 1) && g_trace == nullptr && di->pool != nullptr && ranges > 0 &&
-      pairs > ranges && pairs % ranges != 0 && uneven) {
+      pairs > ranges && (p.cu != nullptr || pairs % ranges != 0)) {
     // even split of the chunk space over one CTA per SM
     grid = (long long)ranges * npass;
     const size_t flag_bytes = round_up((size_t)grid * sizeof(int), 256);
