@@ -386,6 +386,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
 
+      if (TMODE && a.dld != nullptr && i < L) {
+        // the epilogue multiplies the output by this row of xrow, read from global memory: start
+        // that fetch now (one 128-byte line per thread) so that it is in cache by then
+        const char *xr = reinterpret_cast<const char *>(static_cast<const T *>(a.xrow) +
+                                                          ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk + wg * 64);
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(xr));
+      }
       mbar_wait(full_ck, par, abort_flag, a.status, kStFull);
 
       // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
