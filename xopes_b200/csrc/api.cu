@@ -42,8 +42,8 @@ namespace {
 // everything already queued on the caller's stream, join() makes the caller's stream wait for the
 // side stream.  One caller at a time per device: the lock is held from fork to join.
 struct SideStream {
-  cudaStream_t stream = nullptr;
-  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  cudaStream_t stream = nullptr, stream2 = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr, join_ev2 = nullptr;
   std::mutex mu;
   bool ready = false, failed = false;
 };
@@ -57,8 +57,10 @@ SideStream *side_stream() {
   SideStream &s = side[dev];
   if (!s.ready && !s.failed) {
     if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&s.stream2, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&s.fork_ev, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&s.join_ev, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&s.join_ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join_ev2, cudaEventDisableTiming) != cudaSuccess) {
       s.failed = true;
       cudaGetLastError();
     } else {
@@ -73,6 +75,11 @@ bool side_fork(SideStream *s, cudaStream_t st) {
 }
 bool side_join(SideStream *s, cudaStream_t st) {
   return cudaEventRecord(s->join_ev, s->stream) == cudaSuccess && cudaStreamWaitEvent(st, s->join_ev, 0) == cudaSuccess;
+}
+// the second side stream, forked from the same event (call side_fork first)
+bool side_fork2(SideStream *s) { return cudaStreamWaitEvent(s->stream2, s->fork_ev, 0) == cudaSuccess; }
+bool side_join2(SideStream *s, cudaStream_t st) {
+  return cudaEventRecord(s->join_ev2, s->stream2) == cudaSuccess && cudaStreamWaitEvent(st, s->join_ev2, 0) == cudaSuccess;
 }
 
 int sm_count() {
@@ -445,31 +452,46 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
     // with the other two passes, so while one CTA per (sequence, head) leaves SMs idle it runs
-    // beside them on the side stream.
+    // beside them on a side stream.
     LavdPass cv = c;
     cv.x = k; cv.y = q; cv.z = d_o; cv.out = dv; cv.tmode = 0; cv.state_transposed = 0; cv.reverse = 1;
     cv.t0 = dfinal_state; cv.tfinal = dinitial_state; cv.xrow = nullptr; cv.dld = nullptr;
-    SideStream *side = (2 * (int64_t)s.nb() * s.H <= sm_count() + sm_count() / 2) ? side_stream() : nullptr;
-    std::unique_lock<std::mutex> side_lock;
-    if (side != nullptr) {
-      side_lock = std::unique_lock<std::mutex>(side->mu);
-      if (!side_fork(side, st)) return LA_ERR_CUDA;
-      rc = launch_lavd_pass(cv, dtype, side->stream);
-      if (rc != LA_OK) { side_join(side, st); return rc; }
-    }
     // dq: (do, v, k), state S^T, forward; dldk = q * dq
-    c.x = d_o; c.y = v; c.z = k; c.out = dq; c.tmode = 1; c.state_transposed = 1; c.reverse = 0;
-    c.t0 = initial_state; c.tfinal = ws_state; c.xrow = q; c.dld = dldk; c.dld_sub = 0;
-    rc = launch_lavd_pass(c, dtype, st);
+    LavdPass cq = c;
+    cq.x = d_o; cq.y = v; cq.z = k; cq.out = dq; cq.tmode = 1; cq.state_transposed = 1; cq.reverse = 0;
+    cq.t0 = initial_state; cq.tfinal = ws_state; cq.xrow = q; cq.dld = dldk; cq.dld_sub = 0;
     // dk: (v, do, q), state dS^T, reverse; dldk -= k * dk
-    c.x = v; c.y = d_o; c.z = q; c.out = dk; c.reverse = 1;
-    c.t0 = dfinal_state; c.tfinal = nullptr; c.xrow = k; c.dld_sub = 1;
-    if (rc == LA_OK) rc = launch_lavd_pass(c, dtype, st);
-    if (side != nullptr) {
+    LavdPass ck = cq;
+    ck.x = v; ck.y = d_o; ck.z = q; ck.out = dk; ck.reverse = 1;
+    ck.t0 = dfinal_state; ck.tfinal = nullptr; ck.xrow = k; ck.dld_sub = 1;
+    const int64_t pairs = (int64_t)s.nb() * s.H;
+    SideStream *side = (2 * pairs <= sm_count() + sm_count() / 2) ? side_stream() : nullptr;
+    // With room for the dq and dk passes at once (2 x pairs <= SMs) all three run side by side:
+    // dq then adds to a zeroed gradient buffer instead of storing into it, so that it and dk may
+    // touch a tile in either order.
+    const bool all3 = side != nullptr && 2 * pairs <= sm_count();
+    if (side == nullptr) {
+      rc = launch_lavd_pass(cq, dtype, st);
+      if (rc == LA_OK) rc = launch_lavd_pass(ck, dtype, st);
+      if (rc == LA_OK) rc = launch_lavd_pass(cv, dtype, st);
+    } else {
+      std::unique_lock<std::mutex> side_lock(side->mu);
+      if (all3) {
+        cq.dld_add = ck.dld_add = 1;
+        if (cudaMemsetAsync(dldk, 0, (size_t)B * N * H * D * sizeof(float), st) != cudaSuccess) return LA_ERR_CUDA;
+      }
+      if (!side_fork(side, st) || (all3 && !side_fork2(side))) return LA_ERR_CUDA;
+      if (all3) {
+        rc = launch_lavd_pass(cq, dtype, side->stream);
+        if (rc == LA_OK) rc = launch_lavd_pass(ck, dtype, st);
+        if (rc == LA_OK) rc = launch_lavd_pass(cv, dtype, side->stream2);
+        if (!side_join2(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
+      } else {
+        rc = launch_lavd_pass(cv, dtype, side->stream);
+        if (rc == LA_OK) rc = launch_lavd_pass(cq, dtype, st);
+        if (rc == LA_OK) rc = launch_lavd_pass(ck, dtype, st);
+      }
       if (!side_join(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
-      side_lock.unlock();
-    } else if (rc == LA_OK) {
-      rc = launch_lavd_pass(cv, dtype, st);
     }
     if (rc != LA_OK) return rc;
     enable = unsafe;

@@ -49,7 +49,8 @@ struct LavdPass {
   void *out = nullptr;
   const void *xrow = nullptr;
   float *dld = nullptr;
-  int dld_sub = 0;
+  int dld_sub = 0;   // 1: the terms are subtracted from dld (dk pass) instead of stored (dq pass)
+  int dld_add = 0;   // 1: dld starts at zero and both passes add to it atomically (they may overlap)
   const float *t0 = nullptr;
   float *tfinal = nullptr;
   int state_transposed = 0, reverse = 0, tmode = 0;

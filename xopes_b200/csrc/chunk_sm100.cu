@@ -687,7 +687,16 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           ld_next = load_ld(it + 2);
         }
         LA_TRACE(1);
-        if (split) state_copy_low(cur.eg, par);
+        if (split) {
+          // the epilogue dots the output with this row of xrow, read from global memory: start
+          // that fetch now (one 128-byte line per thread) so that it is in cache by then
+          if (i < L) {
+            const char *xr = reinterpret_cast<const char *>(static_cast<const T *>(ap.xrow) + row_base +
+                                                              (long long)n * kChunk * a.H * kChunk + 64 * wg);
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(xr));
+          }
+          state_copy_low(cur.eg, par);
+        }
         // ---- Y <- Y (.) u in place (this warpgroup's 64 columns), once X Y^T has consumed Y
         mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
         mbar_wait(bar_p, par, abort_flag, a.status, kStP);

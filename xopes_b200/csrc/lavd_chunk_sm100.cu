@@ -78,6 +78,7 @@ struct LavdArgs {
   const void *xrow;   // T mode: tensor multiplied into the output for the log-decay gradient
   float *dld;         // T mode: (B,N,H,128) fp32 accumulator, stored (dld_sub = 0) or decremented
   int dld_sub;
+  int dld_add;        // both passes add to a zeroed buffer (TMA reduce / atomics): order-free
   const float *t0;
   float *tfinal;
   int state_transposed, reverse;
@@ -344,7 +345,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             // add the negated terms (dk pass) as four fp32 boxes
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
-              if (a.dld_sub) tma_reduce_add_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              if (a.dld_sub || a.dld_add) tma_reduce_add_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
               else tma_store_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
             }
           }
@@ -601,6 +602,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               *reinterpret_cast<float4 *>(stg + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
               continue;
             }
+            if (a.dld_add) {  // the twin pass may be on this tile too
+              const float sg = a.dld_sub ? -1.f : 1.f;
+              float *dpf = reinterpret_cast<float *>(dp + pc * 2);
+              atomicAdd(dpf + 0, sg * lo.x); atomicAdd(dpf + 1, sg * lo.y); atomicAdd(dpf + 2, sg * lo.z); atomicAdd(dpf + 3, sg * lo.w);
+              atomicAdd(dpf + 4, sg * hi.x); atomicAdd(dpf + 5, sg * hi.y); atomicAdd(dpf + 6, sg * hi.z); atomicAdd(dpf + 7, sg * hi.w);
+              continue;
+            }
             if (a.dld_sub) {
               const float4 ol = dp[pc * 2], oh = dp[pc * 2 + 1];
               lo = make_float4(ol.x - lo.x, ol.y - lo.y, ol.z - lo.z, ol.w - lo.w);
@@ -679,7 +687,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
                      LA_F32, p.B, p.N, p.H)) != LA_OK)
     return rc;
   LavdArgs a;
-  a.out = p.out; a.xrow = p.xrow; a.dld = p.xrow ? p.dld : nullptr; a.dld_sub = p.dld_sub;
+  a.out = p.out; a.xrow = p.xrow; a.dld = p.xrow ? p.dld : nullptr; a.dld_sub = p.dld_sub; a.dld_add = p.dld_add;
   a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
