@@ -512,12 +512,12 @@ def main():
             tensor_path = _lib.load().la_lasd_path(cfg["N"], cfg["D"], cfg["E"], _lib.LA_BF16, 0)
         # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
         # under profiles/, taken on a smaller case and scaled by token*heads (traffic is linear in
-        # them), 8*2048*32 token-heads: o pass 555.4 MB, dq pass 547.5 MB, merged dk/dv launch
-        # 792.3 MB = 1204.9 B per token-head per launch on average; the o pass alone 1059.4 B
+        # them), 8*2048*32 token-heads: o pass 561.3 MB, dq pass 551.4 MB, merged dk/dv launch
+        # 798.8 MB = 1215.3 B per token-head per launch on average; the o pass alone 1070.6 B
         traffic = None
         if args.workload in ("C2", "C5") and (tensor_path == 1 or args.workload == "C5"):
             th = cfg["N"] * cfg["H"] * (cfg.get("B", 1) if args.workload == "C2" else 1.0 / world)
-            traffic = (1204.9 if args.workload == "C2" else 1059.4) * th
+            traffic = (1215.3 if args.workload == "C2" else 1070.6) * th
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
                 "peak_source": peaks["source"],

@@ -14,11 +14,13 @@
 
 #include "chunk.cuh"
 #include "sm100_ptx.cuh"
+#include "tile_common.cuh"
 
 namespace la {
 namespace {
 
 using namespace ptx;
+using namespace tile;
 
 // ------------------------------------------------------------------------------------------------
 // generic fp32 path: one thread per (token, head, e)
@@ -49,28 +51,6 @@ struct SmallC {
   unsigned long long full, done;
   uint32_t tmem_base;
   int abort_flag;
-};
-
-template <typename T> struct FmtC;
-template <> struct FmtC<__nv_bfloat16> {
-  static constexpr uint32_t kAB = 1;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-  }
-  static __device__ __forceinline__ float2 unpack(uint32_t u) {
-    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u));
-  }
-};
-template <> struct FmtC<__half> {
-  static constexpr uint32_t kAB = 0;
-  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-    __half2 v = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-  }
-  static __device__ __forceinline__ float2 unpack(uint32_t u) {
-    return __half22float2(*reinterpret_cast<__half2 *>(&u));
-  }
 };
 
 // grid (tiles, H); 128 threads.  q is (1, N, H, 128).  Without a segment table tokens [0, T1) are
@@ -128,8 +108,8 @@ seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *
     for (int pc = 0; pc < 16; ++pc) {
       const float4 a = src[pc * 2], b = src[pc * 2 + 1];
       uint4 v;
-      v.x = FmtC<T>::pack(a.x, a.y); v.y = FmtC<T>::pack(a.z, a.w);
-      v.z = FmtC<T>::pack(b.x, b.y); v.w = FmtC<T>::pack(b.z, b.w);
+      v.x = Fmt<T>::pack(a.x, a.y); v.y = Fmt<T>::pack(a.z, a.w);
+      v.z = Fmt<T>::pack(b.x, b.y); v.w = Fmt<T>::pack(b.z, b.w);
       *reinterpret_cast<uint4 *>(gbase + kTile + (pc >> 3) * kBox + sw128_offset(tid, pc & 7)) = v;
     }
   }
@@ -139,7 +119,7 @@ seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *
   __syncthreads();
   if (tid == 0) {
     tc_fence_after();
-    const uint32_t idesc = instr_desc(FmtC<T>::kAB, 0, 1, 128, 128);
+    const uint32_t idesc = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks)
       mma_ss(tmem, desc_kmajor(qs + (uint32_t)(ks >> 2) * kBox + (uint32_t)(ks & 3) * 32u),
@@ -167,10 +147,10 @@ seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *
       for (int pc = 0; pc < 4; ++pc) {
         uint4 v = op[pc];
         float2 f;
-        f = FmtC<T>::unpack(v.x); v.x = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 0]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 1]), f.y));
-        f = FmtC<T>::unpack(v.y); v.y = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 2]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 3]), f.y));
-        f = FmtC<T>::unpack(v.z); v.z = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 4]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 5]), f.y));
-        f = FmtC<T>::unpack(v.w); v.w = FmtC<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 6]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 7]), f.y));
+        f = Fmt<T>::unpack(v.x); v.x = Fmt<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 0]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 1]), f.y));
+        f = Fmt<T>::unpack(v.y); v.y = Fmt<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 2]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 3]), f.y));
+        f = Fmt<T>::unpack(v.z); v.z = Fmt<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 4]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 5]), f.y));
+        f = Fmt<T>::unpack(v.w); v.w = Fmt<T>::pack(fmaf(w, __uint_as_float(r[pc * 8 + 6]), f.x), fmaf(w, __uint_as_float(r[pc * 8 + 7]), f.y));
         op[pc] = v;
       }
     }
@@ -180,37 +160,11 @@ seqpar_correct_tc(const __grid_constant__ CUtensorMap map_q, T *o, const float *
   if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-int make_q_map(CUtensorMap *m, const void *ptr, int dtype, int N, int H) {
-  static EncodeTiledFn enc = nullptr;
-  if (enc == nullptr) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult qr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
-        qr != cudaDriverEntryPointSuccess)
-      return LA_ERR_CUDA;
-    enc = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
-  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, 1};
-  const cuuint64_t strides[3] = {256, (cuuint64_t)H * 256, (cuuint64_t)N * H * 256};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapDataType dt = dtype == LA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
-}
-
 template <typename T>
 int launch_tc(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H, int dtype,
               cudaStream_t st, const int *seg = nullptr, int nseg = 0, int total_tiles = 0) {
   alignas(64) CUtensorMap mq;
-  int rc = make_q_map(&mq, q, dtype, N, H);
+  int rc = make_map(&mq, q, dtype, 1, N, H);  // (1, N, H, 128) 16-bit, boxes of 128 tokens x 64 features
   if (rc != LA_OK) return rc;
   if ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(s_in)) & 15u) return LA_ERR_MISALIGNED;
   int *status = status_word_ptr();
