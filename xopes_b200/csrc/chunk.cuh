@@ -71,6 +71,7 @@ int launch_seqpar_correct_multi(const void *q, void *o, const float *cum, const 
                                 int nseg, int total_tiles, int N, int H, int dtype, cudaStream_t st);
 // phase timestamps of CTA 0 (2 x 4096 x 16 int64) are written to buf by later passes; null disables
 void chunk_set_trace(long long *buf);
+long long *chunk_get_trace();
 // one 128x128x128 product through one operand staging variant (see chunk_sm100.cu)
 int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream);
 

@@ -1201,6 +1201,7 @@ int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, c
 }
 
 void chunk_set_trace(long long *buf) { g_trace = buf; }
+long long *chunk_get_trace() { return g_trace; }
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
   return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;

@@ -86,7 +86,18 @@ struct LavdArgs {
   int B, N, H, M;
   int *status;
   int *unsafe;
+  long long *trace;  // optional: clock64() at phase boundaries of CTA 0, thread 0: [pass][chunk < 1024][16]
 };
+
+#ifdef LA_CHUNK_TRACE
+#define LV_TRACE(point)                                                              \
+  do {                                                                               \
+    if (a.trace != nullptr && blockIdx.x == 0 && tid == 0 && it < 1024)              \
+      a.trace[(((TMODE ? 1 : 0) + 2 * a.reverse) * 1024 + it) * 16 + (point)] = clock64(); \
+  } while (0)
+#else
+#define LV_TRACE(point) do { } while (0)
+#endif
 
 // byte offset of the float4 holding features [d, d+4) of row i in the 128B-swizzled fp32 decay tile
 __device__ __forceinline__ uint32_t ck_off(int i, int d) {
@@ -387,6 +398,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
 
+      LV_TRACE(0);
       if (TMODE && a.dld != nullptr && i < L) {
         // the epilogue multiplies the output by this row of xrow, read from global memory: start
         // that fetch now (one 128-byte line per thread) so that it is in cache by then
@@ -395,6 +407,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         asm volatile("prefetch.global.L1 [%0];" ::"l"(xr));
       }
       mbar_wait(full_ck, par, abort_flag, a.status, kStFull);
+      LV_TRACE(1);
 
       // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
       // Thread (dg = tid % 32, seg = tid / 32) scans the four features [4 dg, 4 dg + 4) over the
@@ -451,6 +464,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         named_bar_sync(1, kComputeThreads);
       }
 
+      LV_TRACE(2);
       // ---- R: rescale operands in place, build the state-update operand U
       mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
       if (!TMODE) mbar_wait(full_x, par, abort_flag, a.status, kStFull);
@@ -464,6 +478,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       fence_proxy_async();
       mbar_arrive(bar_r);
       if (!TMODE) mbar_arrive(empty_ck);  // N mode reads the decay tile for the last time above
+      LV_TRACE(3);
 
       // ---- D: scaled 16-bit state copy (B operand of X T), decay of the resident state
       {
@@ -516,9 +531,11 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         mbar_arrive(bar_d);
       }
 
+      LV_TRACE(4);
       // ---- F: causal (or reverse-causal) 16-bit P~ in the first 16 columns of each 32-column batch
       mbar_wait(bar_p, par, abort_flag, a.status, kStP);
       tc_fence_after();
+      LV_TRACE(5);
 #pragma unroll 1
       for (int b2 = 0; b2 < 2; ++b2) {
         const int bt = wg + 2 * b2;
@@ -531,14 +548,20 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           uint32_t r[32];
           tmem_ld32(tl + kColP + bt * 32, r);
           tmem_wait_ld();
+          // bit k of `keep`: column 32 bt + k of this row survives the (reverse-)causal mask
+          const int lo = i - bt * 32;      // forward: columns k <= lo; reverse: columns k >= lo ...
+          const int hi = L - bt * 32;      // ... and k < hi (end of the sequence)
+          uint32_t keep;
+          if (!rev) keep = lo >= 31 ? 0xffffffffu : (lo < 0 ? 0u : (0xffffffffu >> (31 - lo)));
+          else {
+            keep = lo <= 0 ? 0xffffffffu : (lo > 31 ? 0u : (0xffffffffu << lo));
+            if (hi < 32) keep &= hi <= 0 ? 0u : (0xffffffffu >> (32 - hi));
+          }
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
-            const int j = bt * 32 + k;
-            bool k0, k1;
-            if (!rev) { k0 = j <= i; k1 = j + 1 <= i; }
-            else { k0 = (j >= i) && (j < L); k1 = (j + 1 >= i) && (j + 1 < L); }
             // select, not multiply: masked-out entries may be inf or NaN
-            pk[k >> 1] = Fmt<T>::pack(k0 ? __uint_as_float(r[k]) : 0.f, k1 ? __uint_as_float(r[k + 1]) : 0.f);
+            pk[k >> 1] = Fmt<T>::pack(((keep >> k) & 1u) ? __uint_as_float(r[k]) : 0.f,
+                                      ((keep >> (k + 1)) & 1u) ? __uint_as_float(r[k + 1]) : 0.f);
           }
         }
         tmem_st16(tl + kColP + bt * 32, pk);
@@ -547,9 +570,11 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_before();
       mbar_arrive(bar_f);
 
+      LV_TRACE(6);
       // ---- H: epilogue
       mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       tc_fence_after();
+      LV_TRACE(7);
       const bool full_chunk = (L == kChunk);
       const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
       const float so = rev ? -1.f : 1.f;
@@ -638,6 +663,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_before();
       if (TMODE) mbar_arrive(empty_ck);  // T mode reads the decay tile for the last time above
       mbar_arrive(bar_h);
+      LV_TRACE(8);
     }
 
     if (a.tfinal != nullptr) {  // end state -> global
@@ -693,6 +719,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
   a.status = status_word_ptr();
   a.unsafe = p.unsafe;
+  a.trace = chunk_get_trace();
   if (a.status == nullptr || a.unsafe == nullptr) return LA_ERR_CUDA;
   auto kern = lavd_pass_kernel<T, TMODE>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
