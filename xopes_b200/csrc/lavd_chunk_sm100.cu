@@ -58,10 +58,12 @@ constexpr int kStFull = 301, kStEmpty = 302, kStP = 303, kStW = 304, kStD = 305,
 
 struct Small {
   // The single stage is handed back to the producer in three pieces, each as soon as its last
-  // reader is done: the decay tile (N mode: after the rescale; T mode: after the epilogue, which
-  // scales by it), Y and Z (N mode: after the chunk's products; T mode: they stage the gradient
-  // terms and go back once those have been stored), X (it stages the output tile and goes back
-  // once that has been stored).
+  // reader is done.  N mode: the decay tile after the rescale, Y and Z after the chunk's
+  // products, X (which stages the output tile) once that has been stored.  T mode needs the decay
+  // tile until the epilogue (it scales by it and then stages the gradient terms in it), so there
+  // the two 64 KB regions -- decay tile, Y and Z -- swap roles from chunk to chunk: when the
+  // chunk's products are done the next chunk's decay tile is loaded where Y and Z were, and after
+  // the store the next chunk's Y and Z go where the decay tile was.
   unsigned long long full_ck, full_yz, full_x, empty_ck, empty_yz, empty_x;
   unsigned long long bar_p, bar_w, bar_r, bar_d, bar_f, bar_h;
   uint32_t tmem_base;
@@ -162,7 +164,8 @@ __device__ __forceinline__ void rescale_xy(uint8_t *gbase, const uint8_t *ck, co
   }
 }
 template <typename T, bool NEG>
-__device__ __forceinline__ void rescale_z(uint8_t *gbase, const uint8_t *ck, const float *uvec, int i, int wg, int L) {
+__device__ __forceinline__ void rescale_z(uint8_t *gbase, uint32_t zoff, const uint8_t *ck, const float *uvec, int i,
+                                          int wg, int L) {
 #pragma unroll 2
   for (int pc = 0; pc < 8; ++pc) {
     const int d0 = wg * 64 + pc * 8;
@@ -170,7 +173,7 @@ __device__ __forceinline__ void rescale_z(uint8_t *gbase, const uint8_t *ck, con
     float fz[8];
     decay_factors<NEG>(ck, i, d0, fz);
     float2 prod[4];
-    uint4 *pz = reinterpret_cast<uint4 *>(gbase + kOffZ + off);
+    uint4 *pz = reinterpret_cast<uint4 *>(gbase + zoff + off);
     *pz = scale8<T>(*pz, fz, prod);
     *reinterpret_cast<uint4 *>(gbase + kOffU + off) = update8<T>(prod, uvec, d0, i >= L);
   }
@@ -211,7 +214,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     mbar_init(full_ck, 1);
     mbar_init(full_yz, 1);
     mbar_init(full_x, 1);
-    mbar_init(empty_ck, kComputeThreads);
+    mbar_init(empty_ck, TMODE ? 1 : kComputeThreads);
     mbar_init(empty_yz, 1);
     mbar_init(empty_x, 1);
     mbar_init(bar_p, 1);
@@ -239,12 +242,12 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     // ------------------------------------------------------------------ TMA loads (single stage)
     if (lane == 0) {
       int n_ck = 0, n_yz = 0, n_x = 0;
-      auto load_ck = [&](int tok0, uint32_t par) {
+      auto load_ck = [&](int tok0, uint32_t par, uint32_t dst) {
         mbar_wait(empty_ck, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) return false;
         mbar_arrive_expect_tx(full_ck, kCkBytes);
 #pragma unroll
-        for (int gq = 0; gq < 4; ++gq) tma_load_4d(cks + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+        for (int gq = 0; gq < 4; ++gq) tma_load_4d(dst + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
         ++n_ck;
         return true;
       };
@@ -252,15 +255,17 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int n = rev ? (nc - 1 - it) : it;
         const uint32_t par = (uint32_t)it & 1u;
         const int tok0 = (int)t_begin + n * kChunk;
+        const bool swap = TMODE && (it & 1);  // T mode: the two 64 KB regions swap roles every chunk
+        const uint32_t ck_dst = swap ? ys : cks, y_dst = swap ? cks : ys, z_dst = y_dst + kTileBytes;
         // in the order in which the pieces come free
-        if (!load_ck(tok0, par)) break;
+        if (!load_ck(tok0, par, ck_dst)) break;
         mbar_wait(empty_yz, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) break;
         mbar_arrive_expect_tx(full_yz, 2 * kTileBytes);
-        tma_load_4d(ys, &map_y, full_yz, 0, h, tok0, bidx);
-        tma_load_4d(ys + kBoxBytes, &map_y, full_yz, 64, h, tok0, bidx);
-        tma_load_4d(zs, &map_z, full_yz, 0, h, tok0, bidx);
-        tma_load_4d(zs + kBoxBytes, &map_z, full_yz, 64, h, tok0, bidx);
+        tma_load_4d(y_dst, &map_y, full_yz, 0, h, tok0, bidx);
+        tma_load_4d(y_dst + kBoxBytes, &map_y, full_yz, 64, h, tok0, bidx);
+        tma_load_4d(z_dst, &map_z, full_yz, 0, h, tok0, bidx);
+        tma_load_4d(z_dst + kBoxBytes, &map_z, full_yz, 64, h, tok0, bidx);
         ++n_yz;
         mbar_wait(empty_x, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) break;
@@ -294,11 +299,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t idesc_kk = instr_desc(Fmt<T>::kAB, 0, 0, 128, 128);
       const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
       const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
-      const uint64_t d_xk = desc_kmajor(xs), d_yk = desc_kmajor(ys), d_tb = desc_mnmajor(tbs, kBoxBytes);
-      const uint64_t d_zmn = desc_mnmajor(zs, kBoxBytes), d_ymn = desc_mnmajor(ys, kBoxBytes);
+      const uint64_t d_xk = desc_kmajor(xs), d_tb = desc_mnmajor(tbs, kBoxBytes);
       const uint64_t d_umn = desc_mnmajor(us, kBoxBytes);
       for (int it = 0; it < nc; ++it) {
         const uint32_t par = (uint32_t)it & 1u;
+        const uint32_t y_at = (TMODE && (it & 1)) ? cks : ys, z_at = y_at + kTileBytes;
+        const uint64_t d_yk = desc_kmajor(y_at), d_ymn = desc_mnmajor(y_at, kBoxBytes);
+        const uint64_t d_zmn = desc_mnmajor(z_at, kBoxBytes);
         mbar_wait(full_x, par, abort_flag, a.status, kStFull);
         mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
         // N mode multiplies the rescaled X and Y; T mode the tiles as loaded
@@ -332,9 +339,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
                  idesc_kmn, ks > 0);
         mma_commit(bar_w);
-        // N mode: Y and Z have no reader left once the products above are done (in T mode they
-        // go on to stage the gradient terms and the store warp hands them back)
-        if (!TMODE) mma_commit(empty_yz);
+        // Y and Z have no reader left once the products above are done: in N mode they go back
+        // to the producer for the next chunk's Y and Z, in T mode for its decay tile
+        mma_commit(TMODE ? empty_ck : empty_yz);
         mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       }
     }
@@ -352,12 +359,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tma_store_4d(&map_o, xs, 0, h, tok0, bidx);
           tma_store_4d(&map_o, xs + kBoxBytes, 64, h, tok0, bidx);
           if (TMODE && a.dld != nullptr) {
-            // the Y and Z tiles now hold this chunk's log-decay-gradient terms: store (dq pass) or
-            // add the negated terms (dk pass) as four fp32 boxes
+            // the decay tile now holds this chunk's log-decay-gradient terms: store (dq pass) or
+            // add the (negated) terms as four fp32 boxes
+            const uint32_t stg = (it & 1) ? ys : cks;
 #pragma unroll
             for (int gq = 0; gq < 4; ++gq) {
-              if (a.dld_sub || a.dld_add) tma_reduce_add_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
-              else tma_store_4d(&map_dld, ys + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              if (a.dld_sub || a.dld_add) tma_reduce_add_4d(&map_dld, stg + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
+              else tma_store_4d(&map_dld, stg + gq * kBoxBytes, 32 * gq, h, tok0, bidx);
             }
           }
           tma_store_commit();
@@ -375,7 +383,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const int i = q4 * 32 + lane;  // tile row / tensor-memory lane
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
-    uint8_t *ck = gbase + kOffCk;
+    uint8_t *ck = gbase + kOffCk;  // T mode: re-pointed every chunk
     float *segtot = reinterpret_cast<float *>(gbase + kOffU);  // [8][128], before U is written
 
     for (int b2 = 0; b2 < 2; ++b2) {  // starting state -> tensor memory
@@ -398,6 +406,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
 
+      const uint32_t z_off = (TMODE && (it & 1)) ? kOffCk + kTileBytes : kOffZ;
+      if (TMODE) ck = gbase + ((it & 1) ? kOffY : kOffCk);
       LV_TRACE(0);
       if (TMODE && a.dld != nullptr && i < L) {
         // the epilogue multiplies the output by this row of xrow, read from global memory: start
@@ -472,8 +482,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (rev) rescale_xy<T, true>(gbase, ck, sm->uvec, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
         else rescale_xy<T, false>(gbase, ck, sm->uvec, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
       } else {
-        if (rev) rescale_z<T, false>(gbase, ck, sm->uvec, i, wg, L);   // dk: Z = q 2^(ck-m)
-        else rescale_z<T, true>(gbase, ck, sm->uvec, i, wg, L);        // dq: Z = k 2^(m-ck)
+        if (rev) rescale_z<T, false>(gbase, z_off, ck, sm->uvec, i, wg, L);   // dk: Z = q 2^(ck-m)
+        else rescale_z<T, true>(gbase, z_off, ck, sm->uvec, i, wg, L);        // dq: Z = k 2^(m-ck)
       }
       fence_proxy_async();
       mbar_arrive(bar_r);
@@ -618,13 +628,12 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             float4 lo = make_float4(xs[0] * w[pc * 8 + 0], xs[1] * w[pc * 8 + 1], xs[2] * w[pc * 8 + 2], xs[3] * w[pc * 8 + 3]);
             float4 hi = make_float4(xs[4] * w[pc * 8 + 4], xs[5] * w[pc * 8 + 5], xs[6] * w[pc * 8 + 6], xs[7] * w[pc * 8 + 7]);
             if (full_chunk) {
-              // stage in the Y and Z tiles (64 KB, free once the chunk's products are done) in
-              // the layout of the decay tile; the store warp writes them out with TMA
+              // stage in the decay tile (this thread's row, columns already consumed above); the
+              // store warp writes the tile out with TMA
               const float sg = a.dld_sub ? -1.f : 1.f;
               const int d0 = bt * 32 + pc * 8;
-              uint8_t *stg = gbase + kOffY;
-              *reinterpret_cast<float4 *>(stg + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
-              *reinterpret_cast<float4 *>(stg + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
               continue;
             }
             if (a.dld_add) {  // the twin pass may be on this tile too
@@ -661,7 +670,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
       if (full_chunk) fence_proxy_async();
       tc_fence_before();
-      if (TMODE) mbar_arrive(empty_ck);  // T mode reads the decay tile for the last time above
       mbar_arrive(bar_h);
       LV_TRACE(8);
     }
