@@ -410,11 +410,12 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (TMODE) ck = gbase + ((it & 1) ? kOffY : kOffCk);
       LV_TRACE(0);
       if (TMODE && a.dld != nullptr && i < L) {
-        // the epilogue multiplies the output by this row of xrow, read from global memory: start
-        // that fetch now (one 128-byte line per thread) so that it is in cache by then
+        // the epilogue multiplies the output by this row of xrow, read from global memory: pull
+        // it into L2 now (one 128-byte line per thread; L1 is too small beside 227 KB of shared
+        // memory to hold it until then)
         const char *xr = reinterpret_cast<const char *>(static_cast<const T *>(a.xrow) +
                                                           ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk + wg * 64);
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(xr));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(xr));
       }
       mbar_wait(full_ck, par, abort_flag, a.status, kStFull);
       LV_TRACE(1);
@@ -587,53 +588,63 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       LV_TRACE(7);
       const bool full_chunk = (L == kChunk);
       const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
-      const float so = rev ? -1.f : 1.f;
+      // packed fp32x2 arithmetic throughout: every product below is an fp32 multiply rounded to
+      // nearest, exactly as its scalar form
 #pragma unroll 1
       for (int b2 = 0; b2 < 2; ++b2) {
         const int bt = 2 * wg + b2;
+        // the row of xrow for the gradient terms: in flight while the accumulators are read and
+        // the scale factors computed
+        const bool want_dld = TMODE && a.dld != nullptr && i < L;
+        uint4 xv4[4] = {};
+        if (want_dld) {
+          const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
+#pragma unroll
+          for (int pc = 0; pc < 4; ++pc) xv4[pc] = __ldg(xp + pc);
+        }
         uint32_t w1[32], w2[32];
         tmem_ld32(tl + kColW1 + bt * 32, w1);
         tmem_ld32(tl + kColW2 + bt * 32, w2);
         tmem_wait_ld();
-        float w[32], scl[32];
+        float2 w[16], scl[16];  // pairs of adjacent columns
 #pragma unroll
         for (int k = 0; k < 32; k += 4) {
-          float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+          float2 s0 = make_float2(1.f, 1.f), s1 = s0;
           if (TMODE) {
             const float4 c = *reinterpret_cast<const float4 *>(ck + ck_off(i, bt * 32 + k));
-            sc = make_float4(ex2(so * c.x), ex2(so * c.y), ex2(so * c.z), ex2(so * c.w));
+            if (rev) { s0 = make_float2(ex2(-c.x), ex2(-c.y)); s1 = make_float2(ex2(-c.z), ex2(-c.w)); }
+            else { s0 = make_float2(ex2(c.x), ex2(c.y)); s1 = make_float2(ex2(c.z), ex2(c.w)); }
           }
-          w[k + 0] = __uint_as_float(w1[k + 0]) + __uint_as_float(w2[k + 0]);
-          w[k + 1] = __uint_as_float(w1[k + 1]) + __uint_as_float(w2[k + 1]);
-          w[k + 2] = __uint_as_float(w1[k + 2]) + __uint_as_float(w2[k + 2]);
-          w[k + 3] = __uint_as_float(w1[k + 3]) + __uint_as_float(w2[k + 3]);
-          scl[k + 0] = sc.x; scl[k + 1] = sc.y; scl[k + 2] = sc.z; scl[k + 3] = sc.w;
+          w[(k >> 1) + 0] = __fadd2_rn(f2(w1[k + 0], w1[k + 1]), f2(w2[k + 0], w2[k + 1]));
+          w[(k >> 1) + 1] = __fadd2_rn(f2(w1[k + 2], w1[k + 3]), f2(w2[k + 2], w2[k + 3]));
+          scl[(k >> 1) + 0] = s0;
+          scl[(k >> 1) + 1] = s1;
         }
-        if (TMODE && a.dld != nullptr && i < L) {
+        if (want_dld) {
           // Log-decay gradient term x * W.  W = w * scl, but the product is formed as
           // round16(x * scl) * w: round16(x * scl) is exactly the rescaled operand the twin pass
           // feeds to the tensor cores, so the intra-chunk parts of q*dq and k*dk cancel term by term
-          // as they do in exact arithmetic.
-          const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(a.xrow) + row_off + bt * 32);
+          // as they do in exact arithmetic.  The sign of the dk pass goes onto x (a bit flip).
           float4 *dp = reinterpret_cast<float4 *>(a.dld + row_off + bt * 32);
+          const uint32_t flip = (full_chunk && a.dld_sub) ? 0x80008000u : 0u;
 #pragma unroll
           for (int pc = 0; pc < 4; ++pc) {
-            const uint4 xv = xp[pc];
-            float xs[8];
-            float2 t;
-            t = Fmt<T>::unpack(xv.x); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 0], t.y * scl[pc * 8 + 1])); xs[0] = t.x; xs[1] = t.y;
-            t = Fmt<T>::unpack(xv.y); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 2], t.y * scl[pc * 8 + 3])); xs[2] = t.x; xs[3] = t.y;
-            t = Fmt<T>::unpack(xv.z); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 4], t.y * scl[pc * 8 + 5])); xs[4] = t.x; xs[5] = t.y;
-            t = Fmt<T>::unpack(xv.w); t = Fmt<T>::unpack(Fmt<T>::pack(t.x * scl[pc * 8 + 6], t.y * scl[pc * 8 + 7])); xs[6] = t.x; xs[7] = t.y;
-            float4 lo = make_float4(xs[0] * w[pc * 8 + 0], xs[1] * w[pc * 8 + 1], xs[2] * w[pc * 8 + 2], xs[3] * w[pc * 8 + 3]);
-            float4 hi = make_float4(xs[4] * w[pc * 8 + 4], xs[5] * w[pc * 8 + 5], xs[6] * w[pc * 8 + 6], xs[7] * w[pc * 8 + 7]);
+            const uint4 xv = xv4[pc];
+            const uint32_t xw[4] = {xv.x ^ flip, xv.y ^ flip, xv.z ^ flip, xv.w ^ flip};
+            float2 pr[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = mul2(Fmt<T>::unpack(xw[j]), scl[pc * 4 + j]);
+              pr[j] = mul2(Fmt<T>::unpack(Fmt<T>::pack(t.x, t.y)), w[pc * 4 + j]);
+            }
+            float4 lo = make_float4(pr[0].x, pr[0].y, pr[1].x, pr[1].y);
+            float4 hi = make_float4(pr[2].x, pr[2].y, pr[3].x, pr[3].y);
             if (full_chunk) {
               // stage in the decay tile (this thread's row, columns already consumed above); the
               // store warp writes the tile out with TMA
-              const float sg = a.dld_sub ? -1.f : 1.f;
               const int d0 = bt * 32 + pc * 8;
-              *reinterpret_cast<float4 *>(ck + ck_off(i, d0)) = make_float4(sg * lo.x, sg * lo.y, sg * lo.z, sg * lo.w);
-              *reinterpret_cast<float4 *>(ck + ck_off(i, d0 + 4)) = make_float4(sg * hi.x, sg * hi.y, sg * hi.z, sg * hi.w);
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0)) = lo;
+              *reinterpret_cast<float4 *>(ck + ck_off(i, d0 + 4)) = hi;
               continue;
             }
             if (a.dld_add) {  // the twin pass may be on this tile too
@@ -653,14 +664,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           }
         }
 #pragma unroll
-        for (int k = 0; k < 32; ++k) w[k] *= scl[k];
-#pragma unroll
         for (int pc = 0; pc < 4; ++pc) {
           uint4 v;
-          v.x = Fmt<T>::pack(w[pc * 8 + 0], w[pc * 8 + 1]);
-          v.y = Fmt<T>::pack(w[pc * 8 + 2], w[pc * 8 + 3]);
-          v.z = Fmt<T>::pack(w[pc * 8 + 4], w[pc * 8 + 5]);
-          v.w = Fmt<T>::pack(w[pc * 8 + 6], w[pc * 8 + 7]);
+          float2 t;
+          t = mul2(w[pc * 4 + 0], scl[pc * 4 + 0]); v.x = Fmt<T>::pack(t.x, t.y);
+          t = mul2(w[pc * 4 + 1], scl[pc * 4 + 1]); v.y = Fmt<T>::pack(t.x, t.y);
+          t = mul2(w[pc * 4 + 2], scl[pc * 4 + 2]); v.z = Fmt<T>::pack(t.x, t.y);
+          t = mul2(w[pc * 4 + 3], scl[pc * 4 + 3]); v.w = Fmt<T>::pack(t.x, t.y);
           if (full_chunk) {
             *reinterpret_cast<uint4 *>(gbase + kOffX + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
           } else if (i < L) {
