@@ -9,7 +9,8 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libxopes_b200.so")
+# XOPES_B200_LIB points at another build of the library (for A/B measurements)
+LIB_PATH = os.environ.get("XOPES_B200_LIB") or os.path.join(_PKG, "libxopes_b200.so")
 
 LA_F32, LA_BF16, LA_F16 = 0, 1, 2
 FLAG_FORCE_RECURRENCE = 1

@@ -15,10 +15,15 @@
 // A chunk whose half-chunk decay exceeds 2^64 (bf16; 2^10 for fp16) raises the "unsafe" flag; the caller then reruns
 // the call on the fp32 scan kernels (predicated on that flag, no host round trip).
 //
+// The factor e^{g-m} of the state update is not multiplied into the operand: it is owed to the
+// state (kept as T~ with T = T~ scaled per feature by the owed factor) and paid at the start of the
+// next chunk together with that chunk's own factor, so one scaled value serves both as the 16-bit
+// copy and as the state the update adds to.
+//
 // Structure as in chunk_sm100.cu (state resident in tensor memory, TMA producer / MMA issuer /
 // TMA store warps, bounded mbarrier waits, no multicast), but single-stage: the chunk's operands
-// are three 16-bit tiles plus the 64 KB fp32 decay tile, and two more tiles hold the 16-bit state
-// copy and the rescaled update operand, which fills shared memory.  The stage goes back to the
+// are three 16-bit tiles plus the 64 KB fp32 decay tile, one more tile holds the 16-bit state
+// copy and a 4 KB scratch the segment totals of the cumulative sum.  The stage goes back to the
 // producer piece by piece (decay tile, Y and Z, X), each when its last reader is done, and the
 // next chunk is pulled into L2 meanwhile, so that most of the load latency hides behind the rest
 // of the current chunk.
@@ -69,9 +74,13 @@ struct Small {
   uint32_t tmem_base;
   int abort_flag;
   int issued[3];  // chunks whose decay tile / Y and Z / X loads were issued
-  alignas(16) float uvec[kChunk];  // scale of the state-update operand per feature
-  alignas(16) float cvec[kChunk];  // scale of the 16-bit state copy per feature
-  alignas(16) float gfac[kChunk];  // e^g per feature: decay of the state over the chunk
+  // The resident state is kept as T~ with T = T~ (.) uvec (per feature: per row in N mode, per
+  // column in T mode): instead of scaling the update operand by uvec before the product, the
+  // factor is owed to the state and paid at the start of the next chunk, together with that
+  // chunk's own factor (cf = cvec (.) previous uvec scales both the 16-bit copy and T~ itself,
+  // because e^g / uvec = cvec in either direction), and once more when the end state is written.
+  alignas(16) float uvec[kChunk];  // factor owed to the state after this chunk's update
+  alignas(16) float cf[kChunk];    // cvec (.) the factor owed from the previous chunk
 };
 static_assert(sizeof(Small) <= kSmallBytes, "small area overflow");
 
@@ -130,24 +139,10 @@ __device__ __forceinline__ uint4 scale8(uint4 v, const float (&f)[8], float2 (&p
   prod[3] = mul2(Fmt<T>::unpack(v.w), make_float2(f[6], f[7])); o.w = Fmt<T>::pack(prod[3].x, prod[3].y);
   return o;
 }
-// The state-update operand: the scaled piece times the per-feature vector uvec (zero rows past the
-// end of the sequence).
-template <typename T>
-__device__ __forceinline__ uint4 update8(const float2 (&prod)[4], const float *uvec, int d0, bool zero) {
-  const float4 u0 = *reinterpret_cast<const float4 *>(uvec + d0);
-  const float4 u1 = *reinterpret_cast<const float4 *>(uvec + d0 + 4);
-  if (zero) return make_uint4(0u, 0u, 0u, 0u);
-  float2 p;
-  uint4 o;
-  p = mul2(prod[0], make_float2(u0.x, u0.y)); o.x = Fmt<T>::pack(p.x, p.y);
-  p = mul2(prod[1], make_float2(u0.z, u0.w)); o.y = Fmt<T>::pack(p.x, p.y);
-  p = mul2(prod[2], make_float2(u1.x, u1.y)); o.z = Fmt<T>::pack(p.x, p.y);
-  p = mul2(prod[3], make_float2(u1.z, u1.w)); o.w = Fmt<T>::pack(p.x, p.y);
-  return o;
-}
 template <typename T, bool NEG>
-__device__ __forceinline__ void rescale_xy(uint8_t *gbase, const uint8_t *ck, const float *uvec, int i, int wg, int L) {
-  // X <- X 2^(+-ckc), Y <- Y 2^(-+ckc), U <- Y' uvec for this thread's row and 64 columns
+__device__ __forceinline__ void rescale_xy(uint8_t *gbase, const uint8_t *ck, int i, int wg, int L) {
+  // X <- X 2^(+-ckc), Y <- Y 2^(-+ckc) for this thread's row and 64 columns; rows past the end of
+  // the sequence become zero in Y so that they add nothing to the state
 #pragma unroll 2
   for (int pc = 0; pc < 8; ++pc) {
     const int d0 = wg * 64 + pc * 8;
@@ -159,13 +154,12 @@ __device__ __forceinline__ void rescale_xy(uint8_t *gbase, const uint8_t *ck, co
     uint4 *px = reinterpret_cast<uint4 *>(gbase + kOffX + off);
     *px = scale8<T>(*px, fx, prod);
     uint4 *py = reinterpret_cast<uint4 *>(gbase + kOffY + off);
-    *py = scale8<T>(*py, fy, prod);
-    *reinterpret_cast<uint4 *>(gbase + kOffU + off) = update8<T>(prod, uvec, d0, i >= L);
+    const uint4 ys = scale8<T>(*py, fy, prod);
+    *py = i < L ? ys : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 template <typename T, bool NEG>
-__device__ __forceinline__ void rescale_z(uint8_t *gbase, uint32_t zoff, const uint8_t *ck, const float *uvec, int i,
-                                          int wg, int L) {
+__device__ __forceinline__ void rescale_z(uint8_t *gbase, uint32_t zoff, const uint8_t *ck, int i, int wg, int L) {
 #pragma unroll 2
   for (int pc = 0; pc < 8; ++pc) {
     const int d0 = wg * 64 + pc * 8;
@@ -174,8 +168,8 @@ __device__ __forceinline__ void rescale_z(uint8_t *gbase, uint32_t zoff, const u
     decay_factors<NEG>(ck, i, d0, fz);
     float2 prod[4];
     uint4 *pz = reinterpret_cast<uint4 *>(gbase + zoff + off);
-    *pz = scale8<T>(*pz, fz, prod);
-    *reinterpret_cast<uint4 *>(gbase + kOffU + off) = update8<T>(prod, uvec, d0, i >= L);
+    const uint4 zs = scale8<T>(*pz, fz, prod);
+    *pz = i < L ? zs : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
@@ -236,7 +230,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   const uint32_t xs = base + kOffX, ys = base + kOffY, zs = base + kOffZ, cks = base + kOffCk;
-  const uint32_t tbs = base + kOffTb, us = base + kOffU;
+  const uint32_t tbs = base + kOffTb;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA loads (single stage)
@@ -300,7 +294,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint32_t idesc_kmn = instr_desc(Fmt<T>::kAB, 0, 1, 128, 128);
       const uint32_t idesc_mnmn = instr_desc(Fmt<T>::kAB, 1, 1, 128, 128);
       const uint64_t d_xk = desc_kmajor(xs), d_tb = desc_mnmajor(tbs, kBoxBytes);
-      const uint64_t d_umn = desc_mnmajor(us, kBoxBytes);
       for (int it = 0; it < nc; ++it) {
         const uint32_t par = (uint32_t)it & 1u;
         const uint32_t y_at = (TMODE && (it & 1)) ? cks : ys, z_at = y_at + kTileBytes;
@@ -326,12 +319,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, ks > 0);
         }
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // state update: N mode U^T Z, T mode Y^T U
-          if (!TMODE)
-            mma_ss(tmem + kColT, d_umn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
-          else
-            mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_umn + (uint64_t)(ks * 128), idesc_mnmn, 1);
-        }
+        for (int ks = 0; ks < 8; ++ks)  // state update Y^T Z (N mode: Y rescaled; T mode: Z rescaled)
+          mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
         mbar_wait(bar_f, par, abort_flag, a.status, kStF);
         tc_fence_after();
 #pragma unroll
@@ -384,7 +373,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
     uint8_t *ck = gbase + kOffCk;  // T mode: re-pointed every chunk
-    float *segtot = reinterpret_cast<float *>(gbase + kOffU);  // [8][128], before U is written
+    float *segtot = reinterpret_cast<float *>(gbase + kOffU);  // [8][128]
 
     for (int b2 = 0; b2 < 2; ++b2) {  // starting state -> tensor memory
       const int bt = 2 * wg + b2;
@@ -399,6 +388,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tmem_st32(tl + kColT + bt * 32, r);
     }
     tmem_wait_st();
+    if (tid < kChunk) sm->uvec[tid] = 1.f;  // nothing is owed to the starting state
 
     for (int it = 0; it < nc; ++it) {
       const int n = rev ? (nc - 1 - it) : it;
@@ -465,9 +455,10 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           bool bad = false;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            sm->uvec[d0 + c] = rev ? ex2(mm[c]) : ex2(gg[c] - mm[c]);
-            sm->cvec[d0 + c] = rev ? ex2(gg[c] - mm[c]) : ex2(mm[c]);
-            sm->gfac[d0 + c] = ex2(gg[c]);
+            const float u_new = rev ? ex2(mm[c]) : ex2(gg[c] - mm[c]);
+            const float c_new = rev ? ex2(gg[c] - mm[c]) : ex2(mm[c]);
+            sm->cf[d0 + c] = c_new * sm->uvec[d0 + c];  // uvec still holds the previous chunk's
+            sm->uvec[d0 + c] = u_new;
             bad = bad || (-mm[c] > SafeBits<T>::value) || (-(gg[c] - mm[c]) > SafeBits<T>::value);
           }
           if (bad) atomicExch(a.unsafe, 1);
@@ -476,15 +467,15 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       }
 
       LV_TRACE(2);
-      // ---- R: rescale operands in place, build the state-update operand U
+      // ---- R: rescale operands in place
       mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
       if (!TMODE) mbar_wait(full_x, par, abort_flag, a.status, kStFull);
       if (!TMODE) {
-        if (rev) rescale_xy<T, true>(gbase, ck, sm->uvec, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
-        else rescale_xy<T, false>(gbase, ck, sm->uvec, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
+        if (rev) rescale_xy<T, true>(gbase, ck, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
+        else rescale_xy<T, false>(gbase, ck, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
       } else {
-        if (rev) rescale_z<T, false>(gbase, z_off, ck, sm->uvec, i, wg, L);   // dk: Z = q 2^(ck-m)
-        else rescale_z<T, true>(gbase, z_off, ck, sm->uvec, i, wg, L);        // dq: Z = k 2^(m-ck)
+        if (rev) rescale_z<T, false>(gbase, z_off, ck, i, wg, L);   // dk: Z = q 2^(ck-m)
+        else rescale_z<T, true>(gbase, z_off, ck, i, wg, L);        // dq: Z = k 2^(m-ck)
       }
       fence_proxy_async();
       mbar_arrive(bar_r);
@@ -498,40 +489,33 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tmem_ld32(tl + kColT + (2 * wg + 1) * 32, r1);
         tmem_wait_ld();
         uint8_t *box = gbase + kOffTb + wg * kBoxBytes;
-        const float cv_row = sm->cvec[i], gf_row = sm->gfac[i];
+        const float cf_row = sm->cf[i];
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           uint32_t(&r)[32] = hf ? r1 : r0;
 #pragma unroll
           for (int pc = 0; pc < 4; ++pc) {
-            float2 c01, c23, c45, c67, g01, g23, g45, g67;
+            float2 c01, c23, c45, c67;
             if (TMODE) {
               const int d0 = wg * 64 + hf * 32 + pc * 8;
-              const float4 ca = *reinterpret_cast<const float4 *>(&sm->cvec[d0]);
-              const float4 cb = *reinterpret_cast<const float4 *>(&sm->cvec[d0 + 4]);
-              const float4 ga = *reinterpret_cast<const float4 *>(&sm->gfac[d0]);
-              const float4 gb = *reinterpret_cast<const float4 *>(&sm->gfac[d0 + 4]);
+              const float4 ca = *reinterpret_cast<const float4 *>(&sm->cf[d0]);
+              const float4 cb = *reinterpret_cast<const float4 *>(&sm->cf[d0 + 4]);
               c01 = make_float2(ca.x, ca.y); c23 = make_float2(ca.z, ca.w);
               c45 = make_float2(cb.x, cb.y); c67 = make_float2(cb.z, cb.w);
-              g01 = make_float2(ga.x, ga.y); g23 = make_float2(ga.z, ga.w);
-              g45 = make_float2(gb.x, gb.y); g67 = make_float2(gb.z, gb.w);
             } else {
-              c01 = c23 = c45 = c67 = make_float2(cv_row, cv_row);
-              g01 = g23 = g45 = g67 = make_float2(gf_row, gf_row);
+              c01 = c23 = c45 = c67 = make_float2(cf_row, cf_row);
             }
-            const float2 t01 = f2(r[pc * 8 + 0], r[pc * 8 + 1]), t23 = f2(r[pc * 8 + 2], r[pc * 8 + 3]);
-            const float2 t45 = f2(r[pc * 8 + 4], r[pc * 8 + 5]), t67 = f2(r[pc * 8 + 6], r[pc * 8 + 7]);
-            float2 s;
+            // one scaled value serves as the 16-bit copy and as the state the update adds to
+            const float2 s01 = mul2(f2(r[pc * 8 + 0], r[pc * 8 + 1]), c01), s23 = mul2(f2(r[pc * 8 + 2], r[pc * 8 + 3]), c23);
+            const float2 s45 = mul2(f2(r[pc * 8 + 4], r[pc * 8 + 5]), c45), s67 = mul2(f2(r[pc * 8 + 6], r[pc * 8 + 7]), c67);
             uint4 v;
-            s = mul2(t01, c01); v.x = Fmt<T>::pack(s.x, s.y);
-            s = mul2(t23, c23); v.y = Fmt<T>::pack(s.x, s.y);
-            s = mul2(t45, c45); v.z = Fmt<T>::pack(s.x, s.y);
-            s = mul2(t67, c67); v.w = Fmt<T>::pack(s.x, s.y);
+            v.x = Fmt<T>::pack(s01.x, s01.y); v.y = Fmt<T>::pack(s23.x, s23.y);
+            v.z = Fmt<T>::pack(s45.x, s45.y); v.w = Fmt<T>::pack(s67.x, s67.y);
             *reinterpret_cast<uint4 *>(box + sw128_offset(i, hf * 4 + pc)) = v;
-            s = mul2(t01, g01); r[pc * 8 + 0] = __float_as_uint(s.x); r[pc * 8 + 1] = __float_as_uint(s.y);
-            s = mul2(t23, g23); r[pc * 8 + 2] = __float_as_uint(s.x); r[pc * 8 + 3] = __float_as_uint(s.y);
-            s = mul2(t45, g45); r[pc * 8 + 4] = __float_as_uint(s.x); r[pc * 8 + 5] = __float_as_uint(s.y);
-            s = mul2(t67, g67); r[pc * 8 + 6] = __float_as_uint(s.x); r[pc * 8 + 7] = __float_as_uint(s.y);
+            r[pc * 8 + 0] = __float_as_uint(s01.x); r[pc * 8 + 1] = __float_as_uint(s01.y);
+            r[pc * 8 + 2] = __float_as_uint(s23.x); r[pc * 8 + 3] = __float_as_uint(s23.y);
+            r[pc * 8 + 4] = __float_as_uint(s45.x); r[pc * 8 + 5] = __float_as_uint(s45.y);
+            r[pc * 8 + 6] = __float_as_uint(s67.x); r[pc * 8 + 7] = __float_as_uint(s67.y);
           }
         }
         tmem_st32(tl + kColT + (2 * wg) * 32, r0);
@@ -684,8 +668,10 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       LV_TRACE(8);
     }
 
-    if (a.tfinal != nullptr) {  // end state -> global
+    if (a.tfinal != nullptr) {  // end state -> global, with the factor still owed to it
+      named_bar_sync(1, kComputeThreads);  // uvec of the last chunk (or its initial ones) is in place
       tc_fence_after();
+      const float u_row = sm->uvec[i];
       for (int b2 = 0; b2 < 2; ++b2) {
         const int bt = 2 * wg + b2;
         uint32_t r[32];
@@ -694,7 +680,8 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
           const int c = bt * 32 + k;
-          a.tfinal[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))] = __uint_as_float(r[k]);
+          const float u = TMODE ? sm->uvec[c] : u_row;
+          a.tfinal[st_base + (a.state_transposed ? (c * kChunk + i) : (i * kChunk + c))] = __uint_as_float(r[k]) * u;
         }
       }
     }
