@@ -230,7 +230,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   const uint32_t xs = base + kOffX, ys = base + kOffY, zs = base + kOffZ, cks = base + kOffCk;
-  const uint32_t tbs = base + kOffTb;
+  const uint32_t tbs = base + kOffTb, zts = base + kOffU;  // zts: T mode's Z tile
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA loads (single stage)
@@ -239,9 +239,15 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       auto load_ck = [&](int tok0, uint32_t par, uint32_t dst) {
         mbar_wait(empty_ck, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) return false;
-        mbar_arrive_expect_tx(full_ck, kCkBytes);
+        mbar_arrive_expect_tx(full_ck, TMODE ? kCkBytes + kTileBytes : kCkBytes);
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) tma_load_4d(dst + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+        if (TMODE) {
+          // T mode keeps Z in a tile of its own (free like the decay slot once the previous
+          // chunk's products are done), so the rescale of the next chunk never waits for the store
+          tma_load_4d(zts, &map_z, full_ck, 0, h, tok0, bidx);
+          tma_load_4d(zts + kBoxBytes, &map_z, full_ck, 64, h, tok0, bidx);
+        }
         ++n_ck;
         return true;
       };
@@ -255,11 +261,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (!load_ck(tok0, par, ck_dst)) break;
         mbar_wait(empty_yz, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) break;
-        mbar_arrive_expect_tx(full_yz, 2 * kTileBytes);
+        mbar_arrive_expect_tx(full_yz, TMODE ? kTileBytes : 2 * kTileBytes);
         tma_load_4d(y_dst, &map_y, full_yz, 0, h, tok0, bidx);
         tma_load_4d(y_dst + kBoxBytes, &map_y, full_yz, 64, h, tok0, bidx);
-        tma_load_4d(z_dst, &map_z, full_yz, 0, h, tok0, bidx);
-        tma_load_4d(z_dst + kBoxBytes, &map_z, full_yz, 64, h, tok0, bidx);
+        if (!TMODE) {
+          tma_load_4d(z_dst, &map_z, full_yz, 0, h, tok0, bidx);
+          tma_load_4d(z_dst + kBoxBytes, &map_z, full_yz, 64, h, tok0, bidx);
+        }
         ++n_yz;
         mbar_wait(empty_x, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) break;
@@ -296,7 +304,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint64_t d_xk = desc_kmajor(xs), d_tb = desc_mnmajor(tbs, kBoxBytes);
       for (int it = 0; it < nc; ++it) {
         const uint32_t par = (uint32_t)it & 1u;
-        const uint32_t y_at = (TMODE && (it & 1)) ? cks : ys, z_at = y_at + kTileBytes;
+        const uint32_t y_at = (TMODE && (it & 1)) ? cks : ys, z_at = TMODE ? zts : y_at + kTileBytes;
         const uint64_t d_yk = desc_kmajor(y_at), d_ymn = desc_mnmajor(y_at, kBoxBytes);
         const uint64_t d_zmn = desc_mnmajor(z_at, kBoxBytes);
         mbar_wait(full_x, par, abort_flag, a.status, kStFull);
@@ -373,7 +381,10 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tl = tmem + ((uint32_t)(32 * q4) << 16);
     const long long st_base = ((long long)seq * a.H + h) * (long long)(kChunk * kChunk);
     uint8_t *ck = gbase + kOffCk;  // T mode: re-pointed every chunk
-    float *segtot = reinterpret_cast<float *>(gbase + kOffU);  // [8][128]
+    // [8][128] segment totals of the cumulative sum, in the state-copy tile: the copy's last
+    // reader (X T of the previous chunk) is done before the previous epilogue, and the next copy is
+    // written after the cumulative sum
+    float *segtot = reinterpret_cast<float *>(gbase + kOffTb);
 
     for (int b2 = 0; b2 < 2; ++b2) {  // starting state -> tensor memory
       const int bt = 2 * wg + b2;
@@ -396,7 +407,7 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const int L = min(kChunk, len - n * kChunk);
       const long long tok = t_begin + (long long)n * kChunk + i;
 
-      const uint32_t z_off = (TMODE && (it & 1)) ? kOffCk + kTileBytes : kOffZ;
+      const uint32_t z_off = TMODE ? kOffU : kOffZ;
       if (TMODE) ck = gbase + ((it & 1) ? kOffY : kOffCk);
       LV_TRACE(0);
       if (TMODE && a.dld != nullptr && i < L) {
@@ -468,8 +479,10 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
       LV_TRACE(2);
       // ---- R: rescale operands in place
-      mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
-      if (!TMODE) mbar_wait(full_x, par, abort_flag, a.status, kStFull);
+      if (!TMODE) {  // T mode rescales Z only, which came with the decay tile
+        mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
+        mbar_wait(full_x, par, abort_flag, a.status, kStFull);
+      }
       if (!TMODE) {
         if (rev) rescale_xy<T, true>(gbase, ck, i, wg, L);   // dv: X = k 2^(m-ck), Y = q 2^(ck-m)
         else rescale_xy<T, false>(gbase, ck, i, wg, L);      // o:  X = q 2^(ck-m), Y = k 2^(m-ck)
