@@ -22,8 +22,9 @@
 //
 // Structure as in chunk_sm100.cu (state resident in tensor memory, TMA producer / MMA issuer /
 // TMA store warps, bounded mbarrier waits, no multicast), but single-stage: the chunk's operands
-// are three 16-bit tiles plus the 64 KB fp32 decay tile, one more tile holds the 16-bit state
-// copy and a 4 KB scratch the segment totals of the cumulative sum.  The stage goes back to the
+// are three 16-bit tiles plus the 64 KB fp32 decay tile, and one more tile holds the 16-bit state
+// copy (and, before it is written, the segment totals of the cumulative sum).  In T mode Z lives in
+// a further tile of its own and is loaded together with the next decay tile.  The stage goes back to the
 // producer piece by piece (decay tile, Y and Z, X), each when its last reader is done, and the
 // next chunk is pulled into L2 meanwhile, so that most of the load latency hides behind the rest
 // of the current chunk.
