@@ -341,14 +341,17 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
 // One CTA per (sequence, head): in-place reverse cumulative sum over tokens of every feature f,
 // plus the state term (sum_option 0 / 1 of the reference kernel named above).  The sequence is cut
 // into `lanes` contiguous parts, one per group of Fpad threads: part sums, suffix offsets across
-// parts, then the running sum inside each part -- two reads and one write of the buffer.
+// parts, then the running sum inside each part -- two reads and one write of the buffer.  With few
+// (sequence, head) pairs the features are split over blockIdx.z (Fpad features per CTA, a multiple
+// of 32) so that the launch still fills the GPU.
 __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
                                                              const int64_t *cu, int N, int H, int F, int Fpad,
                                                              int D, int E, int f_is_row) {
   extern __shared__ float part[];  // [lanes + 1][Fpad]; row `lanes` holds the state term
   const int h = blockIdx.x, seq = blockIdx.y;
   const int lanes = blockDim.x / Fpad;
-  const int f = threadIdx.x % Fpad, ln = threadIdx.x / Fpad;
+  const int fl = threadIdx.x % Fpad, ln = threadIdx.x / Fpad;
+  const int f = blockIdx.z * Fpad + fl;  // feature of this thread
   int64_t t_begin = 0, t_end = N, bidx = seq;
   if (cu != nullptr) { t_begin = cu[seq]; t_end = cu[seq + 1]; bidx = 0; }
   const int64_t len = t_end - t_begin;
@@ -370,7 +373,7 @@ __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const f
     }
     for (; t < p1; ++t) s += ptr[t * stride];
   }
-  part[ln * Fpad + f] = s;
+  part[ln * Fpad + fl] = s;
   if (ln == 0) {
     float st = 0.f;
     if (on && sfin != nullptr && dsfin != nullptr) {
@@ -381,12 +384,12 @@ __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const f
         for (int d = 0; d < D; ++d) st = fmaf(sfin[base + (int64_t)d * E + f], dsfin[base + (int64_t)d * E + f], st);
       }
     }
-    part[lanes * Fpad + f] = st;
+    part[lanes * Fpad + fl] = st;
   }
   __syncthreads();
   if (!on) return;
-  float run = part[lanes * Fpad + f];
-  for (int l = lanes - 1; l > ln; --l) run += part[l * Fpad + f];
+  float run = part[lanes * Fpad + fl];
+  for (int l = lanes - 1; l > ln; --l) run += part[l * Fpad + fl];
   int64_t t = p1 - 1;
   for (; t - 7 >= p0; t -= 8) {
     float v[8];
@@ -414,9 +417,12 @@ int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfin
                          const int64_t *cu, int B, int N, int H, int F, int D, int E, int f_is_row,
                          int M, cudaStream_t stream) {
   const int nb = cu ? M : B;
-  dim3 grid(H, nb);
-  const int fpad = ((F + 31) / 32) * 32;
+  int fpad = ((F + 31) / 32) * 32;
   if (fpad > 1024) return LA_ERR_UNSUPPORTED;
+  // about two CTAs per SM: split the features while (sequence, head) pairs alone are too few
+  int fsplit = 1;
+  while (fpad % (2 * 32) == 0 && (int64_t)H * nb * fsplit < 296 && fsplit < 8) { fpad /= 2; fsplit *= 2; }
+  dim3 grid(H, nb, fsplit);
   const int lanes = 1024 / fpad;
   const size_t smem = sizeof(float) * (size_t)(lanes + 1) * fpad;
   revcumsum_vec_kernel<<<grid, lanes * fpad, smem, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, fpad,
