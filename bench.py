@@ -339,7 +339,7 @@ def cpu_slice_tokens_per_s(name, cfg, seed=0):
     if name == "C5":
         lens = W.varlen_doc_lengths(cfg["N"], cfg["docs"], 0)
         cu = [0] + [int(x) for x in torch.cumsum(lens, 0)]
-        # sample: the shortest document and as many leading documents as fit ~24K tokens
+        # sample: the shortest document and as many leading documents as fit ~200K tokens
         picks, budget = [int(torch.argmin(lens))], 200000
         for i in range(cfg["docs"]):
             if i not in picks and int(lens[i]) <= budget:
