@@ -2,9 +2,15 @@
  * xopes_b200 -- C ABI of the B200 (sm_100a) lightning-attention library.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
- * i.e. a cudaStream_t), enqueues work on that stream and returns immediately: nothing here
- * allocates, frees, synchronises or throws.  The caller owns every buffer.  The return value is
- * LA_OK or a negative LA_ERR_* code; la_status_string() turns it into text.
+ * i.e. a cudaStream_t), enqueues work on that stream and returns without waiting for it; nothing
+ * here synchronises (except la_device_status and la_debug_lavd_unsafe, which read a word back) or
+ * throws.  The caller owns every tensor and every workspace.  Two things the library creates for
+ * itself, once per device and on first need: a stream-ordered memory pool from which a tcgen05
+ * launch that splits (sequence, head) pairs across CTAs takes its hand-off scratch
+ * (cudaMallocFromPoolAsync / cudaFreeAsync on the caller's stream, about 10 MB per launch in
+ * flight), and two non-blocking side streams with three events on which independent gradient
+ * passes of one backward call run beside each other.  la_lasd_bwd_noalloc uses neither.  The
+ * return value is LA_OK or a negative LA_ERR_* code; la_status_string() turns it into text.
  *
  * Tensor layout (same as the reference operators): q, k are (B, N, H, D), v, o are (B, N, H, E),
  * row-major and contiguous; recurrent states are (B, H, D, E) fp32, contiguous.  `dtype` is the
@@ -32,7 +38,7 @@ extern "C" {
 
 #define LA_OK 0
 #define LA_ERR_NULL_POINTER (-1)   /* a required pointer is NULL                                  */
-#define LA_ERR_BAD_SHAPE (-2)      /* a size is <= 0, or B != 1 with cu_seqlens                    */
+#define LA_ERR_BAD_SHAPE (-2)      /* a size is <= 0, B != 1 with cu_seqlens, or M != 0 without   */
 #define LA_ERR_UNSUPPORTED (-3)    /* dtype / head dimension outside what the kernels cover        */
 #define LA_ERR_CUDA (-4)           /* a CUDA runtime or driver call failed (launch, tensor map)    */
 #define LA_ERR_TOO_LARGE (-5)      /* a size exceeds a documented fixed maximum                    */
@@ -64,11 +70,10 @@ LA_API int la_device_status_clear(void *stream);
  * the reference. */
 LA_API int la_debug_lavd_unsafe(void *stream, int *flag_out);
 
-/* Phase tracing of the chunk kernel (no counterpart in the reference): while buf is non-NULL,
- * every chunk pass writes clock64() stamps of CTA 0, threads 0 and 32, at 15 phase boundaries
- * per chunk into buf (device memory, 2 x 4096 x 16 int64).  NULL switches it off.  The stamps are
- * compiled in only when the library is built with -DLA_CHUNK_TRACE; otherwise this is a no-op. */
-LA_API int la_debug_chunk_trace(void *buf);
+/* Self-test of the watchdog (no counterpart in the reference): launches one CTA that waits, with
+ * a limit of limit_us microseconds (1 .. 1,000,000), on an mbarrier nothing ever arrives on.  The
+ * wait gives up, the kernel returns by itself and la_device_status() then reads 199. */
+LA_API int la_debug_wait_probe(int64_t limit_us, void *stream);
 
 /* Self-test of the tensor-core building blocks (no counterpart in the reference): one
  * 128x128x128 product D (fp32, row-major) from a, b (128x128, 16-bit, row-major, 16-byte aligned)

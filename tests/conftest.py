@@ -25,3 +25,26 @@ def pytest_configure(config):
 def lib():
     from xopes_b200 import _lib
     return _lib.load()
+
+
+@pytest.fixture(autouse=True)
+def _device_status_stays_clear(request):
+    """After every GPU test the watchdog word must read 0: a bounded wait that ran out inside a
+    kernel leaves undefined outputs behind an LA_OK return code, which a parity assert might not
+    notice.  Tests that make a wait run out on purpose clear the word themselves."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    import ctypes
+
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from xopes_b200 import _lib
+    lib = _lib.load()
+    word = ctypes.c_int(-1)
+    assert lib.la_device_status(None, ctypes.byref(word)) == 0
+    if word.value != 0:
+        lib.la_device_status_clear(None)
+        torch.cuda.synchronize()
+        pytest.fail(f"device status word reads {word.value} after the test: a bounded wait gave up")

@@ -65,6 +65,16 @@ def test_argument_checks_return_codes_without_a_gpu(lib):
     rc = lib.la_lasd_fwd(one, one, one, one, 0, 0, 1, None, one, one, None,
                          2, 4, 2, 8, 8, 3, _lib.LA_F32, 0, None)
     assert rc == -2
+    # a document count without cu_seqlens (scratch would be sized for M, kernels would run B)
+    rc = lib.la_lasd_fwd(one, one, one, one, 0, 0, 1, None, None, one, None,
+                         4, 4, 2, 8, 8, 1, _lib.LA_F32, 0, None)
+    assert rc == -2
+    rc = lib.la_lasd_bwd_noalloc(one, one, one, one, 0, 0, 1, None, one, None, None, one, one, one, one, None,
+                                 4, 4, 32, 128, 128, 1, _lib.LA_BF16, 0, None)
+    assert rc == -2
+    rc = lib.la_lavd_bwd(one, one, one, one, None, None, one, None, None, one, one, one, one, None, None,
+                         None, 0, 4, 4, 2, 8, 8, 1, _lib.LA_F32, 0, None)
+    assert rc == -2
     # unknown dtype
     rc = lib.la_lasd_fwd(one, one, one, one, 0, 0, 1, None, None, one, None,
                          1, 4, 2, 8, 8, 0, 9, 0, None)
@@ -77,6 +87,17 @@ def test_argument_checks_return_codes_without_a_gpu(lib):
     rc = lib.la_lasd_bwd(one, one, one, one, 0, 0, 1, None, one, None, None, one, one, one, one,
                          None, None, 0, 1, 4, 2, 8, 8, 0, _lib.LA_F32, 0, None)
     assert rc == -7
+
+
+def test_importing_the_package_maps_no_native_code():
+    """The input generators must be importable without loading the CUDA library (the CPU
+    reference arm of the benchmark uses them)."""
+    import subprocess
+    import sys
+    code = ("import xopes_b200.workloads, sys; "
+            "maps = open('/proc/self/maps').read(); "
+            "sys.exit(1 if 'libxopes_b200' in maps else 0)")
+    assert subprocess.run([sys.executable, "-c", code], cwd=ROOT).returncode == 0
 
 
 def test_workspace_sizes(lib):

@@ -151,7 +151,7 @@ def test_lasd_reference_shapes_fp32(shape, use_state, use_dfinal):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(2, 300, 4, 128, 128), (1, 128, 2, 128, 128), (2, 200, 3, 64, 64),
-                                   (1, 1, 2, 128, 128), (1, 513, 2, 128, 128)])
+                                   (1, 1, 2, 128, 128), (1, 513, 2, 128, 128), (1, 129, 3, 128, 128)])
 def test_lasd_16bit(shape, dtype):
     import xopes_b200 as xb
     _run_lasd_case(xb.lasd_fn, *shape, seed=7, dtype=dtype, use_state=True, use_dfinal=True,

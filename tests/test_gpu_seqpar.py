@@ -61,7 +61,7 @@ def test_segmented_forward_inside_one_gpu(b, n, h, per_head):
     from xopes_b200.lightning_attn import segmented as sg
     d = e = 128
     dtype = torch.bfloat16
-    assert sg.worth_segmenting([(i * n, (i + 1) * n) for i in range(b)], h, sg.auto_cap(b * n, h))
+    assert sg.worth_segmenting([(i * n, (i + 1) * n) for i in range(b)], h, sg.auto_cap(b * n, h, sg.num_sms()), sg.num_sms())
     g = torch.Generator().manual_seed(3)
     cast = lambda t: t.to(dtype).float()  # noqa: E731
     q = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)

@@ -105,12 +105,12 @@ def test_protocol_over_gloo_ranks(world, lens, per_head, exchange):
 
 def test_segment_planning():
     from xopes_b200.lightning_attn import segmented as sg
-    assert sg.auto_cap(131072, 16) % 128 == 0 and sg.auto_cap(100, 16) == 1024
+    assert sg.auto_cap(131072, 16, 148) % 128 == 0 and sg.auto_cap(100, 16, 148) == 1024
     seg_cu, first, last = sg.plan_segments([(0, 300), (300, 5000), (5000, 5100)], 1024)
     assert seg_cu[0] == 0 and seg_cu[-1] == 5100 and len(seg_cu) == len(first) + 1
     assert first == [1, 1, 0, 0, 0, 0, 1] and last == [0, 5, 6]
     # cuts inside a document fall on its 128-token chunk boundaries
     for i in range(2, 6):
         assert (seg_cu[i] - 300) % 128 == 0
-    assert not sg.worth_segmenting([(0, 8192)] * 8, 32, sg.auto_cap(8 * 8192, 32))   # plenty of CTAs already
-    assert sg.worth_segmenting([(0, 32768)], 16, sg.auto_cap(32768, 16))
+    assert not sg.worth_segmenting([(0, 8192)] * 8, 32, sg.auto_cap(8 * 8192, 32, 148), 148)   # plenty of CTAs already
+    assert sg.worth_segmenting([(0, 32768)], 16, sg.auto_cap(32768, 16, 148), 148)

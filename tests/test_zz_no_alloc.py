@@ -63,14 +63,18 @@ def _call(lib, t, out, noalloc):
 
 
 @pytest.mark.parametrize("shape,dtype", [((2, 150, 3, 32, 48), torch.float32),       # scan kernels
-                                         ((1, 300, 2, 128, 128), torch.bfloat16)])   # tcgen05 kernels
+                                         ((1, 300, 2, 128, 128), torch.bfloat16),    # tcgen05 kernels
+                                         ((1, 129, 3, 128, 128), torch.bfloat16)])   # odd B*N*H
 def test_noalloc_matches_caller_scratch_twice_in_a_row(lib, shape, dtype):
     for seed in (1, 2):  # second call reuses the array with the first call's leftovers in it
         t = _inputs(seed, *shape, dtype)
         ref, got = _outputs(t), _outputs(t)
         assert _call(lib, t, ref, noalloc=False) == 0
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         assert _call(lib, t, got, noalloc=True) == 0
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the no-allocation entry point took device memory"
         for name in ref:
             assert_close(f"{name} (call {seed})", ref[name].float(), got[name].float(), 1e-6)
 

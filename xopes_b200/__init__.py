@@ -1,17 +1,13 @@
 """xopes_b200: B200-native (sm_100a) lightning attention -- a drop-in for xopes/ops/lightning_attn.
 
 The compute lives in libxopes_b200.so (hand-written CUDA behind a C ABI, include/xopes_b200.h);
-this package is the host-side mirror of the reference's Python operator interface.  Importing it
-loads the shared library and fails loudly if it has not been built.
+this package is the host-side mirror of the reference's Python operator interface.  The shared
+library is loaded by the first operator call (or by xopes_b200.load_library()), which fails loudly
+if it has not been built: there is no CPU or PyTorch fallback.  Importing the package alone maps no
+native code, so tools that only need the input generators (xopes_b200.workloads) stay pure Python.
 """
-import sys as _sys
-
 from . import _lib
-
-# `python -m xopes_b200.build` must be able to run before the library exists (or when it is stale)
-_BUILDING = "xopes_b200.build" in getattr(_sys, "orig_argv", [])
-if not _BUILDING:
-    _lib.load()
+from ._lib import load as load_library  # noqa: F401
 
 from .lightning_attn import *  # noqa: E402,F401,F403
 from .lightning_attn import __all__ as _la_all  # noqa: E402
@@ -41,4 +37,4 @@ def install_as_xopes():
     })
 
 
-__all__ = list(_la_all) + ["install_as_xopes"]
+__all__ = list(_la_all) + ["install_as_xopes", "load_library"]

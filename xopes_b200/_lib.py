@@ -9,8 +9,7 @@ import os
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-# XOPES_B200_LIB points at another build of the library (for A/B measurements)
-LIB_PATH = os.environ.get("XOPES_B200_LIB") or os.path.join(_PKG, "libxopes_b200.so")
+LIB_PATH = os.path.join(_PKG, "libxopes_b200.so")
 
 LA_F32, LA_BF16, LA_F16 = 0, 1, 2
 FLAG_FORCE_RECURRENCE = 1
@@ -28,7 +27,7 @@ SIGNATURES = {
     "la_device_status": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "la_device_status_clear": (_i32, [_vp]),
     "la_debug_lavd_unsafe": (_i32, [_vp, ctypes.POINTER(_i32)]),
-    "la_debug_chunk_trace": (_i32, [_vp]),
+    "la_debug_wait_probe": (_i32, [_i64, _vp]),
     "la_debug_umma_probe": (_i32, [_i32, _vp, _vp, _vp, _i32, _vp]),
     "la_lasd_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
                            _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),

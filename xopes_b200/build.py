@@ -51,9 +51,7 @@ def _compile(src, force, verbose):
     if (not force and os.path.exists(obj)
             and os.path.getmtime(obj) >= max(os.path.getmtime(srcp), _deps_mtime())):
         return obj, ""
-    # extra flags, e.g. XOPES_B200_NVCC_FLAGS="-DLA_CHUNK_TRACE" to compile the phase tracing in
-    extra = os.environ.get("XOPES_B200_NVCC_FLAGS", "").split()
-    cmd = [_nvcc()] + NVCC_FLAGS + extra + ["-c", srcp, "-o", obj]
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-c", srcp, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))

@@ -97,6 +97,7 @@ int check_common(const void *q, const void *k, const void *v, int64_t B, int64_t
   if (q == nullptr || k == nullptr || v == nullptr) return LA_ERR_NULL_POINTER;
   if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
   if (cu != nullptr && (B != 1 || M <= 0)) return LA_ERR_BAD_SHAPE;
+  if (cu == nullptr && M != 0) return LA_ERR_BAD_SHAPE;  // M counts documents: meaningless without cu_seqlens
   if (!dtype_ok(dtype)) return LA_ERR_UNSUPPORTED;
   if (N > (int64_t)1 << 30 || B > 65535 || H > 65535 || M > 65535) return LA_ERR_TOO_LARGE;
   return LA_OK;
@@ -193,9 +194,9 @@ int la_debug_lavd_unsafe(void *stream, int *flag_out) {
   return LA_OK;
 }
 
-int la_debug_chunk_trace(void *buf) {
-  chunk_set_trace(static_cast<long long *>(buf));
-  return LA_OK;
+int la_debug_wait_probe(int64_t limit_us, void *stream) {
+  if (limit_us <= 0 || limit_us > 1000000) return LA_ERR_BAD_SHAPE;
+  return wait_probe((uint32_t)limit_us, static_cast<cudaStream_t>(stream));
 }
 
 int la_debug_umma_probe(int variant, const void *a, const void *b, float *d, int dtype, void *stream) {
@@ -229,12 +230,19 @@ int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, in
                       final_state, dtype, st);
 }
 
+// Workspace layout: [recomputed final state, rounded up to 16 bytes][row dots of q.dq][row dots of
+// k.dk].  The state comes first so that it is 16-byte aligned whatever B*N*H is (the chunk
+// kernel writes it with 128-bit stores).
+static int64_t lasd_ws_state_floats(int64_t nb, int64_t H, int64_t D, int64_t E) {
+  return (nb * H * D * E + 3) / 4 * 4;
+}
+
 int64_t la_lasd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
                                     int64_t M, int want_dld) {
   if (!want_dld) return 0;
   const int64_t nb = M > 0 ? M : B;
   const int nt = scan_row_tiles((int)D, (int)E, (int)H, (int)nb);
-  return ((int64_t)2 * nt * B * N * H + nb * H * D * E) * (int64_t)sizeof(float);
+  return (lasd_ws_state_floats(nb, H, D, E) + (int64_t)2 * nt * B * N * H) * (int64_t)sizeof(float);
 }
 
 // no_scratch: the chunk passes may not take hand-off scratch from the library's pool
@@ -260,9 +268,10 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     if (workspace == nullptr ||
         workspace_bytes < la_lasd_bwd_workspace_bytes(B, N, H, D, E, M, 1))
       return LA_ERR_WORKSPACE;
-    slots_q = static_cast<float *>(workspace);
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u) return LA_ERR_MISALIGNED;
+    ws_state = static_cast<float *>(workspace);
+    slots_q = ws_state + lasd_ws_state_floats(s.nb(), H, D, E);
     slots_k = slots_q + (int64_t)nt * bnh;
-    ws_state = slots_k + (int64_t)nt * bnh;
   }
   const bool state_term = want_dld && dfinal_state != nullptr;
 
@@ -366,7 +375,8 @@ int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, const float
                         const float *dfinal_state, const int64_t *cu_seqlens, void *dq, void *dk,
                         void *dv, float *dld, float *dinitial_state, int64_t B, int64_t N, int64_t H,
                         int64_t D, int64_t E, int64_t M, int dtype, unsigned flags, void *stream) {
-  if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  const int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc != LA_OK) return rc;
   const int64_t need = la_lasd_bwd_workspace_bytes(B, N, H, D, E, M, dld != nullptr);
   if (need > (int64_t)LA_NOALLOC_SCRATCH_BYTES) return LA_ERR_TOO_LARGE;
   void *scratch = noalloc_scratch_ptr();

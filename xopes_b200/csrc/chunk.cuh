@@ -69,9 +69,9 @@ int launch_seqpar_fold_segments(float *states, const float *G, const int *seg, f
                                 cudaStream_t st);
 int launch_seqpar_correct_multi(const void *q, void *o, const float *cum, const float *s_in, const int *seg,
                                 int nseg, int total_tiles, int N, int H, int dtype, cudaStream_t st);
-// phase timestamps of CTA 0 (2 x 4096 x 16 int64) are written to buf by later passes; null disables
-void chunk_set_trace(long long *buf);
-long long *chunk_get_trace();
+// One CTA waits on an mbarrier that nothing ever arrives on, with a limit of limit_us: the wait
+// gives up, records its code in the device status word and the kernel returns (chunk_sm100.cu).
+int wait_probe(uint32_t limit_us, cudaStream_t stream);
 // one 128x128x128 product through one operand staging variant (see chunk_sm100.cu)
 int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream);
 

@@ -106,7 +106,6 @@ struct ChunkArgs {
   const long long *cu;
   int B, N, H, M;
   int *status;
-  long long *trace;  // optional: clock64() at phase boundaries of CTA 0 (threads 0 and 32)
 };
 
 // How the (sequence, head) pairs of a launch are spread over its CTAs.
@@ -221,18 +220,6 @@ __device__ __forceinline__ int ld_acquire(const int *p) {
 __device__ __forceinline__ void st_release(int *p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-
-// trace[thread slot][chunk][point]: 16 points per chunk, 3 thread slots (threads 0 and 32 of the
-// compute warps, the tensor-core issue thread) of 4096 chunks at most
-#ifdef LA_CHUNK_TRACE
-#define LA_TRACE(point)                                                                   \
-  do {                                                                                    \
-    if (a.trace != nullptr && blockIdx.x == 0 && (tid == 0 || tid == 32 || tid == kMmaWarp * 32) && gi < 4096) \
-      a.trace[((tid == 0 ? 0 : (tid == 32 ? 1 : 2)) * 4096 + gi) * 16 + (point)] = clock64(); \
-  } while (0)
-#else
-#define LA_TRACE(point) do { } while (0)
-#endif
 
 // byte offset of the k-th 16-element slice of a K-major [128][128] tile (two boxes of 64 columns)
 __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) * kBoxBytes + (uint32_t)(ks & 3) * 32u; }
@@ -384,10 +371,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           const uint64_t d_ymn = desc_mnmajor(ys, kBoxBytes), d_zmn = desc_mnmajor(zs, kBoxBytes);
           // descriptor advance per 16-element K slice, in 16-byte units: K-major tiles step 32 B
           // inside a 128 B row and jump to the second box after 4 slices; MN-major tiles step 16 rows
-          LA_TRACE(0);
           mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
           tc_fence_after();
-          LA_TRACE(1);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
@@ -398,7 +383,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mbar_wait(bar_d, par, abort_flag, a.status, kStD);
           if (gi > 0) mbar_wait(bar_h, par ^ 1u, abort_flag, a.status, kStH);
           tc_fence_after();
-          LA_TRACE(2);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
@@ -419,7 +403,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mbar_wait(bar_y, par, abort_flag, a.status, kStY);
           mbar_wait(bar_fullz + 8 * s, ph, abort_flag, a.status, kStFull);
           tc_fence_after();
-          LA_TRACE(3);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
@@ -429,7 +412,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mma_commit(bar_empty + 8 * s);
           mbar_wait(bar_f, par, abort_flag, a.status, kStF);
           tc_fence_after();
-          LA_TRACE(4);
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ts(tmem + kColW1, tmem + kColP + (ks >> 1) * 32 + (ks & 1) * 8, d_zmn + (uint64_t)(ks * 128),
@@ -437,7 +419,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           mma_commit(bar_w);
           // the next chunk's X Y^T overwrites P, which the product above reads as P~
           mbar_wait(bar_w, par, abort_flag, a.status, kStW);
-          LA_TRACE(5);
         }
         g0 += tk.cnt;
       }
@@ -623,10 +604,10 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (tk.waits) {
           if (tid == 0) {
             const int *flag = sc.flags + (blockIdx.x - sc.npass);
-            uint32_t polls = 0;
+            const uint64_t t0 = globaltimer_ns();
             while (ld_acquire(flag) == 0 && *abort_flag == 0) {
               __nanosleep(200);
-              if (++polls > (1u << 22)) {
+              if (globaltimer_ns() - t0 > 2000000000ull) {  // 2 s
                 *abort_flag = 1;
                 atomicCAS(a.status, 0, kStHandoff);
               }
@@ -679,14 +660,12 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         uint8_t *stage = gbase + (size_t)s * kStageBytes;
         const float c_i = cur.c;
 
-        LA_TRACE(0);
         // ---- decays of the next chunk, while the tensor cores are still on this one's X Y^T
         Decay nxt{};
         if (it + 1 < nc) {  // uniform over the CTA
           nxt = decay_of(it + 1, ld_next, (gi + 1) & 1);
           ld_next = load_ld(it + 2);
         }
-        LA_TRACE(1);
         if (split) {
           // the epilogue dots the output with this row of xrow, read from global memory: start
           // that fetch now (one 128-byte line per thread) so that it is in cache by then
@@ -701,7 +680,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
         mbar_wait(bar_p, par, abort_flag, a.status, kStP);
         tc_fence_after();
-        LA_TRACE(2);
         {
           uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
           uint4 v[8];
@@ -724,7 +702,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         }
         fence_proxy_async();
         mbar_arrive(bar_y);
-        LA_TRACE(3);
 
         // ---- masked 16-bit P~ (first 16 columns of each 32-column batch of P).  This thread's
         // batches are wg and wg + 2 ({0,2} / {1,3} balances the triangular work); both loads
@@ -788,21 +765,17 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_f);
-        LA_TRACE(4);
 
         // ---- while the tensor cores finish this chunk: state copy of the next one
         if (it + 1 < nc) {  // uniform over the CTA
           mbar_wait(bar_t, par, abort_flag, a.status, kStT);  // T holds this chunk's final state
           tc_fence_after();
-          LA_TRACE(5);
           state_copy(nxt.eg);
         }
-        LA_TRACE(6);
 
         // ---- epilogue W = W1 + s_i W2 (this warpgroup's 64 columns)
         mbar_wait(bar_w, par, abort_flag, a.status, kStW);
         tc_fence_after();
-        LA_TRACE(7);
         const bool full_chunk = (L == kChunk);
         const long long row_off = row_base + (long long)n * kChunk * a.H * kChunk;
         const float s_i = cur.s;
@@ -857,7 +830,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (full_chunk) fence_proxy_async();
         tc_fence_before();
         mbar_arrive(bar_h);
-        LA_TRACE(8);
         cur = nxt;
       }
       g0 += nc;
@@ -917,8 +889,6 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-long long *g_trace = nullptr;
-
 // wprefix[s] = sum over sequences before s of max(chunks, 1); one block
 __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wprefix) {
   __shared__ long long part[1024];
@@ -947,50 +917,51 @@ __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wpre
 }
 
 struct DeviceInfo {
-  bool ready = false, attr_bf16 = false, attr_f16 = false;
-  int sms = 0;
-  cudaMemPool_t pool = nullptr;  // hand-off scratch; null if the pool could not be made
+  bool ready = false, attr_bf16 = false, attr_f16 = false, pool_tried = false;
+  int sms = 0, dev = 0;
+  cudaMemPool_t pool = nullptr;  // hand-off scratch; made on first need, null if that failed
 };
 
-// per-device facts and the stream-ordered pool the hand-off scratch comes from
+std::mutex g_info_mu;
+
+// per-device facts (no allocation of any kind)
 DeviceInfo *device_info() {
   static DeviceInfo info[64];
-  static std::mutex mu;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
+  std::lock_guard<std::mutex> lock(g_info_mu);
   DeviceInfo &d = info[dev];
   if (!d.ready) {
     if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
-    cudaMemPoolProps props = {};
-    props.allocType = cudaMemAllocationTypePinned;
-    props.handleTypes = cudaMemHandleTypeNone;
-    props.location.type = cudaMemLocationTypeDevice;
-    props.location.id = dev;
-    if (cudaMemPoolCreate(&d.pool, &props) == cudaSuccess) {
-      uint64_t keep = ~0ull;  // freed scratch stays in the pool for the next launch
-      cudaMemPoolSetAttribute(d.pool, cudaMemPoolAttrReleaseThreshold, &keep);
-    } else {
-      d.pool = nullptr;
-      cudaGetLastError();
-    }
+    d.dev = dev;
     d.ready = true;
   }
   return &d;
 }
 
-inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
-
-// XOPES_B200_CHUNK_SCHED (read once): bit 0 set = never split the chunk space evenly (one CTA per
-// pair), bit 1 set = never merge two passes into one launch.  For measurements.
-int sched_knob() {
-  static int v = -1;
-  if (v < 0) {
-    const char *e = getenv("XOPES_B200_CHUNK_SCHED");
-    v = e ? atoi(e) & 3 : 0;
+// The stream-ordered pool the hand-off scratch of the split schedule comes from; created by the
+// first launch that takes that schedule (never by a launch with no_scratch set).
+cudaMemPool_t handoff_pool(DeviceInfo *d) {
+  std::lock_guard<std::mutex> lock(g_info_mu);
+  if (!d->pool_tried) {
+    d->pool_tried = true;
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = d->dev;
+    if (cudaMemPoolCreate(&d->pool, &props) == cudaSuccess) {
+      uint64_t keep = ~0ull;  // freed scratch stays in the pool for the next launch
+      cudaMemPoolSetAttribute(d->pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    } else {
+      d->pool = nullptr;
+      cudaGetLastError();
+    }
   }
-  return v;
+  return d->pool;
 }
+
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <typename T>
 int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
@@ -1008,7 +979,6 @@ int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
-  a.trace = g_trace;
   return LA_OK;
 }
 
@@ -1043,14 +1013,14 @@ int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t str
   void *scratch = nullptr;
   // Worth it when whole pairs per CTA would leave SMs idle in the last round (always the case
   // with ragged documents).
-  if (!p.no_scratch && !(sched_knob() & 1) && g_trace == nullptr && di->pool != nullptr && ranges > 0 &&
-      pairs > ranges && (p.cu != nullptr || pairs % ranges != 0)) {
+  if (!p.no_scratch && ranges > 0 && pairs > ranges && (p.cu != nullptr || pairs % ranges != 0)) {
     // even split of the chunk space over one CTA per SM
     grid = (long long)ranges * npass;
     const size_t flag_bytes = round_up((size_t)grid * sizeof(int), 256);
     const size_t prefix_bytes = p.cu ? round_up(((size_t)p.M + 1) * sizeof(long long), 256) : 0;
     const size_t bytes = flag_bytes + prefix_bytes + (size_t)grid * kChunk * kChunk * sizeof(float);
-    if (cudaMallocFromPoolAsync(&scratch, bytes, di->pool, stream) != cudaSuccess) {
+    cudaMemPool_t pool = handoff_pool(di);
+    if (pool == nullptr || cudaMallocFromPoolAsync(&scratch, bytes, pool, stream) != cudaSuccess) {
       cudaGetLastError();
       scratch = nullptr;
       grid = pairs * npass;
@@ -1175,6 +1145,25 @@ umma_probe_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// The give-up path of mbar_wait on its own: the barrier below is initialised and never arrived on,
+// so the wait runs out after limit_us, raises the abort flag and records kStProbe; a second wait
+// on the same barrier must then return at once.
+constexpr int kStProbe = 199;
+__global__ void wait_probe_kernel(uint32_t limit_us, int *status) {
+  __shared__ unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int *af = &abort_flag;
+  mbar_wait(b, 0, af, status, kStProbe, limit_us);
+  mbar_wait(b, 0, af, status, kStProbe + 1, 1u << 22);  // returns at once: the CTA has given up
+}
+
 template <typename T>
 int probe_t(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream) {
   alignas(64) CUtensorMap ma, mb;
@@ -1200,8 +1189,12 @@ int umma_probe(int variant, const void *a, const void *b, float *d, int dtype, c
   return LA_ERR_UNSUPPORTED;
 }
 
-void chunk_set_trace(long long *buf) { g_trace = buf; }
-long long *chunk_get_trace() { return g_trace; }
+int wait_probe(uint32_t limit_us, cudaStream_t stream) {
+  int *status = status_word_ptr();
+  if (status == nullptr) return LA_ERR_CUDA;
+  wait_probe_kernel<<<1, 64, 0, stream>>>(limit_us, status);
+  return launch_status();
+}
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
   return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
@@ -1233,10 +1226,6 @@ int launch_chunk_pass_pair(const ChunkPass &p, const ChunkPass &q, int dtype, cu
   if (p.B != q.B || p.N != q.N || p.H != q.H || p.M != q.M || p.cu != q.cu || p.reverse != q.reverse ||
       p.ld != q.ld || p.ld_sb != q.ld_sb || p.ld_sn != q.ld_sn || p.ld_sh != q.ld_sh)
     return LA_ERR_BAD_SHAPE;
-  if (sched_knob() & 2) {
-    rc = launch_chunk_pass(p, dtype, stream);
-    return rc != LA_OK ? rc : launch_chunk_pass(q, dtype, stream);
-  }
   if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, &q, dtype, stream);
   if (dtype == LA_F16) return launch_t<__half>(p, &q, dtype, stream);
   return LA_ERR_UNSUPPORTED;

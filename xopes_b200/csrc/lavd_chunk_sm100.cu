@@ -98,18 +98,7 @@ struct LavdArgs {
   int B, N, H, M;
   int *status;
   int *unsafe;
-  long long *trace;  // optional: clock64() at phase boundaries of CTA 0, thread 0: [pass][chunk < 1024][16]
 };
-
-#ifdef LA_CHUNK_TRACE
-#define LV_TRACE(point)                                                              \
-  do {                                                                               \
-    if (a.trace != nullptr && blockIdx.x == 0 && tid == 0 && it < 1024)              \
-      a.trace[(((TMODE ? 1 : 0) + 2 * a.reverse) * 1024 + it) * 16 + (point)] = clock64(); \
-  } while (0)
-#else
-#define LV_TRACE(point) do { } while (0)
-#endif
 
 // byte offset of the float4 holding features [d, d+4) of row i in the 128B-swizzled fp32 decay tile
 __device__ __forceinline__ uint32_t ck_off(int i, int d) {
@@ -410,7 +399,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
       const uint32_t z_off = TMODE ? kOffU : kOffZ;
       if (TMODE) ck = gbase + ((it & 1) ? kOffY : kOffCk);
-      LV_TRACE(0);
       if (TMODE && a.dld != nullptr && i < L) {
         // the epilogue multiplies the output by this row of xrow, read from global memory: pull
         // it into L2 now (one 128-byte line per thread; L1 is too small beside 227 KB of shared
@@ -420,7 +408,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         asm volatile("prefetch.global.L2 [%0];" ::"l"(xr));
       }
       mbar_wait(full_ck, par, abort_flag, a.status, kStFull);
-      LV_TRACE(1);
 
       // ---- S: per-feature inclusive cumulative log2 decay down the 128 rows, centred on row 63.
       // Thread (dg = tid % 32, seg = tid / 32) scans the four features [4 dg, 4 dg + 4) over the
@@ -478,7 +465,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         named_bar_sync(1, kComputeThreads);
       }
 
-      LV_TRACE(2);
       // ---- R: rescale operands in place
       if (!TMODE) {  // T mode rescales Z only, which came with the decay tile
         mbar_wait(full_yz, par, abort_flag, a.status, kStFull);
@@ -494,7 +480,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       fence_proxy_async();
       mbar_arrive(bar_r);
       if (!TMODE) mbar_arrive(empty_ck);  // N mode reads the decay tile for the last time above
-      LV_TRACE(3);
 
       // ---- D: scaled 16-bit state copy (B operand of X T), decay of the resident state
       {
@@ -540,11 +525,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         mbar_arrive(bar_d);
       }
 
-      LV_TRACE(4);
       // ---- F: causal (or reverse-causal) 16-bit P~ in the first 16 columns of each 32-column batch
       mbar_wait(bar_p, par, abort_flag, a.status, kStP);
       tc_fence_after();
-      LV_TRACE(5);
 #pragma unroll 1
       for (int b2 = 0; b2 < 2; ++b2) {
         const int bt = wg + 2 * b2;
@@ -579,11 +562,9 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       tc_fence_before();
       mbar_arrive(bar_f);
 
-      LV_TRACE(6);
       // ---- H: epilogue
       mbar_wait(bar_w, par, abort_flag, a.status, kStW);
       tc_fence_after();
-      LV_TRACE(7);
       const bool full_chunk = (L == kChunk);
       const long long row_off = ((bidx * (long long)a.N + tok) * a.H + h) * (long long)kChunk;
       // packed fp32x2 arithmetic throughout: every product below is an fp32 multiply rounded to
@@ -679,7 +660,6 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (full_chunk) fence_proxy_async();
       tc_fence_before();
       mbar_arrive(bar_h);
-      LV_TRACE(8);
     }
 
     if (a.tfinal != nullptr) {  // end state -> global, with the factor still owed to it
@@ -738,7 +718,6 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
   a.status = status_word_ptr();
   a.unsafe = p.unsafe;
-  a.trace = chunk_get_trace();
   if (a.status == nullptr || a.unsafe == nullptr) return LA_ERR_CUDA;
   auto kern = lavd_pass_kernel<T, TMODE>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)

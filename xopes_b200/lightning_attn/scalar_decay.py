@@ -67,9 +67,10 @@ def _segmentation(lib, q, ld32, strides, cu, b, n, h, d, e, flags):
         return None
     if lib.la_lasd_path(n, d, e, _lib.dtype_code(q), flags) != 1:
         return None
-    cap = sg.auto_cap(b * n, h)
+    sms = sg.num_sms(q.device)
+    cap = sg.auto_cap(b * n, h, sms)
     bounds = [(i * n, (i + 1) * n) for i in range(b)]
-    if not sg.worth_segmenting(bounds, h, cap):
+    if not sg.worth_segmenting(bounds, h, cap, sms):
         return None
     sb, sn, sh = strides
     if sn == 0 and sb == 0:            # per-head constant

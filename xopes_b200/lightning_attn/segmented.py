@@ -16,12 +16,20 @@ import torch
 
 from .. import _lib
 
-NUM_SMS = 148
+_SMS = {}
 
 
-def auto_cap(total_tokens: int, h: int) -> int:
+def num_sms(device=None) -> int:
+    """SM count of the device (the same number the library's launch logic queries)."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SMS[idx]
+
+
+def auto_cap(total_tokens: int, h: int, sms: int) -> int:
     """Segment length (a multiple of the 128-token chunk) that yields about one CTA per SM."""
-    segs = max(1, NUM_SMS // max(1, h))
+    segs = max(1, sms // max(1, h))
     cap = -(-total_tokens // segs)
     return max(1024, -(-cap // 128) * 128)
 
@@ -46,7 +54,7 @@ def plan_segments(doc_bounds: List[Tuple[int, int]], cap: int):
     return seg_cu, first, last_of_doc
 
 
-def worth_segmenting(doc_bounds, h: int, cap: int) -> bool:
+def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
     """Segmenting pays an extra pass over the continued segments (768 B per token and head, about
     half of all tokens when every long sequence is cut once) plus a few small launches, so it is
     used only when the plain launch would leave most SMs idle or one sequence would run at least
@@ -55,9 +63,9 @@ def worth_segmenting(doc_bounds, h: int, cap: int) -> bool:
     ms with the stitching, i.e. no gain at 1.5-2.3 balanced shares."""
     ctas = len(doc_bounds) * h
     longest = max(b - a for a, b in doc_bounds)
-    if ctas <= NUM_SMS // 4:
+    if ctas <= sms // 4:
         return longest > cap + cap // 2
-    return ctas < NUM_SMS and longest >= 3 * cap
+    return ctas < sms and longest >= 3 * cap
 
 
 class _Plan:

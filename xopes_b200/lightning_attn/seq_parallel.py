@@ -74,10 +74,11 @@ def _cuda_local_forward(q, k, v, ld, local_cu):
     _, t, h, d = q.shape
     e = v.shape[-1]
     bounds = [(local_cu[i], local_cu[i + 1]) for i in range(len(local_cu) - 1)]
-    cap = sg.auto_cap(t, h)
+    sms = sg.num_sms(q.device) if q.is_cuda else 148
+    cap = sg.auto_cap(t, h, sms)
     lib = _lib.load()
     if (q.is_cuda and lib.la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1
-            and sg.worth_segmenting(bounds, h, cap)):
+            and sg.worth_segmenting(bounds, h, cap, sms)):
         # few long documents on this rank: cut them further so that every SM has a segment
         ld32, strides = _prep_ld(ld, 1, t, h)
         with torch.no_grad():

@@ -82,25 +82,28 @@ def varlen_doc_lengths(n_total, n_docs, seed=0):
 
 
 def varlen_inputs(n_total, n_docs, h, d, e, dtype=torch.bfloat16, seed=0, block=65536,
-                  token_range=None):
+                  token_range=None, device="cpu"):
     """Configuration 5: one packed stream, q,k,v ~ N(0,1), q and k scaled by 1/sqrt(D);
     ld_h = log(1 - 2^(-5 - h/2)).  The stream is generated in blocks of `block` tokens, each from
     its own generator seeded by (seed, block index), so a rank can generate just its own token
-    range [a, b) and still see exactly the values of the whole stream."""
+    range [a, b) and still see exactly the values of the whole stream.  With a CUDA `device` the
+    blocks are drawn by that device's generator (the same values on every GPU of one model, not
+    the CPU generator's values): the 1M-token stream is 6 G normal variates, minutes on the host."""
     lens = varlen_doc_lengths(n_total, n_docs, seed)
     cu = torch.zeros(n_docs + 1, dtype=torch.int64)
     cu[1:] = torch.cumsum(lens, 0)
     a, b = token_range if token_range is not None else (0, n_total)
-    q = torch.empty(1, b - a, h, d, dtype=dtype)
-    k = torch.empty(1, b - a, h, d, dtype=dtype)
-    v = torch.empty(1, b - a, h, e, dtype=dtype)
+    device = torch.device(device)
+    q = torch.empty(1, b - a, h, d, dtype=dtype, device=device)
+    k = torch.empty(1, b - a, h, d, dtype=dtype, device=device)
+    v = torch.empty(1, b - a, h, e, dtype=dtype, device=device)
     for j in range(a // block, (b + block - 1) // block):
         s0, s1 = j * block, min((j + 1) * block, n_total)
         t = s1 - s0
-        g = _gen((seed + 1) * 100003 + j)
-        qb = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
-        kb = (torch.randn(t, h, d, generator=g) * d ** -0.5).to(dtype)
-        vb = torch.randn(t, h, e, generator=g).to(dtype)
+        g = torch.Generator(device=device).manual_seed((seed + 1) * 100003 + j)
+        qb = (torch.randn(t, h, d, generator=g, device=device) * d ** -0.5).to(dtype)
+        kb = (torch.randn(t, h, d, generator=g, device=device) * d ** -0.5).to(dtype)
+        vb = torch.randn(t, h, e, generator=g, device=device).to(dtype)
         lo, hi = max(s0, a), min(s1, b)
         q[0, lo - a:hi - a] = qb[lo - s0:hi - s0]
         k[0, lo - a:hi - a] = kb[lo - s0:hi - s0]
