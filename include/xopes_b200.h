@@ -65,9 +65,10 @@ LA_API int la_lasd_path(int64_t N, int64_t D, int64_t E, int dtype, unsigned fla
 LA_API int la_device_status(void *stream, int *status_out);
 LA_API int la_device_status_clear(void *stream);
 
-/* Reads (and synchronises the stream for) the word the last vector-decay call on this GPU left:
- * non-zero means it fell back from the tensor-core kernels to the scan kernels.  No counterpart in
- * the reference. */
+/* Reads (and synchronises the stream for) what the last vector-decay call on this GPU left behind:
+ * 0 = it ran on the one-reference tensor-core kernels, 1 = a chunk decayed too fast for those and
+ * the two-reference tensor-core kernels reran it, 2 = those gave up too and the scan kernels reran
+ * it.  No counterpart in the reference. */
 LA_API int la_debug_lavd_unsafe(void *stream, int *flag_out);
 
 /* Self-test of the watchdog (no counterpart in the reference): launches one CTA that waits, with
@@ -149,10 +150,12 @@ LA_API int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, cons
  * ------------------------------------------------------------------------------------------- */
 
 /* Which kernel family a vector-decay call runs: 1 = tcgen05/TMA chunk kernels (16-bit inputs,
- * D = E = 128, N >= 128, ldk only), 0 = fp32 scan kernels.  On path 1 a chunk whose decay is too
- * strong for the tensor-core formulation (more than 2^-64 over half a chunk for bf16, 2^-10 for
- * fp16) makes the same call
- * rerun on the scan kernels, decided on the device.  The flag word behind that decision is one per
+ * D = E = 128, N >= 128, ldk only), 0 = fp32 scan kernels.  On path 1 the decay decides, on the
+ * device, how far the call gets: the one-reference kernels handle chunks whose halves (64 tokens)
+ * decay by at most 2^-64 per feature (bf16; 2^-10 for fp16); if a chunk exceeds that, the
+ * two-reference kernels rerun the call (safe while every 32-token quarter decays by at most 2^-96;
+ * the reference's own benchmark decay logsigmoid(N(0,1)) is about 2^-37 per quarter); if a chunk
+ * exceeds that too, the scan kernels rerun it.  The two flag words behind those decisions are per
  * GPU: vector-decay calls whose kernels overlap on one GPU must be serialised. */
 LA_API int la_lavd_path(int64_t N, int64_t D, int64_t E, int dtype, int has_ldk, int has_ldv,
                         unsigned flags);

@@ -15,18 +15,14 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda"
 
-# The log-decay gradient is a reverse cumulative sum over the whole sequence of
-# (q.dq - k.dk), two large terms that nearly cancel (the reference forms it the same way,
-# log_decay_with_cumsum/dld_with_cumsum_triton.py:20-133).  With 16-bit operands the rounding of
-# the 16-bit state copy fed to the tensor cores does not cancel between the dq and dk passes and
-# random-walks through the cumulative sum and grows with the sequence length, so dld alone gets a
-# wider bound for 16-bit inputs (measured with the split state copy: bf16 7e-3 at N=300, 1.8e-2
-# at N=2048; fp16 1e-3).  Every other output keeps 1e-2.
-TOL_DLD_16BIT = 3e-2
-
-
+# The log-decay gradient is a reverse cumulative sum over the whole sequence of (q.dq - k.dk), two
+# large terms that nearly cancel (the reference forms it the same way,
+# log_decay_with_cumsum/dld_with_cumsum_triton.py:20-133).  It keeps the same 1e-2 bound as every
+# other 16-bit output: when it is requested the kernels feed the state copy and the rescaled
+# state-update operand to the tensor cores as high + low 16-bit halves, so that the inter-chunk parts
+# of the two terms cancel (measured: 1e-3 .. 3e-3 from N = 128 to N = 16384).
 def dld_tol(dtype, tol):
-    return tol if dtype == torch.float32 else TOL_DLD_16BIT
+    return tol
 
 
 def cuda(g):
@@ -246,13 +242,16 @@ def _lavd_unsafe_flag(lib):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("regime", ["weak", "medium", "strong"])
+@pytest.mark.parametrize("regime", ["weak", "medium", "reference_benchmark", "strong"])
 @pytest.mark.parametrize("shape,lens", [((2, 384, 2), None), ((1, 300, 3), None), ((1, 128, 1), None),
-                                        ((1, 700, 2), [1, 127, 128, 129, 300, 15])])
+                                        ((1, 700, 2), [1, 127, 128, 129, 300, 15]), ((1, 2048, 2), None)])
 def test_lavd_tensor_path(shape, lens, regime, dtype, lib):
     """Vector decay (ldk only) with D = E = 128 in 16 bit: the tcgen05 chunk kernels.  "weak" is the
-    benchmark's decay (logsigmoid(x)/16) and must stay on the tensor path; "strong" decays by far
-    more than 2^-64 per half chunk and must fall back to the scan kernels on its own."""
+    benchmark configuration's decay (logsigmoid(x)/16) and must stay on the one-reference kernels;
+    "reference_benchmark" is the decay of the reference's own benchmark script
+    (logsigmoid(N(0,1)), benchmarks/lightning_attention/benchmark.py:315), about 2^-74 per half
+    chunk: it must be served by the two-reference tensor-core kernels (bf16), not by the scan;
+    "strong" decays by far more than 2^-96 per 32 tokens and must fall back to the scan kernels."""
     import xopes_b200 as xb
     from xopes_b200 import _lib
     b, n, h = shape
@@ -263,6 +262,7 @@ def test_lavd_tensor_path(shape, lens, regime, dtype, lib):
     x = torch.randn(b, n, h, d, generator=g)
     ldk = {"weak": torch.nn.functional.logsigmoid(x) / 16,
            "medium": torch.nn.functional.logsigmoid(x + 1),
+           "reference_benchmark": torch.nn.functional.logsigmoid(x),
            "strong": torch.nn.functional.logsigmoid(x * 2 - 4)}[regime]
     qf = cast(torch.randn(b, n, h, d, generator=g))
     kf = cast((1 - torch.exp(ldk)) * torch.randn(b, n, h, d, generator=g) * d ** -0.5)
@@ -281,15 +281,48 @@ def test_lavd_tensor_path(shape, lens, regime, dtype, lib):
     ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
     flag_bwd = _lavd_unsafe_flag(lib)
     if regime == "weak":
-        assert flag_fwd == 0 and flag_bwd == 0, "benchmark-range decays must stay on the tensor path"
+        assert flag_fwd == 0 and flag_bwd == 0, "benchmark-range decays must stay on the one-reference kernels"
+    if regime == "reference_benchmark" and dtype == torch.bfloat16:
+        assert flag_fwd <= 1 and flag_bwd <= 1, "logsigmoid(N(0,1)) decays must stay on the tensor cores"
+        if n >= 2048:
+            assert flag_fwd == 1 and flag_bwd == 1, "expected the two-reference kernels to serve this"
     if regime == "strong":
-        assert flag_fwd != 0 and flag_bwd != 0, "out-of-range decays must fall back"
+        assert flag_fwd == 2 and flag_bwd == 2, "out-of-range decays must fall back to the scan"
     rq, rk, rv, rlk, _, rs0 = orc.lavd_backward(qf, kf, vf, ldk, None, dof, s0, dsf, cu)
     assert_close("dq", rq, q.grad.float(), TOL_BF16)
     assert_close("dk", rk, k.grad.float(), TOL_BF16)
     assert_close("dv", rv, v.grad.float(), TOL_BF16)
-    assert_close("dldk", rlk, lk.grad, TOL_DLD_16BIT)
+    assert_close("dldk", rlk, lk.grad, TOL_BF16)
     assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
+def test_lavd_benchmark_length_slice():
+    """A (B=1, H=2) slice of benchmark configuration 3 at its full length N = 16384 (bf16,
+    ldk = logsigmoid(x)/16, k = (1 - exp(ldk)) k_raw, no initial state): every gradient the
+    configuration asks for, including the log-decay gradient, within 1e-2."""
+    import xopes_b200 as xb
+    from xopes_b200 import workloads
+    w = workloads.lavd_inputs(1, 16384, 2, 128, 128, torch.bfloat16, seed=3)
+    q, k, v, lk = (w[x].to(DEV).requires_grad_() for x in ("q", "k", "v", "ldk"))
+    o, sf = xb.lightning_attn_func(q, k, v, ldk=lk, decay_type="vector")
+    o.backward(w["do"].to(DEV))
+    f = {n: t.float() for n, t in w.items()}
+    ro, rsf = orc.lavd_forward(f["q"], f["k"], f["v"], f["ldk"], None)
+    rq, rk, rv, rlk, _, _ = orc.lavd_backward(f["q"], f["k"], f["v"], f["ldk"], None, f["do"])
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    assert_close("dldk", rlk, lk.grad, TOL_BF16)
+
+
+def test_lasd_benchmark_length_slice_with_decay_gradient():
+    """A (B=1, H=2) slice at the length of benchmark configuration 2 (N = 8192, bf16) with a
+    data-dependent decay whose gradient is requested, an initial state and a final-state gradient."""
+    import xopes_b200 as xb
+    _run_lasd_case(xb.lasd_fn, 1, 8192, 2, 128, 128, seed=13, dtype=torch.bfloat16, use_state=True,
+                   use_dfinal=True, weak_decay=False, tol=TOL_BF16)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -20,9 +20,10 @@ int *status_word_ptr() {
   return ptrs[dev];
 }
 
-__device__ int g_lavd_unsafe = 0;
+// [0]: raised by the one-reference vector-decay chunk kernels when a chunk leaves their safe range
+// (the two-reference kernels then run); [1]: raised by those in turn (the scan kernels then run)
+__device__ int g_lavd_unsafe[2] = {0, 0};
 
-// device word the vector-decay chunk kernels raise when the inputs leave their safe range
 static int *lavd_unsafe_ptr() {
   static int *ptrs[64] = {nullptr};
   int dev = 0;
@@ -189,8 +190,10 @@ int la_debug_lavd_unsafe(void *stream, int *flag_out) {
   int *p = lavd_unsafe_ptr();
   if (p == nullptr) return LA_ERR_CUDA;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (cudaMemcpyAsync(flag_out, p, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return LA_ERR_CUDA;
+  int w[2] = {0, 0};
+  if (cudaMemcpyAsync(w, p, sizeof(w), cudaMemcpyDeviceToHost, st) != cudaSuccess) return LA_ERR_CUDA;
   if (cudaStreamSynchronize(st) != cudaSuccess) return LA_ERR_CUDA;
+  *flag_out = w[1] != 0 ? 2 : (w[0] != 0 ? 1 : 0);
   return LA_OK;
 }
 
@@ -414,12 +417,15 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
   if (path == 1) {
     int *unsafe = lavd_unsafe_ptr();
     if (unsafe == nullptr) return LA_ERR_CUDA;
-    if (cudaMemsetAsync(unsafe, 0, sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
+    if (cudaMemsetAsync(unsafe, 0, 2 * sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
     c.x = q; c.y = k; c.z = v; c.ldk = ldk; c.out = o; c.t0 = initial_state; c.tfinal = final_state;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
-    enable = unsafe;  // the scan below runs only if a chunk left the tensor path's safe range
+    // the two-reference kernels run only if a chunk left the one-reference range ...
+    c.ref2 = 1; c.enable = unsafe; c.unsafe = unsafe + 1;
+    if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
+    enable = unsafe + 1;  // ... and the scan below only if one left theirs too
   }
   return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype, st,
                       enable);
@@ -457,7 +463,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if (path == 1) {
     int *unsafe = lavd_unsafe_ptr();
     if (unsafe == nullptr) return LA_ERR_CUDA;
-    if (cudaMemsetAsync(unsafe, 0, sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
+    if (cudaMemsetAsync(unsafe, 0, 2 * sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
@@ -480,10 +486,25 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     // dq then adds to a zeroed gradient buffer instead of storing into it, so that it and dk may
     // touch a tile in either order.
     const bool all3 = side != nullptr && 2 * pairs <= sm_count();
+    // The same three passes with two reference rows per chunk, enqueued behind the first set and
+    // run only if that set raised its word: dv beside dq and dk when a side stream is in use, dq
+    // before dk (dk subtracts from the terms dq stored).
+    auto second_set = [&](cudaStream_t s_v) -> int {
+      LavdPass v2 = cv, q2 = cq, k2 = ck;
+      v2.ref2 = q2.ref2 = k2.ref2 = 1;
+      v2.enable = q2.enable = k2.enable = unsafe;
+      v2.unsafe = q2.unsafe = k2.unsafe = unsafe + 1;
+      q2.dld_add = k2.dld_add = 0;
+      int r2 = launch_lavd_pass(v2, dtype, s_v);
+      if (r2 == LA_OK) r2 = launch_lavd_pass(q2, dtype, st);
+      if (r2 == LA_OK) r2 = launch_lavd_pass(k2, dtype, st);
+      return r2;
+    };
     if (side == nullptr) {
       rc = launch_lavd_pass(cq, dtype, st);
       if (rc == LA_OK) rc = launch_lavd_pass(ck, dtype, st);
       if (rc == LA_OK) rc = launch_lavd_pass(cv, dtype, st);
+      if (rc == LA_OK) rc = second_set(st);
     } else {
       std::unique_lock<std::mutex> side_lock(side->mu);
       if (all3) {
@@ -502,9 +523,14 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
         if (rc == LA_OK) rc = launch_lavd_pass(ck, dtype, st);
       }
       if (!side_join(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
+      if (rc == LA_OK) {  // second set: fork again, dv on the side stream
+        if (!side_fork(side, st)) return LA_ERR_CUDA;
+        rc = second_set(side->stream);
+        if (!side_join(side, st) && rc == LA_OK) rc = LA_ERR_CUDA;
+      }
     }
     if (rc != LA_OK) return rc;
-    enable = unsafe;
+    enable = unsafe + 1;
   }
   ScanParams p;
   if (ldv != nullptr) {

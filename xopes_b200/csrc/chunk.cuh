@@ -41,8 +41,11 @@ int launch_chunk_pass_pair(const ChunkPass &p, const ChunkPass &q, int dtype, cu
 // One directional vector-decay (ldk) pass on tcgen05 (lavd_chunk_sm100.cu).  tmode = 0: the decay
 // acts on the contraction dimension of X Y^T (o and dv passes); tmode = 1: on the output dimension
 // (dq and dk passes, state transposed), with the optional log-decay-gradient accumulation
-// dld (+)= xrow * W.  `unsafe` is raised when a chunk's decay exceeds the range of the mid-chunk
-// reference; the caller then reruns on the scan kernels, predicated on that word.
+// dld (+)= xrow * W.  ref2 = 0: one reference row per chunk, safe while half a chunk decays by at
+// most 2^-64 (bf16); ref2 = 1: two reference rows, safe while a 32-row quarter decays by at most
+// 2^-96.  `unsafe` is raised when a chunk exceeds that range; the caller then reruns the next
+// formulation (two references, then the scan kernels), each predicated on the previous one's word
+// through `enable`.
 struct LavdPass {
   const void *x = nullptr, *y = nullptr, *z = nullptr;
   const float *ldk = nullptr;
@@ -57,6 +60,8 @@ struct LavdPass {
   const int64_t *cu = nullptr;
   int B = 0, N = 0, H = 0, M = 0;
   int *unsafe = nullptr;
+  int ref2 = 0;
+  const int *enable = nullptr;  // optional device word: the launch does nothing while it reads 0
 };
 bool lavd_chunk_supported(int64_t N, int64_t D, int64_t E, int dtype, bool has_ldk, bool has_ldv);
 int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream);

@@ -60,7 +60,7 @@ constexpr uint32_t kColT = 0, kColP = 128, kColW1 = 256, kColW2 = 384;
 
 // status codes written to the device status word
 constexpr int kStFull = 101, kStEmpty = 102, kStP = 103, kStW = 104, kStD = 105, kStF = 106, kStH = 107,
-              kStT = 108, kStY = 109, kStX = 110, kStL = 111;
+              kStT = 108, kStY = 109, kStX = 110, kStL = 111, kStU = 113;
 
 struct Small {
   // X and Y of a stage are released as soon as the products that read them are done (mid-chunk);
@@ -78,6 +78,7 @@ struct Small {
   unsigned long long bar_h;   // output tile staged, W1/W2 consumed        (compute -> store and MMA warps)
   unsigned long long bar_x;   // X T_in with the high half of the state copy complete (MMA warp -> compute)
   unsigned long long bar_l;   // low half of the state copy written, T rescaled (compute -> MMA warp)
+  unsigned long long bar_u;   // X T_in with the low half complete: the copy tile is free (MMA warp -> compute)
   uint32_t tmem_base;
   int abort_flag;
   int issued;    // chunks whose X and Y loads were issued
@@ -272,10 +273,14 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
   const uint32_t bar_p = smem_u32(&sm->bar_p), bar_w = smem_u32(&sm->bar_w);
   const uint32_t bar_d = smem_u32(&sm->bar_d), bar_f = smem_u32(&sm->bar_f), bar_h = smem_u32(&sm->bar_h);
   const uint32_t bar_t = smem_u32(&sm->bar_t), bar_y = smem_u32(&sm->bar_y);
-  const uint32_t bar_x = smem_u32(&sm->bar_x), bar_l = smem_u32(&sm->bar_l);
+  const uint32_t bar_x = smem_u32(&sm->bar_x), bar_l = smem_u32(&sm->bar_l), bar_u = smem_u32(&sm->bar_u);
   // With a log-decay gradient requested the 16-bit state copy is split into a high and a low
   // half (two passes of X T_in over the same buffer): the gradient is a long cumulative sum of
-  // nearly cancelling terms and the rounding of a single 16-bit copy dominates its error.
+  // nearly cancelling terms and the rounding of a single 16-bit copy dominates its error.  For the
+  // same reason the rescaled operand Y (.) u of the state update is then fed to the tensor cores as
+  // a high and a low 16-bit half (the low half borrows the copy tile once X T_in is done with it):
+  // the states the dq pass and the dk pass build must agree to well below 16-bit rounding for the
+  // inter-chunk terms of q.dq and k.dk to cancel.
   const bool split = ap.rowdot != nullptr;
   volatile int *abort_flag = &sm->abort_flag;
 
@@ -290,6 +295,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
     mbar_init(bar_w, 1);
     mbar_init(bar_t, 1);
     mbar_init(bar_x, 1);
+    mbar_init(bar_u, 1);
     mbar_init(bar_l, kComputeThreads);
     mbar_init(bar_d, kComputeThreads);
     mbar_init(bar_y, kComputeThreads);
@@ -397,6 +403,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
               const uint64_t ko = (uint64_t)((ks >> 2) * (kBoxBytes >> 4) + (ks & 3) * 2);
               mma_ss(tmem + kColW2, d_xk + ko, d_tb + (uint64_t)(ks * 128), idesc_kmn, 1);
             }
+            mma_commit(bar_u);  // the copy tile may now take the low half of Y (.) u
           }
           // T += (Y (.) u)^T Z as soon as the rescaled Y is there; its completion frees T for the
           // next chunk's state copy while P~ Z still runs
@@ -406,6 +413,11 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             mma_ss(tmem + kColT, d_ymn + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+          if (split) {  // low half of Y (.) u, in the copy tile (same layout as Y)
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              mma_ss(tmem + kColT, d_tb + (uint64_t)(ks * 128), d_zmn + (uint64_t)(ks * 128), idesc_mnmn, 1);
+          }
           mma_commit(bar_t);
           // every product that reads this stage's X or Y has been issued: the producer may refill
           // them (for the chunk after the next one) as soon as those products are done
@@ -680,7 +692,29 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         mbar_wait(bar_full + 8 * s, ph, abort_flag, a.status, kStFull);
         mbar_wait(bar_p, par, abort_flag, a.status, kStP);
         tc_fence_after();
-        {
+        if (split) {
+          // high half in place, low half into the copy tile, once X T_lo has let go of it
+          mbar_wait(bar_u, par, abort_flag, a.status, kStU);
+          uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
+          uint8_t *lbox = gbase + kOffTb + wg * kBoxBytes;
+          const float2 u2 = make_float2(cur.u, cur.u);
+#pragma unroll 2
+          for (int pc = 0; pc < 8; ++pc) {
+            const uint32_t off = sw128_offset(i, pc);
+            const uint4 y = *reinterpret_cast<const uint4 *>(ybox + off);
+            const uint32_t yw[4] = {y.x, y.y, y.z, y.w};
+            uint32_t hw[4], lw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 p = mul2(Fmt<T>::unpack(yw[j]), u2);
+              hw[j] = Fmt<T>::pack(p.x, p.y);
+              const float2 hf = Fmt<T>::unpack(hw[j]);
+              lw[j] = Fmt<T>::pack(p.x - hf.x, p.y - hf.y);
+            }
+            *reinterpret_cast<uint4 *>(ybox + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4 *>(lbox + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+          }
+        } else {
           uint8_t *ybox = stage + kTileBytes + wg * kBoxBytes;
           uint4 v[8];
 #pragma unroll
