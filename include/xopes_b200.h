@@ -184,6 +184,38 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
                 void *stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Cutting long sequences into segments that run in parallel (no counterpart in the reference, whose
+ * chunk kernels get their parallelism from materialised per-chunk states,
+ * scalar_decay/lasd_parallel_triton.py:22-253; here the same associativity is used at segment
+ * granularity so that nothing per-chunk is written to HBM).
+ *
+ * la_lasd_state_pass: for every (sequence, head) the state its own tokens build from a zero start,
+ *     states[s,h] = sum_j w_j y_j^T z_j   (128 x 128 fp32, row = feature of y, column = feature of z)
+ * and gsum[s,h] = the sequence's total log decay.  reverse = 0: w_j = exp(sum of ld after token j)
+ * (state at the sequence's end, forward flow: (y,z) = (k,v) gives S, (v,k) gives S^T);
+ * reverse = 1: w_j = exp(sum of ld up to and including token j) (state at the sequence's start for
+ * the backward recurrences: (q,do) gives dS, (do,q) gives dS^T).  y, z are (B,N,H,128) 16-bit; ld as
+ * in la_lasd_fwd; with cu_seqlens the "sequences" are its M segments (ranges = 0: M + 1 boundaries;
+ * ranges = 1: M explicit (begin, end) token pairs, so that a subset of segments can be given).
+ * Reads 512 B per token and head.  D = E = 128, 16-bit only.
+ *
+ * la_lasd_fold_states: from the segments' own states `local` (nseg,H,D,E) and totals gsum (nseg,H),
+ * the state ENTERING each segment (`incoming`, same shape): forward flow (reverse = 0) walks the
+ * segments in order, a segment flagged first-of-document starts from ext[document] (or zero);
+ * reverse flow walks them backwards, a segment flagged last-of-document starts from
+ * ext[document].  seg_table is int32 (nseg,4): {document, first-of-document, last-of-document, row
+ * of `local` / gsum with the segment's own state, or -1 if none was computed (counts as zero)}.
+ * `ends` (optional, same shape) receives the state after each segment.
+ * ------------------------------------------------------------------------------------------- */
+LA_API int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld_sb,
+                              int64_t ld_sn, int64_t ld_sh, const int64_t *cu_seqlens, float *states,
+                              float *gsum, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
+                              int64_t M, int dtype, int reverse, int ranges, void *stream);
+LA_API int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *seg_table,
+                               const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H,
+                               int64_t D, int64_t E, int reverse, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Sequence-parallel scalar decay (no counterpart in the reference, which has no distributed code;
  * the math is lasd_torch's varlen recurrence, scalar_decay/lasd_torch.py:61-103, cut at a rank
  * boundary).  A rank whose first document started on an earlier rank runs la_lasd_fwd with a zero

@@ -52,11 +52,13 @@ def test_emulated_ranks_match_whole_stream(world, lens, h, d, e, dtype, tol, per
 
 
 @pytest.mark.parametrize("per_head", [True, False])
-@pytest.mark.parametrize("b,n,h", [(1, 8192, 2), (2, 3000, 1)])
-def test_segmented_forward_inside_one_gpu(b, n, h, per_head):
-    """Few long sequences: lasd_fn cuts them into segments that run concurrently and stitches them
-    (xopes_b200/lightning_attn/segmented.py).  Output, final state and the gradients that follow
-    must match the oracle on the whole sequences."""
+@pytest.mark.parametrize("b,n,h", [(1, 8192, 2), (2, 3000, 1), (1, 4000, 3)])
+def test_segmented_passes_inside_one_gpu(b, n, h, per_head):
+    """Few long sequences: lasd_fn cuts them into segments that all run at once, each from its true
+    incoming state (xopes_b200/lightning_attn/segmented.py: state-only pass, fold, varlen chunk
+    pass), forward and backward.  Outputs, final state and every gradient -- including the
+    log-decay gradient and the gradient of the initial state, with a final-state gradient coming
+    in -- must match the oracle on the whole sequences."""
     import xopes_b200 as xb
     from xopes_b200.lightning_attn import segmented as sg
     d = e = 128
@@ -74,13 +76,67 @@ def test_segmented_forward_inside_one_gpu(b, n, h, per_head):
         ld = ld_full = torch.nn.functional.logsigmoid(torch.randn(b, n, h, generator=g) + 4)
     s0 = 0.1 * torch.randn(b, h, d, e, generator=g)
     do = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = 0.1 * torch.randn(b, h, d, e, generator=g)
     qc, kc, vc = (t.to(dtype).cuda().requires_grad_() for t in (q, k, v))
-    o, sf = xb.lasd_fn(qc, kc, vc, ld.cuda(), initial_state=s0.cuda())
+    ldc, s0c = ld.cuda().requires_grad_(), s0.cuda().requires_grad_()
+    o, sf = xb.lasd_fn(qc, kc, vc, ldc, initial_state=s0c)
     ro, rsf = orc.lasd_forward(q, k, v, ld_full, s0)
     assert_close("o", ro, o.float(), TOL_BF16)
     assert_close("final_state", rsf, sf, TOL_BF16)
-    (o.float() * do.cuda()).sum().backward()
-    rq, rk, rv, _, _ = orc.lasd_backward(q, k, v, ld_full, do, s0)
+    ((o.float() * do.cuda()).sum() + (sf * dsf.cuda()).sum()).backward()
+    rq, rk, rv, rld, rs0 = orc.lasd_backward(q, k, v, ld_full, do, s0, dsf)
     assert_close("dq", rq, qc.grad.float(), TOL_BF16)
     assert_close("dk", rk, kc.grad.float(), TOL_BF16)
     assert_close("dv", rv, vc.grad.float(), TOL_BF16)
+    assert_close("dld", rld.sum((0, 1)) if per_head else rld, ldc.grad, TOL_BF16)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
+def test_state_pass_and_fold_match_the_oracle(lib):
+    """la_lasd_state_pass / la_lasd_fold_states through the C ABI: the state a segment's own tokens
+    build (forward and reverse flow) and the states entering every segment of two documents, against
+    the oracle's final states / initial-state gradients of the same token ranges."""
+    from xopes_b200 import _lib
+    n, h, d = 1000, 2, 128
+    g = torch.Generator().manual_seed(8)
+    cast = lambda t: t.bfloat16().float()  # noqa: E731
+    q = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    k = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(1, n, h, d, generator=g))
+    do = cast(torch.randn(1, n, h, d, generator=g))
+    ld = torch.nn.functional.logsigmoid(torch.randn(1, n, h, generator=g) + 3)
+    segs = [(0, 256), (256, 300), (300, 684), (684, 1000)]          # documents: [0,300) and [300,1000)
+    dev = "cuda"
+    qc, kc, vc, doc_, ldc = (t.to(dev) for t in (q.bfloat16(), k.bfloat16(), v.bfloat16(), do.bfloat16(), ld))
+    ranges = torch.tensor(segs, dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for reverse, (y, z) in ((0, (kc, vc)), (1, (qc, doc_))):
+        states = torch.empty(len(segs), h, d, d, device=dev)
+        gsum = torch.empty(len(segs), h, device=dev)
+        rc = lib.la_lasd_state_pass(y.data_ptr(), z.data_ptr(), ldc.data_ptr(), 0, h, 1, ranges.data_ptr(),
+                                    states.data_ptr(), gsum.data_ptr(), 1, n, h, d, d, len(segs), _lib.LA_BF16,
+                                    reverse, 1, stream)
+        assert rc == 0
+        for j, (a, b) in enumerate(segs):
+            sl = slice(a, b)
+            if reverse == 0:
+                _, ref = orc.lasd_forward(q[:, sl], k[:, sl], v[:, sl], ld[:, sl])
+            else:  # gradient of a (zero-valued) initial state = the reverse-flow state at the segment start
+                zero = torch.zeros(1, h, d, d)
+                *_, ref = orc.lasd_backward(q[:, sl], k[:, sl], v[:, sl], ld[:, sl], do[:, sl], zero)
+            assert_close(f"state seg {j} reverse={reverse}", ref[0], states[j], TOL_BF16)
+            assert_close(f"gsum seg {j}", ld[0, sl].sum(0), gsum[j], 1e-5)
+        # fold: documents {0: segs 0-1, 1: segs 2-3}
+        tab = torch.tensor([[0, 1, 0, 0], [0, 0, 1, 1], [1, 1, 0, 2], [1, 0, 1, 3]], dtype=torch.int32, device=dev)
+        ext = 0.1 * torch.randn(2, h, d, d, generator=g).to(dev)
+        inc = torch.empty_like(states)
+        rc = lib.la_lasd_fold_states(states.data_ptr(), gsum.data_ptr(), tab.data_ptr(), ext.data_ptr(),
+                                     inc.data_ptr(), None, len(segs), h, d, d, reverse, stream)
+        assert rc == 0
+        dec = torch.exp(gsum).view(len(segs), h, 1, 1)
+        if reverse == 0:
+            want = [ext[0], states[0] + dec[0] * ext[0], ext[1], states[2] + dec[2] * ext[1]]
+        else:
+            want = [states[1] + dec[1] * ext[0], ext[0], states[3] + dec[3] * ext[1], ext[1]]
+        for j in range(len(segs)):
+            assert_close(f"incoming seg {j} reverse={reverse}", want[j], inc[j], 1e-6)

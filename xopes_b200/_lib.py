@@ -43,6 +43,9 @@ SIGNATURES = {
     "la_lavd_bwd_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64, _i64, _i64]),
     "la_lavd_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
+    "la_lasd_state_pass": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp,
+                                  _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
+    "la_lasd_fold_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_seqpar_fold": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_fold_segments": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_correct_multi": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

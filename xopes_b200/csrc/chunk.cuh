@@ -66,6 +66,25 @@ struct LavdPass {
 bool lavd_chunk_supported(int64_t N, int64_t D, int64_t E, int dtype, bool has_ldk, bool has_ldv);
 int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream);
 
+// State-only pass (state_pass_sm100.cu): per (sequence, head) the state the sequence's own tokens
+// build from a zero start, T = sum_j decay_j y_j^T z_j (row = feature of y, column = feature of z),
+// and the sequence's total log decay.  reverse = 0: decay from token j (exclusive) to the end of the
+// sequence (state at the end, forward flow); reverse = 1: decay from the start to token j
+// (inclusive) (state at the start, reverse flow).  16-bit, 128 features.
+struct StatePass {
+  const void *y = nullptr, *z = nullptr;  // (B,N,H,128) dtype
+  const float *ld = nullptr;
+  int64_t ld_sb = 0, ld_sn = 0, ld_sh = 0;
+  const int64_t *cu = nullptr;
+  float *states = nullptr;                 // (nb,H,128,128) fp32
+  float *gsum = nullptr;                   // (nb,H) fp32, optional
+  int B = 0, N = 0, H = 0, M = 0, reverse = 0;
+  int ranges = 0;  // 1: cu holds M (begin, end) token ranges instead of M + 1 boundaries
+};
+int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream);
+int launch_fold_states(const float *local, const float *gsum, const int *seg, const float *ext, float *out,
+                       float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st);
+
 // o[0,t,h,:] += exp(cum[t,h]) * q[0,t,h,:] S_in[h] for t < T1 (sequence-parallel correction, seqpar.cu)
 int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,
                           int D, int E, int dtype, cudaStream_t st);

@@ -107,6 +107,7 @@ class LasdFunction(torch.autograd.Function):
             o = o.view(b, n, h, e)
             ctx.save_for_backward(q, k, v, ld, s0, cu)
             ctx.flags = flags
+            ctx.seg = (bounds, cap, strides)
             ctx.state_dtype = None if initial_state is None else initial_state.dtype
             ctx.set_materialize_grads(False)
             return o, sf
@@ -119,6 +120,7 @@ class LasdFunction(torch.autograd.Function):
         _lib.check(rc, "la_lasd_fwd")
         ctx.save_for_backward(q, k, v, ld, s0, cu)
         ctx.flags = flags
+        ctx.seg = None
         ctx.state_dtype = None if initial_state is None else initial_state.dtype
         ctx.set_materialize_grads(False)
         return o, sf
@@ -138,6 +140,22 @@ class LasdFunction(torch.autograd.Function):
         ld32, (sb, sn, sh) = _prep_ld(ld, b, n, h)
         want_dld = ctx.needs_input_grad[3]
         want_ds0 = s0 is not None and ctx.needs_input_grad[4]
+        if ctx.seg is not None:
+            # few long sequences: the same cut into segments as the forward, in both directions
+            from .segmented import lasd_backward_segmented
+            bounds, cap, strides = ctx.seg
+            dq, dk, dv, dld, ds0 = lasd_backward_segmented(
+                q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), ld32, strides, s0,
+                do.view(1, b * n, h, e), dsf, bounds, cap, want_dld, want_ds0)
+            dq, dk, dv = dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e)
+            if want_dld:
+                dld = dld.view(b, n, h)
+                if ld.dim() == 1:
+                    dld = dld.sum(dim=(0, 1))
+                dld = dld.to(ld.dtype)
+            if want_ds0:
+                ds0 = ds0.to(ctx.state_dtype)
+            return dq, dk, dv, dld, ds0, None, None
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dld = torch.empty(b, n, h, dtype=torch.float32, device=q.device) if want_dld else None
         ds0 = torch.empty(nb, h, d, e, dtype=torch.float32, device=q.device) if want_ds0 else None

@@ -1,14 +1,25 @@
-"""Segmented scalar-decay forward: sequence parallelism inside one GPU.
+"""Segmented scalar-decay passes: sequence parallelism inside one GPU.
 
 The chunk kernel gives one CTA to every (sequence, head) and walks the sequence chunk by chunk, so
-a call with few, long sequences (B*H well below the 148 SMs) is bound by that serial walk.  Here
-long sequences are cut into segments that run as independent "documents" with a zero incoming
-state, all at once; the segments of a sequence are then stitched exactly as ranks are in the
-sequence-parallel forward: the segments' end states are folded front to back
-(la_seqpar_fold_segments) and every segment that continues a sequence receives the missing term
-o_t += exp(cum_t) q_t^T S_in (la_seqpar_correct_multi).  The price is one more pass over the
-corrected tokens (768 B per token and head instead of 1,024), so segments are made no shorter than
-needed to occupy the GPU.  Forward only; 16-bit inputs with D = E = 128.
+a call with few, long sequences (B*H well below the SM count) is bound by that serial walk, and so
+is a rank of the sequence-parallel forward whose documents are much longer than a balanced share.
+Here long sequences are cut into segments that all run at once, each from its TRUE incoming state:
+
+  1. a state-only pass (la_lasd_state_pass: reads k and v, 512 B per token and head, no output rows)
+     gives every segment that something follows its own end state and total log decay;
+  2. a fold over the few segments of each sequence (la_lasd_fold_states) turns those into the state
+     entering every segment;
+  3. the ordinary varlen chunk pass runs with the segments as its "documents" and those states as
+     their initial states.
+
+The backward pass does the same in both directions: forward states (k, v) for the dq pass and
+reverse states (q, do) for the dk and dv passes; a segment then is to la_lasd_bwd exactly what a
+document with an initial state and a final-state gradient is, log-decay gradient included.
+
+This is the associativity the reference's chunk kernels use at chunk granularity with states
+materialised in HBM (scalar_decay/lasd_parallel_triton.py:22-253); at segment granularity the
+extra traffic is 64 KB per segment and head plus the state-only pass over all but each sequence's
+last segment.  16-bit inputs with D = E = 128.
 """
 from typing import List, Optional, Tuple
 
@@ -50,22 +61,23 @@ def plan_segments(doc_bounds: List[Tuple[int, int]], cap: int):
             first.append(1 if k == 0 else 0)
             t = e
             k += 1
+        if n == 0:  # an empty document is one empty segment
+            seg_cu.append(b)
+            first.append(1)
         last_of_doc.append(len(first) - 1)
     return seg_cu, first, last_of_doc
 
 
 def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
-    """Segmenting pays an extra pass over the continued segments (768 B per token and head, about
-    half of all tokens when every long sequence is cut once) plus a few small launches, so it is
-    used only when the plain launch would leave most SMs idle or one sequence would run at least
-    three times longer than a balanced share.  Measured on 131072-token shards of 8-10 documents
-    and 16 heads: the segment kernel alone 0.39 ms against 0.65-0.70 ms unsegmented, but 0.68-0.76
-    ms with the stitching, i.e. no gain at 1.5-2.3 balanced shares."""
+    """Segmenting pays a state-only pass over all but the last segment of every cut sequence
+    (512 B per token and head on top of 1,024) and two small launches, so it is used when the plain
+    launch would leave most SMs idle or one sequence would run at least twice as long as a
+    balanced share."""
     ctas = len(doc_bounds) * h
     longest = max(b - a for a, b in doc_bounds)
     if ctas <= sms // 4:
         return longest > cap + cap // 2
-    return ctas < sms and longest >= 3 * cap
+    return ctas <= 2 * sms and longest > cap + cap // 4
 
 
 class _Plan:
@@ -74,23 +86,32 @@ class _Plan:
     def __init__(self, doc_bounds, cap, dev):
         seg_cu, first, last_of_doc = plan_segments(doc_bounds, cap)
         nseg = len(first)
-        lens = [seg_cu[i + 1] - seg_cu[i] for i in range(nseg)]
-        cont = [i for i in range(nseg) if not first[i]]
-        tiles, tile0 = 0, []
-        for i in cont:
-            tile0.append(tiles)
-            tiles += -(-lens[i] // 128)
-        table_all = [[seg_cu[i], lens[i], 0, first[i]] for i in range(nseg)]
-        table_cont = [[seg_cu[i], lens[i], tile0[j], 0] for j, i in enumerate(cont)]
-        self.nseg, self.ncont, self.tiles = nseg, len(cont), tiles
-        self.cu_dev = torch.tensor(seg_cu, dtype=torch.int64).to(dev)
-        tab = torch.tensor(table_all + table_cont, dtype=torch.int32).to(dev)
-        self.tab_all, self.tab_cont = tab[:nseg], tab[nseg:]
-        self.first_idx = torch.tensor([i for i in range(nseg) if first[i]], dtype=torch.int64).to(dev)
-        self.cont_idx = torch.tensor(cont, dtype=torch.int64).to(dev)
-        self.last_idx = torch.tensor(last_of_doc, dtype=torch.int64).to(dev)
-        self.lens_f = torch.tensor(lens, dtype=torch.float32).to(dev).view(nseg, 1)
-        self.steps = None  # 1..T as fp32, made on first use by a constant-decay call
+        last = [0] * nseg
+        for i in last_of_doc:
+            last[i] = 1
+        doc_of, d = [], -1
+        for i in range(nseg):
+            if first[i]:
+                d += 1
+            doc_of.append(d)
+        # forward flow: every segment that another one follows needs its own end state;
+        # reverse flow: every segment that another one precedes needs its own start state
+        fwd_rows = [i for i in range(nseg) if not last[i]]
+        rev_rows = [i for i in range(nseg) if not first[i]]
+        fwd_idx = {s: j for j, s in enumerate(fwd_rows)}
+        rev_idx = {s: j for j, s in enumerate(rev_rows)}
+        self.nseg, self.ndocs = nseg, len(doc_bounds)
+        self.n_fwd, self.n_rev = len(fwd_rows), len(rev_rows)
+        self.cut = nseg > len(doc_bounds)
+        i64 = lambda x: torch.tensor(x, dtype=torch.int64).to(dev)  # noqa: E731
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32).to(dev)  # noqa: E731
+        self.cu_dev = i64(seg_cu)
+        self.fwd_ranges = i64([[seg_cu[s], seg_cu[s + 1]] for s in fwd_rows] or [[0, 0]])
+        self.rev_ranges = i64([[seg_cu[s], seg_cu[s + 1]] for s in rev_rows] or [[0, 0]])
+        self.tab_fwd = i32([[doc_of[s], first[s], last[s], fwd_idx.get(s, -1)] for s in range(nseg)])
+        self.tab_rev = i32([[doc_of[s], first[s], last[s], rev_idx.get(s, -1)] for s in range(nseg)])
+        self.first_idx = i64([i for i in range(nseg) if first[i]])
+        self.last_idx = i64(last_of_doc)
 
 
 _PLANS = {}
@@ -106,6 +127,33 @@ def _plan(doc_bounds, cap, dev) -> _Plan:
     return p
 
 
+def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool):
+    """State entering every segment (forward flow: at its first token from ext = the documents'
+    initial states; reverse flow: after its last token from ext = their final-state gradients),
+    (nseg, H, 128, 128) fp32."""
+    _, t, h, d = y.shape
+    e = z.shape[-1]
+    dev = y.device
+    n_loc = pl.n_rev if reverse else pl.n_fwd
+    ranges = pl.rev_ranges if reverse else pl.fwd_ranges
+    tab = pl.tab_rev if reverse else pl.tab_fwd
+    _, sn, sh = ld_strides
+    stream = _lib.stream_of(y)
+    incoming = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    local = torch.empty(max(n_loc, 1), h, d, e, dtype=torch.float32, device=dev)
+    gsum = torch.empty(max(n_loc, 1), h, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        if n_loc:
+            rc = lib.la_lasd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(ranges),
+                                        _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
+                                        _lib.dtype_code(y), 1 if reverse else 0, 1, stream)
+            _lib.check(rc, "la_lasd_state_pass")
+        rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(tab), _lib.ptr(ext),
+                                     _lib.ptr(incoming), None, pl.nseg, h, d, e, 1 if reverse else 0, stream)
+        _lib.check(rc, "la_lasd_fold_states")
+    return incoming
+
+
 def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds, cap):
     """q, k, v: (1, T, H, 128) contiguous 16-bit CUDA tensors (a batch flattened to one stream);
     ld32 fp32 with element strides over (stream token, head) = ld_strides[1:]; doc_bounds the
@@ -116,46 +164,43 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev)
-    nseg = pl.nseg
-
-    s0 = None
-    if initial_state is not None:
-        s0 = torch.zeros(nseg, h, d, e, dtype=torch.float32, device=dev)
-        s0.index_copy_(0, pl.first_idx, initial_state)
+    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
-    st = torch.empty(nseg, h, d, e, dtype=torch.float32, device=dev)
+    st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
     _, sn, sh = ld_strides
-    stream = _lib.stream_of(q)
     with torch.cuda.device(dev):
-        rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s0),
-                             _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, nseg,
-                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, stream)
+        rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
+                             _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
+                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd (segmented)")
-        # inclusive cumulative log decay of the stream, (T, H), and each segment's total
-        if sn == 0:  # constant per head
-            if pl.steps is None or pl.steps.numel() != t:
-                pl.steps = torch.arange(1, t + 1, dtype=torch.float32, device=dev).view(t, 1)
-            ldh = torch.as_strided(ld32, (1, h), (0, sh))
-            cum = pl.steps * ldh
-            seg_decay = pl.lens_f * ldh
-        else:
-            ldt = torch.as_strided(ld32, (h, t), (sh, sn))
-            cum = torch.cumsum(ldt.contiguous(), dim=1).t().contiguous()
-            total = cum.index_select(0, pl.cu_dev[1:] - 1)
-            # a segment's decay = cum at its end minus cum just before its start
-            starts = pl.cu_dev[:-1]
-            before = torch.where((starts > 0).view(-1, 1), cum.index_select(0, (starts - 1).clamp(min=0)),
-                                 torch.zeros(1, h, device=dev))
-            seg_decay = total - before
-        s_in = torch.empty(nseg, h, d, e, dtype=torch.float32, device=dev)
-        rc = lib.la_seqpar_fold_segments(_lib.ptr(st), _lib.ptr(seg_decay.contiguous()), _lib.ptr(pl.tab_all),
-                                         _lib.ptr(s_in), nseg, h, d, e, stream)
-        _lib.check(rc, "la_seqpar_fold_segments")
-        if pl.ncont:
-            s_in_cont = s_in.index_select(0, pl.cont_idx)
-            rc = lib.la_seqpar_correct_multi(_lib.ptr(q), _lib.ptr(o), _lib.ptr(cum), _lib.ptr(s_in_cont),
-                                             _lib.ptr(pl.tab_cont), pl.ncont, pl.tiles, t, h, d, e,
-                                             _lib.dtype_code(q), stream)
-            _lib.check(rc, "la_seqpar_correct_multi")
-    final = st.index_select(0, pl.last_idx)
-    return o, final
+    return o, st.index_select(0, pl.last_idx)
+
+
+def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal_state, doc_bounds, cap,
+                            want_dld: bool, want_ds0: bool):
+    """Backward twin: q, k, v, do (1, T, H, 128); initial_state / dfinal_state (ndocs, H, 128, 128)
+    fp32 or None.  Returns (dq, dk, dv, dld (1,T,H) fp32 or None, dinitial_state (ndocs,...) or None)."""
+    lib = _lib.load()
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    pl = _plan(doc_bounds, cap, dev)
+    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
+    ds_out = _incoming_states(lib, q, do, ld32, ld_strides, pl, dfinal_state, reverse=True)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dld = torch.empty(1, t, h, dtype=torch.float32, device=dev) if want_dld else None
+    ds0 = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev) if want_ds0 else None
+    ws, ws_bytes = None, 0
+    if want_dld:
+        ws_bytes = lib.la_lasd_bwd_workspace_bytes(1, t, h, d, e, pl.nseg, 1)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    _, sn, sh = ld_strides
+    with torch.cuda.device(dev):
+        rc = lib.la_lasd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
+                             _lib.ptr(do), _lib.ptr(ds_out), _lib.ptr(pl.cu_dev), _lib.ptr(dq), _lib.ptr(dk),
+                             _lib.ptr(dv), _lib.ptr(dld), _lib.ptr(ds0), _lib.ptr(ws), ws_bytes, 1, t, h, d, e,
+                             pl.nseg, _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, _lib.stream_of(q))
+        _lib.check(rc, "la_lasd_bwd (segmented)")
+    if want_ds0:
+        ds0 = ds0.index_select(0, pl.first_idx)
+    return dq, dk, dv, dld, ds0
