@@ -71,6 +71,10 @@ LA_API int la_device_status_clear(void *stream);
  * it.  No counterpart in the reference. */
 LA_API int la_debug_lavd_unsafe(void *stream, int *flag_out);
 
+/* Text of the last CUDA error this library met on the calling thread (after an LA_ERR_CUDA return);
+ * empty if none.  No counterpart in the reference. */
+LA_API const char *la_debug_last_cuda_error(void);
+
 /* Self-test of the watchdog (no counterpart in the reference): launches one CTA that waits, with
  * a limit of limit_us microseconds (1 .. 1,000,000), on an mbarrier nothing ever arrives on.  The
  * wait gives up, the kernel returns by itself and la_device_status() then reads 199. */

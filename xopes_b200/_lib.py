@@ -28,6 +28,7 @@ SIGNATURES = {
     "la_device_status_clear": (_i32, [_vp]),
     "la_debug_lavd_unsafe": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "la_debug_wait_probe": (_i32, [_i64, _vp]),
+    "la_debug_last_cuda_error": (ctypes.c_char_p, []),
     "la_debug_umma_probe": (_i32, [_i32, _vp, _vp, _vp, _i32, _vp]),
     "la_lasd_fwd": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp,
                            _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
@@ -100,5 +101,8 @@ def require_cuda(*tensors):
 
 def check(rc: int, what: str):
     if rc != 0:
-        msg = load().la_status_string(rc).decode()
+        lib = load()
+        msg = lib.la_status_string(rc).decode()
+        if rc == -4:
+            msg += " [" + lib.la_debug_last_cuda_error().decode() + "]"
         raise RuntimeError(f"{what} failed: {msg} (status {rc})")

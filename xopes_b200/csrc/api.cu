@@ -8,6 +8,11 @@ namespace la {
 
 __device__ int g_status_word = 0;
 
+char *last_cuda_error_buf() {
+  static thread_local char buf[256] = "";
+  return buf;
+}
+
 int *status_word_ptr() {
   static int *ptrs[64] = {nullptr};
   int dev = 0;
@@ -95,6 +100,9 @@ bool dtype_ok(int dtype) { return dtype == LA_F32 || dtype == LA_BF16 || dtype =
 
 int check_common(const void *q, const void *k, const void *v, int64_t B, int64_t N, int64_t H,
                  int64_t D, int64_t E, int64_t M, const int64_t *cu, int dtype) {
+  // An error another library left behind on this thread (the runtime keeps the last one until it is
+  // read) must not be taken for a failure of the launches that follow.
+  cudaGetLastError();
   if (q == nullptr || k == nullptr || v == nullptr) return LA_ERR_NULL_POINTER;
   if (B <= 0 || N <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
   if (cu != nullptr && (B != 1 || M <= 0)) return LA_ERR_BAD_SHAPE;
@@ -196,6 +204,8 @@ int la_debug_lavd_unsafe(void *stream, int *flag_out) {
   *flag_out = w[1] != 0 ? 2 : (w[0] != 0 ? 1 : 0);
   return LA_OK;
 }
+
+const char *la_debug_last_cuda_error(void) { return last_cuda_error_buf(); }
 
 int la_debug_wait_probe(int64_t limit_us, void *stream) {
   if (limit_us <= 0 || limit_us > 1000000) return LA_ERR_BAD_SHAPE;

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #include "../../include/xopes_b200.h"
 
@@ -25,9 +26,16 @@ template <> struct Cvt<__half> {
 
 static inline size_t dtype_size(int dtype) { return dtype == LA_F32 ? 4 : 2; }
 
+// Text of the last CUDA error this library met on the calling thread (la_debug_last_cuda_error).
+char *last_cuda_error_buf();
+static inline void note_cuda_error(cudaError_t e, const char *where) {
+  snprintf(last_cuda_error_buf(), 256, "%s: %s", where, cudaGetErrorString(e));
+}
+
 // Launch-error check that never synchronises: reports configuration errors only.
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) note_cuda_error(e, "kernel launch");
   return e == cudaSuccess ? LA_OK : LA_ERR_CUDA;
 }
 

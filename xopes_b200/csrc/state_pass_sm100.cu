@@ -272,8 +272,11 @@ int launch_t(const StatePass &p, int dtype, cudaStream_t stream) {
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   auto kern = state_pass_kernel<T>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+  const cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (ea != cudaSuccess) {
+    note_cuda_error(ea, "cudaFuncSetAttribute(state_pass_kernel)");
     return LA_ERR_CUDA;
+  }
   const long long nb = p.cu ? p.M : p.B;
   kern<<<(unsigned)(nb * p.H), kThreads, kSmemBytes, stream>>>(my, mz, a);
   return launch_status();

@@ -79,6 +79,14 @@ inline EncodeTiledFn encode_fn() {
 inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return LA_ERR_CUDA;
+  // The encoder is a driver call and needs this thread to have the device's context current; a
+  // thread that has made no runtime call yet (an autograd worker, say) has none until the runtime
+  // binds it, which this no-op does.  Once per thread.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
   const cuuint64_t esz = dtype == LA_F32 ? 4 : 2;
   const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
@@ -91,6 +99,7 @@ inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, in
   const CUresult r = enc(m, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) snprintf(last_cuda_error_buf(), 256, "cuTensorMapEncodeTiled: CUresult %d (ptr %p, B %d N %d H %d)", (int)r, ptr, B, N, H);
   return r == CUDA_SUCCESS ? LA_OK : LA_ERR_CUDA;
 }
 
