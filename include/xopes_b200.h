@@ -209,14 +209,16 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
  * reverse flow walks them backwards, a segment flagged last-of-document starts from
  * ext[document].  seg_table is int32 (nseg,4): {document, first-of-document, last-of-document, row
  * of `local` / gsum with the segment's own state, or -1 if none was computed (counts as zero)}.
- * `ends` (optional, same shape) receives the state after each segment.
+ * emit (optional, int32 (nseg)) names the row of `incoming` each segment's entering state goes to,
+ * -1 for none: the state-only pass may run on finer pieces than the segments that need an entering
+ * state.  `ends` (optional, (nseg,H,D,E)) receives the state after each segment.
  * ------------------------------------------------------------------------------------------- */
 LA_API int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld_sb,
                               int64_t ld_sn, int64_t ld_sh, const int64_t *cu_seqlens, float *states,
                               float *gsum, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
                               int64_t M, int dtype, int reverse, int ranges, void *stream);
 LA_API int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *seg_table,
-                               const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H,
+                               const int32_t *emit, const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H,
                                int64_t D, int64_t E, int reverse, void *stream);
 
 /* ---------------------------------------------------------------------------------------------

@@ -1,4 +1,4 @@
-"""GPU, 2 devices: the sequence-parallel forward over real NCCL ranks (skipped on a 1-GPU box).
+"""GPU, 2 devices: the sequence-parallel forward and backward over real NCCL ranks (skipped on a 1-GPU box).
 Each rank is a child process on its own GPU; NVLS is switched off and no kernel of this library
 touches a peer's memory, so a rank ends only between steps with nothing in flight."""
 import os
@@ -31,6 +31,7 @@ def _worker(rank, world, port, exchange, ret):
         q = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
         k = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
         v = cast(torch.randn(1, n, h, d, generator=g))
+        do = cast(torch.randn(1, n, h, d, generator=g))
         ld = torch.log(1 - 2.0 ** (-5 - torch.arange(h, dtype=torch.float32) / 2))
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
         a, b = token_range(n, rank, world)
@@ -38,8 +39,17 @@ def _worker(rank, world, port, exchange, ret):
         o, states, plan = xb.lasd_seqpar_forward(q[:, a:b].bfloat16().to(dev), k[:, a:b].bfloat16().to(dev),
                                                  v[:, a:b].bfloat16().to(dev), ld.to(dev), cu, exchange=exchange)
         torch.cuda.synchronize()
-        ro, _ = orc.lasd_forward(q, k, v, ld.view(1, 1, h).expand(1, n, h), None, cu)
-        ret[rank] = orc.rel_l2(ro[:, a:b], o.float().cpu())
+        ld_full = ld.view(1, 1, h).expand(1, n, h)
+        ro, _ = orc.lasd_forward(q, k, v, ld_full, None, cu)
+        errs = [orc.rel_l2(ro[:, a:b], o.float().cpu())]
+        if exchange == "all_gather":  # the backward over the same ranks
+            dq, dk, dv = xb.lasd_seqpar_backward(q[:, a:b].bfloat16().to(dev), k[:, a:b].bfloat16().to(dev),
+                                                 v[:, a:b].bfloat16().to(dev), ld.to(dev),
+                                                 do[:, a:b].bfloat16().to(dev), cu, plan.s_in)
+            torch.cuda.synchronize()
+            rq, rk, rv, _, _ = orc.lasd_backward(q, k, v, ld_full, do, None, None, cu)
+            errs += [orc.rel_l2(r[:, a:b], x.float().cpu()) for r, x in ((rq, dq), (rk, dk), (rv, dv))]
+        ret[rank] = max(errs)
     finally:
         dist.destroy_process_group()
 

@@ -51,6 +51,52 @@ def test_emulated_ranks_match_whole_stream(world, lens, h, d, e, dtype, tol, per
                 assert_close(f"state doc {doc}", rs[doc], states[j], tol)
 
 
+@pytest.mark.parametrize("world,lens,per_head", [(4, [100, 700, 400, 336], True), (3, [900, 1400, 772], False),
+                                                  (2, [2048, 2048], True)])
+def test_emulated_ranks_backward_matches_whole_stream(world, lens, per_head):
+    """Sequence-parallel backward with the CUDA local backward and the CUDA correction kernel, ranks
+    emulated one after another on one device: dq, dk, dv of every rank against the oracle's gradients
+    of the whole stream."""
+    from xopes_b200.lightning_attn import seq_parallel as sp
+    n, h, d, e, dtype = sum(lens), 2, 128, 128, torch.bfloat16
+    g = torch.Generator().manual_seed(12)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    q = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    k = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(1, n, h, e, generator=g))
+    do = cast(torch.randn(1, n, h, e, generator=g))
+    if per_head:
+        ld = torch.log(1 - 2.0 ** (-5 - torch.arange(h, dtype=torch.float32) / 2))
+        ld_full = ld.view(1, 1, h).expand(1, n, h)
+    else:
+        ld_full = torch.nn.functional.logsigmoid(torch.randn(1, n, h, generator=g) + 3)
+    cu = [0] + [int(x) for x in torch.tensor(lens).cumsum(0)]
+    dev = "cuda"
+    fwd = []
+    for r in range(world):
+        a, b = sp.token_range(n, r, world)
+        plan = sp.shard_documents(cu, a, b)
+        loc = [t[:, a:b].to(dtype).to(dev).contiguous() for t in (q, k, v, do)]
+        ldl = ld.to(dev) if per_head else ld_full[:, a:b].to(dev).contiguous()
+        o, states, summary = sp.local_phase(loc[0], loc[1], loc[2], ldl, plan)
+        fwd.append((plan, loc, ldl, summary, a, b))
+    gathered = torch.stack([x[3] for x in fwd])
+    bwd = []
+    for r, (plan, loc, ldl, _, a, b) in enumerate(fwd):
+        s_in = sp.fold_incoming_state(gathered, r, h, d, e) if plan.open_start else None
+        dq, dk, dv, ds0, summ = sp.local_backward_phase(loc[0], loc[1], loc[2], ldl, loc[3], plan, s_in)
+        bwd.append((dq, dk, dv, summ))
+    gathered_b = torch.stack([x[3] for x in bwd])
+    rq, rk, rv, _, _ = orc.lasd_backward(q, k, v, ld_full, do, None, None, torch.tensor(cu))
+    for r, (plan, loc, ldl, _, a, b) in enumerate(fwd):
+        dq, dk, dv, _ = bwd[r]
+        ds_out = sp.fold_outgoing_gradient(gathered_b, r, h, d, e)
+        sp.correct_backward_phase(loc[1], loc[2], dk, dv, ldl, ds_out, plan)
+        assert_close(f"dq rank {r}", rq[:, a:b], dq.float(), TOL_BF16)
+        assert_close(f"dk rank {r}", rk[:, a:b], dk.float(), TOL_BF16)
+        assert_close(f"dv rank {r}", rv[:, a:b], dv.float(), TOL_BF16)
+
+
 @pytest.mark.parametrize("per_head", [True, False])
 @pytest.mark.parametrize("b,n,h", [(1, 8192, 2), (2, 3000, 1), (1, 4000, 3)])
 def test_segmented_passes_inside_one_gpu(b, n, h, per_head):
@@ -130,7 +176,7 @@ def test_state_pass_and_fold_match_the_oracle(lib):
         tab = torch.tensor([[0, 1, 0, 0], [0, 0, 1, 1], [1, 1, 0, 2], [1, 0, 1, 3]], dtype=torch.int32, device=dev)
         ext = 0.1 * torch.randn(2, h, d, d, generator=g).to(dev)
         inc = torch.empty_like(states)
-        rc = lib.la_lasd_fold_states(states.data_ptr(), gsum.data_ptr(), tab.data_ptr(), ext.data_ptr(),
+        rc = lib.la_lasd_fold_states(states.data_ptr(), gsum.data_ptr(), tab.data_ptr(), None, ext.data_ptr(),
                                      inc.data_ptr(), None, len(segs), h, d, d, reverse, stream)
         assert rc == 0
         dec = torch.exp(gsum).view(len(segs), h, 1, 1)

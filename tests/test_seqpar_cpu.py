@@ -103,6 +103,140 @@ def test_protocol_over_gloo_ranks(world, lens, per_head, exchange):
             assert err_o < 1e-5 and err_s < 1e-5, f"rank {r}: o {err_o:.2e} state {err_s:.2e}"
 
 
+def _oracle_backward(q, k, v, ld, do, local_cu, s0):
+    from oracle import lightning_attn_oracle as orc
+    cu = torch.tensor(local_cu, dtype=torch.int64)
+    t, h = q.shape[1], q.shape[2]
+    ld_full = ld.view(1, 1, h).expand(1, t, h) if ld.dim() == 1 else ld
+    dq, dk, dv, _, ds0 = orc.lasd_backward(q, k, v, ld_full, do, s0, None, cu)
+    if s0 is None:  # the oracle returns no state gradient without an initial state
+        zero = torch.zeros(len(local_cu) - 1, h, q.shape[3], v.shape[3])
+        dq, dk, dv, _, ds0 = orc.lasd_backward(q, k, v, ld_full, do, zero, None, cu)
+    return dq, dk, dv, ds0
+
+
+def _torch_correct_bwd(x, out, cum, s_in, t1):
+    out[0, :t1] += torch.exp(cum).unsqueeze(-1) * torch.einsum("thd,hde->the", x[0, :t1].float(), s_in)
+
+
+def _worker_bwd(rank, world, port, lens, per_head, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import lightning_attn_oracle as orc
+        from xopes_b200.lightning_attn.seq_parallel import (lasd_seqpar_backward, lasd_seqpar_forward,
+                                                            token_range)
+        n, h, d, e = sum(lens), 2, 8, 8
+        g = torch.Generator().manual_seed(6)
+        q = torch.randn(1, n, h, d, generator=g) * d ** -0.5
+        k = torch.randn(1, n, h, d, generator=g) * d ** -0.5
+        v = torch.randn(1, n, h, e, generator=g)
+        do = torch.randn(1, n, h, e, generator=g)
+        if per_head:
+            ld = torch.log(1 - 2.0 ** (-3 - torch.arange(h, dtype=torch.float32)))
+            ld_full = ld.view(1, 1, h).expand(1, n, h)
+        else:
+            ld_full = torch.nn.functional.logsigmoid(torch.randn(1, n, h, generator=g) + 2)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+        a, b = token_range(n, rank, world)
+        ld_arg = ld if per_head else ld_full[:, a:b]
+        _, _, plan = lasd_seqpar_forward(q[:, a:b], k[:, a:b], v[:, a:b], ld_arg, cu,
+                                         local_forward=_oracle_forward, correct=_torch_correct)
+        dq, dk, dv = lasd_seqpar_backward(q[:, a:b], k[:, a:b], v[:, a:b], ld_arg, do[:, a:b], cu, plan.s_in,
+                                          local_backward=_oracle_backward, correct=_torch_correct_bwd)
+        rq, rk, rv, _, _ = orc.lasd_backward(q, k, v, ld_full, do, None, None, cu)
+        ret[rank] = tuple(float((x - r[:, a:b]).abs().max()) for x, r in ((dq, rq), (dk, rk), (dv, rv)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,lens,per_head", [
+    (2, [5, 20, 15], False),      # one document crosses the cut
+    (3, [10, 60, 26], True),      # a document covers a whole rank (both ends open)
+    (3, [32, 32, 32], False),     # boundaries coincide with the cuts: nothing to exchange
+])
+def test_backward_protocol_over_gloo_ranks(world, lens, per_head):
+    port = 31500 + (os.getpid() + world * 11) % 2000
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker_bwd, args=(world, port, lens, per_head, ret), nprocs=world, join=True)
+        assert len(ret) == world
+        for r in range(world):
+            assert max(ret[r]) < 1e-5, f"rank {r}: dq, dk, dv max abs errors {ret[r]}"
+
+
+def _worker_missing(rank, world, port, ret):
+    """Rank 1 never joins the exchange (it leaves between steps, nothing in flight); rank 0 must get
+    an error within the group's timeout instead of blocking."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from xopes_b200.lightning_attn.seq_parallel import SeqParExchangeError, lasd_seqpar_forward, token_range
+    n, h, d = 40, 2, 8
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, n, h, d, generator=g)
+    ld = torch.log(1 - 2.0 ** (-3 - torch.arange(h, dtype=torch.float32)))
+    cu = torch.tensor([0, 30, 40], dtype=torch.int64)
+    a, b = token_range(n, rank, world)
+    if rank == 1:
+        time.sleep(1.0)   # leaves without publishing its summary
+        ret[rank] = "left"
+        return
+    t0 = time.perf_counter()
+    try:
+        lasd_seqpar_forward(q[:, a:b], q[:, a:b], q[:, a:b], ld, cu, local_forward=_oracle_forward,
+                            correct=_torch_correct)
+        ret[rank] = "no error"
+    except SeqParExchangeError:
+        ret[rank] = ("error", time.perf_counter() - t0)
+
+
+def test_missing_rank_turns_into_an_error_not_a_hang():
+    port = 33500 + os.getpid() % 2000
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker_missing, args=(2, port, ret), nprocs=2, join=True)
+        assert ret[1] == "left"
+        assert ret[0][0] == "error" and ret[0][1] < 30.0, ret[0]
+
+
+def _worker_late(rank, world, port, ret):
+    """A rank that publishes late (but inside the timeout) changes nothing in the result."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        from oracle import lightning_attn_oracle as orc
+        from xopes_b200.lightning_attn.seq_parallel import lasd_seqpar_forward, token_range
+        n, h, d = 40, 2, 8
+        g = torch.Generator().manual_seed(1)
+        q = torch.randn(1, n, h, d, generator=g) * 0.3
+        ld = torch.log(1 - 2.0 ** (-3 - torch.arange(h, dtype=torch.float32)))
+        cu = torch.tensor([0, 30, 40], dtype=torch.int64)
+        a, b = token_range(n, rank, world)
+        if rank == 0:
+            time.sleep(1.5)
+        o, _, _ = lasd_seqpar_forward(q[:, a:b], q[:, a:b], q[:, a:b], ld, cu, local_forward=_oracle_forward,
+                                      correct=_torch_correct)
+        ro, _ = orc.lasd_forward(q, q, q, ld.view(1, 1, h).expand(1, n, h), None, cu)
+        ret[rank] = float((o - ro[:, a:b]).abs().max())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_late_rank_still_gives_the_right_result():
+    port = 35500 + os.getpid() % 2000
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_worker_late, args=(2, port, ret), nprocs=2, join=True)
+        assert len(ret) == 2 and max(ret.values()) < 1e-5, dict(ret)
+
+
 def test_segment_planning():
     from xopes_b200.lightning_attn import segmented as sg
     assert sg.auto_cap(131072, 16, 148) % 128 == 0 and sg.auto_cap(100, 16, 148) == 1024

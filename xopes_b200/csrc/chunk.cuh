@@ -82,8 +82,8 @@ struct StatePass {
   int ranges = 0;  // 1: cu holds M (begin, end) token ranges instead of M + 1 boundaries
 };
 int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream);
-int launch_fold_states(const float *local, const float *gsum, const int *seg, const float *ext, float *out,
-                       float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st);
+int launch_fold_states(const float *local, const float *gsum, const int *seg, const int *emit, const float *ext,
+                       float *out, float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st);
 
 // o[0,t,h,:] += exp(cum[t,h]) * q[0,t,h,:] S_in[h] for t < T1 (sequence-parallel correction, seqpar.cu)
 int launch_seqpar_correct(const void *q, void *o, const float *cum, const float *s_in, int T1, int N, int H,

@@ -644,7 +644,9 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             const float4 *row = reinterpret_cast<const float4 *>(src + i * kChunk + bt * 32);
 #pragma unroll
             for (int kk = 0; kk < 8; ++kk) {
-              const float4 v = __ldcg(row + kk);
+              // the eight loads of a thread fall into one 128-byte line: through L1 (the caller's
+              // state is read-only for the launch; hand-off slots never take this branch)
+              const float4 v = __ldg(row + kk);
               r[4 * kk + 0] = __float_as_uint(v.x); r[4 * kk + 1] = __float_as_uint(v.y);
               r[4 * kk + 2] = __float_as_uint(v.z); r[4 * kk + 3] = __float_as_uint(v.w);
             }
@@ -652,6 +654,15 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           tmem_st32(tl + kColT + bt * 32, r);
         }
         tmem_wait_st();
+        // the next task's starting state: pull it into L2 now, it is needed when this task ends
+        if (ap.t0 != nullptr && k + 1 < ntasks) {
+          const Task nx = task_of(a, range(), k + 1, ntasks);
+          if (!nx.waits) {
+            const char *pn = reinterpret_cast<const char *>(ap.t0 + ((long long)nx.seq * a.H + nx.h) * (long long)(kChunk * kChunk));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)tid * 128));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)(tid + kComputeThreads) * 128));
+          }
+        }
       }
       const int nc = t_cnt;
 

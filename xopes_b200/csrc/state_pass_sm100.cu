@@ -290,7 +290,8 @@ int launch_t(const StatePass &p, int dtype, cudaStream_t stream) {
 // own state or -1 if it was not computed (then it counts as zero: fine for a segment nothing
 // follows)}.  ends[k] (optional) receives the state after folding segment k.
 __global__ void fold_states_kernel(const float *__restrict__ local, const float *__restrict__ gsum,
-                                   const int *__restrict__ seg, const float *__restrict__ ext, float *__restrict__ out,
+                                   const int *__restrict__ seg, const int *__restrict__ emit,
+                                   const float *__restrict__ ext, float *__restrict__ out,
                                    float *__restrict__ ends, int nseg, int H, int DE, int reverse) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long hde = (long long)H * DE;
@@ -301,7 +302,8 @@ __global__ void fold_states_kernel(const float *__restrict__ local, const float 
     const int k = reverse ? nseg - 1 - kk : kk;
     const bool fresh = seg[4 * k + (reverse ? 2 : 1)] != 0;
     if (fresh) s = ext != nullptr ? ext[(long long)seg[4 * k] * hde + idx] : 0.f;
-    out[k * hde + idx] = s;
+    const int slot = emit != nullptr ? emit[k] : k;  // -1: nobody needs the state entering this piece
+    if (slot >= 0) out[slot * hde + idx] = s;
     const int li = seg[4 * k + 3];
     s = li >= 0 ? local[li * hde + idx] + expf(gsum[(long long)li * H + h]) * s : 0.f;
     if (ends != nullptr) ends[k * hde + idx] = s;
@@ -320,11 +322,11 @@ int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream) {
   return LA_ERR_UNSUPPORTED;
 }
 
-int launch_fold_states(const float *local, const float *gsum, const int *seg, const float *ext, float *out,
-                       float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st) {
+int launch_fold_states(const float *local, const float *gsum, const int *seg, const int *emit, const float *ext,
+                       float *out, float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st) {
   const long long hde = (long long)H * DE;
   const int threads = 256;
-  fold_states_kernel<<<(unsigned)((hde + threads - 1) / threads), threads, 0, st>>>(local, gsum, seg, ext, out, ends,
+  fold_states_kernel<<<(unsigned)((hde + threads - 1) / threads), threads, 0, st>>>(local, gsum, seg, emit, ext, out, ends,
                                                                                    nseg, H, DE, reverse);
   return launch_status();
 }

@@ -9,7 +9,7 @@ from typing import Optional, Tuple
 import torch
 
 from .constant_decay import lacd_fn
-from .seq_parallel import lasd_seqpar_forward
+from .seq_parallel import SeqParExchangeError, lasd_seqpar_backward, lasd_seqpar_forward
 from .scalar_decay import (lasd_decode_step, lasd_fn, lasd_parallel_cuda, lasd_parallel_triton,
                            lasd_recurrence_cuda, lasd_recurrence_triton)
 from .vector_decay import (lavd_decode_step, lavd_fn, lavd_parallel_cuda, lavd_parallel_triton,
@@ -42,5 +42,6 @@ __all__ = [
     "lightning_attn_func", "lacd_fn", "lasd_fn", "lavd_fn", "lasd_parallel_cuda",
     "lasd_recurrence_cuda", "lavd_parallel_cuda", "lavd_recurrence_cuda", "lasd_parallel_triton",
     "lasd_recurrence_triton", "lavd_parallel_triton", "lavd_recurrence_triton",
-    "lasd_decode_step", "lavd_decode_step", "lasd_seqpar_forward",
+    "lasd_decode_step", "lavd_decode_step", "lasd_seqpar_forward", "lasd_seqpar_backward",
+    "SeqParExchangeError",
 ]

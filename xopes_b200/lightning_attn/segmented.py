@@ -83,7 +83,7 @@ def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
 class _Plan:
     """Host lists and device tables of one segmentation; built once per (documents, cap, device)."""
 
-    def __init__(self, doc_bounds, cap, dev):
+    def __init__(self, doc_bounds, cap, dev, piece_target):
         seg_cu, first, last_of_doc = plan_segments(doc_bounds, cap)
         nseg = len(first)
         last = [0] * nseg
@@ -95,35 +95,51 @@ class _Plan:
                 d += 1
             doc_of.append(d)
         # forward flow: every segment that another one follows needs its own end state;
-        # reverse flow: every segment that another one precedes needs its own start state
-        fwd_rows = [i for i in range(nseg) if not last[i]]
-        rev_rows = [i for i in range(nseg) if not first[i]]
-        fwd_idx = {s: j for j, s in enumerate(fwd_rows)}
-        rev_idx = {s: j for j, s in enumerate(rev_rows)}
+        # reverse flow: every segment that another one precedes needs its own start state.  The
+        # state-only pass runs on finer pieces than the segments (there are few segments that need
+        # it, and a piece per CTA walks its tokens serially), and the fold runs over the pieces.
         self.nseg, self.ndocs = nseg, len(doc_bounds)
-        self.n_fwd, self.n_rev = len(fwd_rows), len(rev_rows)
-        self.cut = nseg > len(doc_bounds)
         i64 = lambda x: torch.tensor(x, dtype=torch.int64).to(dev)  # noqa: E731
         i32 = lambda x: torch.tensor(x, dtype=torch.int32).to(dev)  # noqa: E731
         self.cu_dev = i64(seg_cu)
-        self.fwd_ranges = i64([[seg_cu[s], seg_cu[s + 1]] for s in fwd_rows] or [[0, 0]])
-        self.rev_ranges = i64([[seg_cu[s], seg_cu[s + 1]] for s in rev_rows] or [[0, 0]])
-        self.tab_fwd = i32([[doc_of[s], first[s], last[s], fwd_idx.get(s, -1)] for s in range(nseg)])
-        self.tab_rev = i32([[doc_of[s], first[s], last[s], rev_idx.get(s, -1)] for s in range(nseg)])
         self.first_idx = i64([i for i in range(nseg) if first[i]])
         self.last_idx = i64(last_of_doc)
+        self.flow = {}
+        for reverse in (False, True):
+            need = [(not first[s]) if reverse else (not last[s]) for s in range(nseg)]
+            need_tokens = sum(seg_cu[s + 1] - seg_cu[s] for s in range(nseg) if need[s])
+            piece = max(512, -(-need_tokens // max(1, piece_target)) // 128 * 128 + 128) if need_tokens else 512
+            ranges, table, emit = [], [], []
+            for s in range(nseg):
+                a, b = seg_cu[s], seg_cu[s + 1]
+                cuts = list(range(a, b, piece)) if (need[s] and b > a) else [a]
+                for j, c0 in enumerate(cuts):
+                    c1 = min(b, c0 + piece) if need[s] else b
+                    is_first = first[s] and j == 0
+                    is_last = last[s] and j == len(cuts) - 1
+                    row = -1
+                    if need[s]:
+                        row = len(ranges)
+                        ranges.append([c0, c1])
+                    table.append([doc_of[s], 1 if is_first else 0, 1 if is_last else 0, row])
+                    # the state entering segment s: before its first piece (forward flow), after
+                    # its last piece (reverse flow)
+                    emit.append(s if (j == (len(cuts) - 1 if reverse else 0)) else -1)
+            self.flow[reverse] = dict(n_loc=len(ranges), ranges=i64(ranges or [[0, 0]]), table=i32(table),
+                                      emit=i32(emit), nunits=len(table))
 
 
 _PLANS = {}
 
 
-def _plan(doc_bounds, cap, dev) -> _Plan:
-    key = (tuple(doc_bounds), cap, dev.type, dev.index)
+def _plan(doc_bounds, cap, dev, h) -> _Plan:
+    key = (tuple(doc_bounds), cap, dev.type, dev.index, h)
     p = _PLANS.get(key)
     if p is None:
         if len(_PLANS) >= 64:
             _PLANS.clear()
-        p = _PLANS[key] = _Plan(doc_bounds, cap, dev)
+        # about four state-pass pieces per SM: enough to fill the GPU and hide each CTA's ramp-up
+        p = _PLANS[key] = _Plan(doc_bounds, cap, dev, max(1, 4 * num_sms(dev) // max(1, h)))
     return p
 
 
@@ -134,9 +150,8 @@ def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool)
     _, t, h, d = y.shape
     e = z.shape[-1]
     dev = y.device
-    n_loc = pl.n_rev if reverse else pl.n_fwd
-    ranges = pl.rev_ranges if reverse else pl.fwd_ranges
-    tab = pl.tab_rev if reverse else pl.tab_fwd
+    fl = pl.flow[reverse]
+    n_loc = fl["n_loc"]
     _, sn, sh = ld_strides
     stream = _lib.stream_of(y)
     incoming = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
@@ -144,12 +159,13 @@ def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool)
     gsum = torch.empty(max(n_loc, 1), h, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         if n_loc:
-            rc = lib.la_lasd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(ranges),
+            rc = lib.la_lasd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(fl["ranges"]),
                                         _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
                                         _lib.dtype_code(y), 1 if reverse else 0, 1, stream)
             _lib.check(rc, "la_lasd_state_pass")
-        rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(tab), _lib.ptr(ext),
-                                     _lib.ptr(incoming), None, pl.nseg, h, d, e, 1 if reverse else 0, stream)
+        rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(fl["table"]), _lib.ptr(fl["emit"]),
+                                     _lib.ptr(ext), _lib.ptr(incoming), None, fl["nunits"], h, d, e,
+                                     1 if reverse else 0, stream)
         _lib.check(rc, "la_lasd_fold_states")
     return incoming
 
@@ -163,7 +179,7 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
-    pl = _plan(doc_bounds, cap, dev)
+    pl = _plan(doc_bounds, cap, dev, h)
     s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
     st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
@@ -184,7 +200,7 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
-    pl = _plan(doc_bounds, cap, dev)
+    pl = _plan(doc_bounds, cap, dev, h)
     s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
     ds_out = _incoming_states(lib, q, do, ld32, ld_strides, pl, dfinal_state, reverse=True)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)

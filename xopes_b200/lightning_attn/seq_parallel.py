@@ -16,6 +16,17 @@ into contiguous ranges, one per rank, and a document that crosses a cut is stitc
                          o_t += exp(cum_t) q_t^T S_in        (la_seqpar_correct)
                      to that document's local tokens and exp(G_first) S_in to its end state.
 
+The backward mirrors it in the other direction (lasd_seqpar_backward): every rank runs the local
+backward with the forward state S_in it received and a zero incoming state gradient, publishes the
+state gradient leaving its FIRST document towards the previous rank (d initial_state of that
+document, R_loc), the ranks fold from the right,
+                         dS_out(r-1) = open_start(r) * ( R_loc(r) + spans(r) * exp(G(r)) * dS_out(r) )
+and a rank whose last document continues adds to that document's local tokens
+                         dk_t += exp(rs_t) v_t dS_out^T ,  dv_t += exp(rs_t) k_t dS_out
+(rs_t = log decay from token t, exclusive, to the rank's end) with the same correction kernel.
+dq needs no correction.  The single-device math is the reference's reverse recurrence
+(scalar_decay/lasd_recurrence_triton.py:279-400).
+
 The three phases are separate functions so that tests can run them with any transport (gloo ranks
 on CPU, or several emulated ranks in one process); lasd_seqpar_forward composes them over
 torch.distributed.
@@ -36,6 +47,7 @@ class ShardPlan:
     doc_ids: List[int]         # global index of every local document
     open_start: bool           # first local document began on an earlier rank
     open_end: bool             # last local document continues on the next rank
+    s_in: Optional[torch.Tensor] = None   # set by the forward: true state entering the rank (H,D,E)
 
 
 def token_range(n_total: int, rank: int, world: int) -> Tuple[int, int]:
@@ -191,7 +203,7 @@ def lasd_seqpar_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: t
     o, states, summary = local_phase(q, k, v, ld, plan, local_forward)
     if exchange == "all_gather":
         gathered = torch.empty(world * summary.numel(), dtype=torch.float32, device=summary.device)
-        dist.all_gather_into_tensor(gathered, summary, group=group)
+        exchange_summaries(gathered, summary, group)
         s_in = fold_incoming_state(gathered.view(world, -1), rank, h, d, e)
     elif exchange == "chain":
         s_in = torch.zeros(h, d, e, dtype=torch.float32, device=summary.device)
@@ -203,6 +215,7 @@ def lasd_seqpar_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: t
     else:
         raise ValueError(f"unknown exchange {exchange!r}")
     correct_phase(q, o, states, ld, s_in, plan, correct)
+    plan.s_in = s_in if plan.open_start else None
     return o, states, plan
 
 
@@ -211,3 +224,122 @@ def fold_incoming_state_step(row: torch.Tensor, s_in: torch.Tensor, h: int, d: i
     s_loc = row[: h * d * e].view(h, d, e)
     g = row[h * d * e: h * d * e + h]
     return (row[-2] * (s_loc + row[-1] * torch.exp(g).view(h, 1, 1) * s_in)).contiguous()
+
+
+# --------------------------------------------------------------------------------------------
+# backward
+# --------------------------------------------------------------------------------------------
+def _cuda_local_backward(q, k, v, ld, do, local_cu, s0):
+    """Local backward over the rank's documents (cut further into segments when they are few and
+    long): returns dq, dk, dv and d initial_state per local document."""
+    from . import segmented as sg
+    from .scalar_decay import _prep_ld
+    _, t, h, d = q.shape
+    bounds = [(local_cu[i], local_cu[i + 1]) for i in range(len(local_cu) - 1)]
+    sms = sg.num_sms(q.device)
+    cap = sg.auto_cap(t, h, sms)
+    if not sg.worth_segmenting(bounds, h, cap, sms):
+        cap = 1 << 40  # documents as they are
+    ld32, strides = _prep_ld(ld, 1, t, h)
+    with torch.no_grad():
+        dq, dk, dv, _, ds0 = sg.lasd_backward_segmented(q.contiguous(), k.contiguous(), v.contiguous(), ld32,
+                                                        strides, s0, do.contiguous(), None, bounds, cap,
+                                                        want_dld=False, want_ds0=True)
+    return dq, dk, dv, ds0
+
+
+def local_backward_phase(q, k, v, ld, do, plan: ShardPlan, s_in, local_backward: Optional[Callable] = None):
+    """Phase 1 of the backward.  Returns (dq, dk, dv, ds0, summary); summary is the flat fp32 tensor
+    a rank publishes towards the ranks before it: [R_loc (H*D*E), G (H), open_start, spans]."""
+    bwd = local_backward or _cuda_local_backward
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    ndocs = len(plan.doc_ids)
+    s0 = None
+    if plan.open_start and s_in is not None:
+        s0 = torch.zeros(ndocs, h, d, e, dtype=torch.float32, device=dev)
+        s0[0] = s_in
+    dq, dk, dv, ds0 = bwd(q, k, v, ld, do, plan.local_cu, s0)
+    if not plan.open_start:
+        return dq, dk, dv, ds0, torch.zeros(h * d * e + h + 2, dtype=torch.float32, device=dev)
+    t1 = plan.local_cu[1]
+    g = ld.float() * float(t1) if ld.dim() == 1 else _ld_local(ld, t, h)[:t1].sum(0)
+    spans = 1.0 if (plan.open_end and ndocs == 1) else 0.0
+    flags = torch.tensor([1.0, spans], dtype=torch.float32).to(dev, non_blocking=True)
+    return dq, dk, dv, ds0, torch.cat([ds0[0].reshape(-1), g, flags])
+
+
+def fold_outgoing_gradient(gathered: torch.Tensor, rank: int, h: int, d: int, e: int) -> torch.Tensor:
+    """The state gradient entering `rank` from the right (for its last, continuing document), from
+    the summaries of the ranks after it: gathered is (world, H*D*E + H + 2)."""
+    world = gathered.shape[0]
+    s = torch.zeros(h, d, e, dtype=torch.float32, device=gathered.device)
+    for r in range(world - 1, rank, -1):
+        row = gathered[r]
+        r_loc = row[: h * d * e].view(h, d, e)
+        g = row[h * d * e: h * d * e + h]
+        s = row[-2] * (r_loc + row[-1] * torch.exp(g).view(h, 1, 1) * s)
+    return s
+
+
+def correct_backward_phase(k, v, dk, dv, ld, ds_out, plan: ShardPlan, correct: Optional[Callable] = None):
+    """Phase 3 of the backward, in place on dk and dv: the terms of the last local document that
+    come from the state gradient entering at the rank's end."""
+    if not plan.open_end:
+        return
+    fix = correct or _cuda_correct
+    _, t, h, _ = k.shape
+    last0 = plan.local_cu[-2]
+    n = t - last0
+    if ld.dim() == 1:
+        steps = torch.arange(n - 1, -1, -1, dtype=torch.float32, device=k.device)   # tokens after t
+        rs = steps.view(n, 1) * ld.float().view(1, h)
+    else:
+        lt = _ld_local(ld, t, h)[last0:]
+        rs = (torch.flip(torch.cumsum(torch.flip(lt, [0]).t().contiguous(), dim=1), [1]).t() - lt).contiguous()
+    fix(v[:, last0:], dk[:, last0:], rs, ds_out.transpose(1, 2).contiguous(), n)
+    fix(k[:, last0:], dv[:, last0:], rs, ds_out.contiguous(), n)
+
+
+def lasd_seqpar_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: torch.Tensor, do: torch.Tensor,
+                         cu_seqlens: torch.Tensor, s_in: Optional[torch.Tensor], group=None,
+                         local_backward: Optional[Callable] = None, correct: Optional[Callable] = None):
+    """Backward of lasd_seqpar_forward for q, k, v: this rank's token range of each tensor and of
+    the upstream gradient do; s_in is the state that entered the rank in the forward
+    (plan.s_in of lasd_seqpar_forward; None if the rank starts on a document boundary).  One
+    all-gather of the ranks' outgoing state gradients, folded from the right.  Returns
+    (dq, dk, dv) for the local tokens.  Gradients of ld and of per-document initial states are not
+    produced here."""
+    import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    cu = [int(x) for x in cu_seqlens.tolist()]
+    start, end = token_range(cu[-1], rank, world)
+    if q.shape[1] != end - start:
+        raise ValueError(f"rank {rank} holds {q.shape[1]} tokens, expected {end - start}")
+    plan = shard_documents(cu, start, end)
+    _, _, h, d = q.shape
+    e = v.shape[-1]
+    dq, dk, dv, _, summary = local_backward_phase(q, k, v, ld, do, plan, s_in, local_backward)
+    gathered = torch.empty(world * summary.numel(), dtype=torch.float32, device=summary.device)
+    exchange_summaries(gathered, summary, group)
+    ds_out = fold_outgoing_gradient(gathered.view(world, -1), rank, h, d, e)
+    correct_backward_phase(k, v, dk, dv, ld, ds_out, plan, correct)
+    return dq, dk, dv
+
+
+class SeqParExchangeError(RuntimeError):
+    """The exchange of chunk-end states between ranks failed or timed out (a rank is missing or
+    late beyond the process group's timeout).  Nothing on the device waits for another rank, so the
+    caller may drop the step or rebuild the group."""
+
+
+def exchange_summaries(gathered: torch.Tensor, summary: torch.Tensor, group=None):
+    """One all-gather of the ranks' summaries.  The collective is ordered on the host (NCCL stream
+    order / gloo), so a missing rank shows up here as the process group's timeout or a broken
+    connection, which is turned into SeqParExchangeError instead of propagating a backend error."""
+    import torch.distributed as dist
+    try:
+        dist.all_gather_into_tensor(gathered, summary, group=group)
+    except (RuntimeError, ValueError) as exc:  # DistBackendError derives from RuntimeError
+        raise SeqParExchangeError(f"state exchange failed: {exc}") from exc
