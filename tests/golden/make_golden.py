@@ -9,8 +9,10 @@ The reference's torch operators are loaded BY FILE PATH (importing the `xopes` p
 GPU because it queries the Triton driver at import time).  For every case this script
 
   1. draws seeded inputs on the CPU,
-  2. runs the reference forward (lasd_torch / lavd_torch) and autograd through it,
-  3. checks that oracle/lightning_attn_oracle.py reproduces all of it (rel-L2 <= 1e-5),
+  2. runs the reference forward (lasd_torch / lavd_torch) and autograd through it, or the
+     reference's chunk-level fixtures (scalar_decay/torch_utils.py),
+  3. checks that oracle/lightning_attn_oracle.py (oracle/chunk_fixtures.py) reproduces all of it
+     (rel-L2 <= 1e-5),
   4. stores inputs and the reference's outputs in one .npz per case.
 
 The .npz files are what the CPU tests pin the oracle against and what the GPU tests compare the
@@ -27,6 +29,7 @@ import torch.nn.functional as F
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
+from oracle import chunk_fixtures as cfx  # noqa: E402
 from oracle import lightning_attn_oracle as orc  # noqa: E402
 
 
@@ -152,6 +155,45 @@ def lavd_case(ref, name, seed, b, n, h, d, e, use_ldv, use_init, use_dfinal, sha
          dldk=grads["ldk"], dldv=grads.get("ldv"), dinitial_state=grads.get("s0"))
 
 
+def chunk_fixture_case(ref_root, name, seed, b, n, h, d, e, block):
+    """Outputs of the reference's chunk-level torch fixtures (scalar_decay/torch_utils.py): per-chunk
+    intra outputs, each chunk's own state, the scanned states (forward and reverse) and the inter
+    outputs.  The file imports `contiguous` from the xopes package, which cannot be imported without
+    a GPU; a pass-through stand-in of that decorator (it only calls .contiguous() on tensor
+    arguments, xopes/utils/utils.py:15-26) is registered for the by-path import."""
+    import types
+    stub = types.ModuleType("xopes.utils")
+    stub.contiguous = lambda fn: fn
+    saved = {m: sys.modules.get(m) for m in ("xopes", "xopes.utils")}
+    sys.modules["xopes"], sys.modules["xopes.utils"] = types.ModuleType("xopes"), stub
+    try:
+        tu = load(ref_root, "xopes/ops/lightning_attn/scalar_decay/torch_utils.py", "ref_lasd_torch_utils")
+    finally:
+        for m, old in saved.items():
+            if old is None:
+                sys.modules.pop(m, None)
+            else:
+                sys.modules[m] = old
+    gen = torch.Generator().manual_seed(seed)
+    q = g((b, n, h, d), gen, d ** -0.5)
+    k = g((b, n, h, d), gen, d ** -0.5)
+    v = g((b, n, h, e), gen)
+    ld = F.logsigmoid(g((b, n, h), gen) + 1.0)
+    s0 = 0.1 * g((b, h, d, e), gen)
+    out = dict(q=q, k=k, v=v, ld=ld, initial_state=s0, block=torch.tensor(block))
+    for rev, tag in ((False, "fwd"), (True, "rev")):
+        out["intra_" + tag] = tu.lasd_intra_torch(q, k, v, ld, reverse=rev, BLOCK_N=block)
+        loc, glob = tu.compute_states(k, v, ld, s0, BLOCK_N=block, reverse=rev)
+        out["local_" + tag], out["global_" + tag] = loc, glob
+        check(f"{name}.intra_{tag}", out["intra_" + tag], cfx.lasd_chunk_intra(q, k, v, ld, block, rev))
+        oloc, oglob = cfx.lasd_chunk_states(k, v, ld, s0, block, rev)
+        check(f"{name}.local_{tag}", loc, oloc)
+        check(f"{name}.global_{tag}", glob, oglob)
+    out["inter"] = tu.lasd_inter_torch(q, k, v, ld, s0, BLOCK_N=block)
+    check(name + ".inter", out["inter"], cfx.lasd_chunk_inter(q, k, v, ld, s0, block))
+    save(name, **out)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XOPES_REFERENCE_ROOT")
     if not ref_root:
@@ -167,6 +209,8 @@ def main():
     lasd_case(lasd, "lasd_d128_perhead", 14, 1, 257, 2, 128, 128, True, False, decay="perhead")
     lasd_case(lasd, "lasd_varlen", 15, 1, 90, 2, 32, 32, True, True, lens=[1, 40, 17, 32])
     lasd_case(lasd, "lasd_decode", 16, 3, 1, 4, 64, 48, True, True)
+    # chunk-level intermediates (ragged last chunk)
+    chunk_fixture_case(ref_root, "chunkfx_lasd", 17, 1, 300, 2, 16, 24, 128)
     # vector decay
     lavd_case(lavd, "lavd_k_only", 21, 2, 41, 2, 16, 24, False, True, True)
     lavd_case(lavd, "lavd_kv", 22, 2, 35, 2, 24, 16, True, True, True)

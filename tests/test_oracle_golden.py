@@ -2,6 +2,7 @@
 written by tests/golden/make_golden.py from lasd_torch / lavd_torch and autograd through them)."""
 import pytest
 
+from oracle import chunk_fixtures as cfx
 from oracle import lightning_attn_oracle as orc
 from util import TOL_FP32, assert_close, golden_cases, load_golden
 
@@ -52,3 +53,19 @@ def test_oracle_varlen_equals_per_document_runs():
                                   g["ld"][:, a0:a1], g["initial_state"][i:i + 1])
         assert_close("o", oi, o[:, a0:a1], 1e-6)
         assert_close("state", si[0], sf[i], 1e-6)
+
+
+def test_chunk_fixture_oracle_matches_reference_vectors():
+    """oracle/chunk_fixtures.py against the outputs of the reference's own chunk-level fixtures
+    (scalar_decay/torch_utils.py: lasd_intra_torch, compute_states, lasd_inter_torch)."""
+    g = load_golden("chunkfx_lasd")
+    q, k, v, ld, s0, block = g["q"], g["k"], g["v"], g["ld"], g["initial_state"], int(g["block"])
+    for rev, tag in ((False, "fwd"), (True, "rev")):
+        assert_close("intra_" + tag, g["intra_" + tag], cfx.lasd_chunk_intra(q, k, v, ld, block, rev), TOL_FP32)
+        loc, glob = cfx.lasd_chunk_states(k, v, ld, s0, block, rev)
+        assert_close("local_" + tag, g["local_" + tag], loc, TOL_FP32)
+        assert_close("global_" + tag, g["global_" + tag], glob, TOL_FP32)
+    assert_close("inter", g["inter"], cfx.lasd_chunk_inter(q, k, v, ld, s0, block), TOL_FP32)
+    # the pieces add up: intra + inter is the full forward
+    o, _ = orc.lasd_forward(q, k, v, ld, s0)
+    assert_close("intra + inter", o, g["intra_fwd"] + g["inter"], TOL_FP32)
