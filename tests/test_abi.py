@@ -41,10 +41,14 @@ def test_status_strings(lib):
 
 
 def test_path_choice(lib):
-    # tensor-core chunk kernels: 16-bit inputs with D = E = 128 only
-    assert lib.la_lasd_path(8192, 128, 128, _lib.LA_BF16, 0) in (0, 1)
+    # tensor-core chunk kernels: 16-bit inputs, head dimensions up to 128 in multiples of 8, N >= 128
+    assert lib.la_lasd_path(8192, 128, 128, _lib.LA_BF16, 0) == 1
     assert lib.la_lasd_path(8192, 128, 128, _lib.LA_F32, 0) == 0
-    assert lib.la_lasd_path(8192, 64, 128, _lib.LA_BF16, 0) == 0
+    assert lib.la_lasd_path(8192, 64, 128, _lib.LA_BF16, 0) == 1
+    assert lib.la_lasd_path(8192, 64, 64, _lib.LA_F16, 0) == 1
+    assert lib.la_lasd_path(8192, 256, 128, _lib.LA_BF16, 0) == 0
+    assert lib.la_lasd_path(8192, 60, 64, _lib.LA_BF16, 0) == 0
+    assert lib.la_lasd_path(64, 128, 128, _lib.LA_BF16, 0) == 0
     assert lib.la_lasd_path(8192, 128, 128, _lib.LA_BF16, _lib.FLAG_FORCE_RECURRENCE) == 0
     assert lib.la_lasd_path(8192, 33, 63, _lib.LA_BF16, _lib.FLAG_REQUIRE_TENSOR) == -3
     assert lib.la_lasd_path(8192, 128, 128, 7, 0) == -3

@@ -147,11 +147,24 @@ def test_lasd_reference_shapes_fp32(shape, use_state, use_dfinal):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(2, 300, 4, 128, 128), (1, 128, 2, 128, 128), (2, 200, 3, 64, 64),
-                                   (1, 1, 2, 128, 128), (1, 513, 2, 128, 128), (1, 129, 3, 128, 128)])
+                                   (1, 1, 2, 128, 128), (1, 513, 2, 128, 128), (1, 129, 3, 128, 128),
+                                   (2, 300, 2, 64, 128), (1, 257, 2, 128, 32), (2, 384, 3, 96, 40),
+                                   (1, 700, 2, 8, 16)])
 def test_lasd_16bit(shape, dtype):
     import xopes_b200 as xb
     _run_lasd_case(xb.lasd_fn, *shape, seed=7, dtype=dtype, use_state=True, use_dfinal=True,
                    weak_decay=False, tol=TOL_BF16)
+
+
+def test_lasd_reference_training_shape_bf16():
+    """The reference's training shape (tests/lightning_attn/scalar_decay/test.py:13-32:
+    (8, 2048, 12, 64, 64)) at a quarter of its batch, in bf16: head dimension 64 on the tensor-core
+    path, 24 (sequence, head) pairs."""
+    import xopes_b200 as xb
+    from xopes_b200 import _lib
+    assert xb.load_library().la_lasd_path(2048, 64, 64, _lib.LA_BF16, _lib.FLAG_REQUIRE_TENSOR) == 1
+    _run_lasd_case(xb.lasd_fn, 2, 2048, 12, 64, 64, seed=2024, dtype=torch.bfloat16, use_state=True,
+                   use_dfinal=True, weak_decay=True, tol=TOL_BF16)
 
 
 def test_config1_fp32_forward():

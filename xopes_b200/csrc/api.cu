@@ -237,6 +237,7 @@ int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, in
     c.ld = ld; c.ld_sb = ld_sb; c.ld_sn = ld_sn; c.ld_sh = ld_sh;
     c.t0 = initial_state; c.tfinal = final_state; c.state_transposed = 0; c.reverse = 0;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens;
+    c.fx = s.D; c.fz = s.E;
     return launch_chunk_pass(c, dtype, st);
   }
   return scan_forward(s, q, k, v, ld, ld_sb, ld_sn, ld_sh, nullptr, nullptr, initial_state, o,
@@ -294,6 +295,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.no_scratch = no_scratch;
     // dq: (X,Y,Z) = (do, v, k), state S^T, forward direction
     c.x = d_o; c.y = v; c.z = k; c.out = dq; c.t0 = initial_state; c.state_transposed = 1;
+    c.fx = s.E; c.fz = s.D;
     c.tfinal = state_term ? ws_state : nullptr; c.reverse = 0;
     c.xrow = want_dld ? q : nullptr; c.rowdot = slots_q;
     // With few (sequence, head) pairs the dq pass runs beside the merged dk/dv launch.
@@ -315,6 +317,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     // the tokens last to first and both read q and do: one launch, neighbouring CTAs.
     ChunkPass c2 = c;
     c2.x = k; c2.y = q; c2.z = d_o; c2.out = dv; c2.t0 = dfinal_state; c2.state_transposed = 0;
+    c2.fx = s.D; c2.fz = s.E;
     c2.tfinal = dinitial_state; c2.reverse = 1; c2.xrow = nullptr; c2.rowdot = nullptr;
     rc = launch_chunk_pass_pair(c, c2, dtype, st);
     if (side != nullptr) {

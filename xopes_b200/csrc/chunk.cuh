@@ -15,18 +15,19 @@ namespace la {
 // transposed gives dk; (k,q,do) reversed gives dv
 // (xopes/ops/lightning_attn/scalar_decay/lasd_parallel_triton.py:548-563,651-733).
 struct ChunkPass {
-  const void *x = nullptr, *y = nullptr, *z = nullptr;  // (B,N,H,128) dtype
-  void *out = nullptr;                                   // (B,N,H,128) dtype
-  const void *xrow = nullptr;                            // optional (B,N,H,128): rowdot = sum_f xrow*W
+  const void *x = nullptr, *y = nullptr, *z = nullptr;  // (B,N,H,fx), (B,N,H,fx), (B,N,H,fz) dtype
+  void *out = nullptr;                                   // (B,N,H,fz) dtype
+  const void *xrow = nullptr;                            // optional (B,N,H,fz): rowdot = sum_f xrow*W
   float *rowdot = nullptr;                               // (B,N,H) fp32
   const float *ld = nullptr;
   int64_t ld_sb = 0, ld_sn = 0, ld_sh = 0;
-  const float *t0 = nullptr;                             // (nb,H,128,128) fp32 or null
-  float *tfinal = nullptr;                               // (nb,H,128,128) fp32 or null
+  const float *t0 = nullptr;                             // (nb,H,D,E) fp32 or null
+  float *tfinal = nullptr;                               // (nb,H,D,E) fp32 or null
   int state_transposed = 0;                              // T[i][j] lives at state[j][i]
   int reverse = 0;
   const int64_t *cu = nullptr;
   int B = 0, N = 0, H = 0, M = 0;
+  int fx = 128, fz = 128;  // features per head of x, y (the contraction of X Y^T) and of z, out, xrow
   int no_scratch = 0;  // 1: never take hand-off scratch from the library's pool (one CTA per pair)
 };
 

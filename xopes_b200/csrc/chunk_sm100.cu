@@ -106,6 +106,7 @@ struct ChunkArgs {
   int state_transposed, reverse;
   const long long *cu;
   int B, N, H, M;
+  int fx, fz;  // features of X and Y (the contraction of X Y^T) and of Z, the output and xrow; <= 128
   int *status;
 };
 
@@ -237,7 +238,13 @@ __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) 
 // Every role walks the CTA's tasks in the same order and numbers the chunks it has handled with
 // one running counter; pipeline stages and mbarrier parities follow that counter, so the
 // pipeline never drains between tasks.
-template <typename T>
+//
+// F128 = true: every tensor has 128 features per head.  F128 = false: head dimensions below 128
+// (multiples of 8).  The tiles stay 128 wide: the tensor maps then describe fewer features than a
+// box holds, TMA fills the rest of the box with zeros on load and clips it on store, and the zero
+// features add nothing to any product; only the accesses that bypass TMA (states, ragged last
+// chunks, the row-dot operand) look at the real widths.
+template <typename T, bool F128>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Launch lp) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -453,7 +460,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             const uint32_t zs = base + (uint32_t)s * kStageBytes + 2 * kTileBytes;
             const int tok0 = (int)tk.t_begin + n * kChunk;
             tma_store_4d(map_o, zs, 0, tk.h, tok0, tk.bidx);
-            tma_store_4d(map_o, zs + kBoxBytes, 64, tk.h, tok0, tk.bidx);
+            if (F128 || ap.fz > 64) tma_store_4d(map_o, zs + kBoxBytes, 64, tk.h, tok0, tk.bidx);
             tma_store_commit();
             tma_store_wait_read();
           }
@@ -607,7 +614,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         t_len = tk.len;
         t_cnt = tk.cnt;
         ld_row = a.ld + tk.bidx * a.ld_sb + tk.h * a.ld_sh + (tk.t_begin + i) * a.ld_sn;
-        row_base = ((tk.bidx * (long long)a.N + tk.t_begin + i) * a.H + tk.h) * (long long)kChunk;
+        row_base = ((tk.bidx * (long long)a.N + tk.t_begin + i) * a.H + tk.h) * (long long)(F128 ? kChunk : ap.fz);
 
         // starting state -> tensor memory (this warpgroup's 64 columns): the caller's state, or
         // what the neighbouring CTA left in its hand-off slot
@@ -628,15 +635,25 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
           named_bar_sync(3, kComputeThreads);
           src = sc.handoff + (size_t)(blockIdx.x - sc.npass) * (kChunk * kChunk);
         } else if (ap.t0 != nullptr) {
-          src = ap.t0 + ((long long)tk.seq * a.H + tk.h) * (long long)(kChunk * kChunk);
+          src = ap.t0 + ((long long)tk.seq * a.H + tk.h) * (long long)(F128 ? kChunk * kChunk : ap.fx * ap.fz);
           src_tr = ap.state_transposed != 0;
         }
+        const bool narrow = !F128 && !tk.waits;  // the caller's state has the real widths
         for (int b2 = 0; b2 < 2; ++b2) {
           const int bt = 2 * wg + b2;
           uint32_t r[32];
           if (src == nullptr) {
 #pragma unroll
             for (int kk = 0; kk < 32; ++kk) r[kk] = 0u;
+          } else if (narrow) {  // (fx, fz) state: T[i][c] at c * fx + i (transposed) or i * fz + c
+            const int fx = ap.fx, fz = ap.fz;
+#pragma unroll
+            for (int kk = 0; kk < 32; ++kk) {
+              const int c = bt * 32 + kk;
+              float val = 0.f;
+              if (i < fx && c < fz) val = __ldcg(src + (src_tr ? c * fx + i : i * fz + c));
+              r[kk] = __float_as_uint(val);
+            }
           } else if (src_tr) {  // element (i, c) at c * 128 + i: a warp reads 128 contiguous bytes
 #pragma unroll
             for (int kk = 0; kk < 32; ++kk) r[kk] = __float_as_uint(__ldcg(src + (bt * 32 + kk) * kChunk + i));
@@ -658,9 +675,11 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (ap.t0 != nullptr && k + 1 < ntasks) {
           const Task nx = task_of(a, range(), k + 1, ntasks);
           if (!nx.waits) {
-            const char *pn = reinterpret_cast<const char *>(ap.t0 + ((long long)nx.seq * a.H + nx.h) * (long long)(kChunk * kChunk));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)tid * 128));
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)(tid + kComputeThreads) * 128));
+            if (F128) {
+              const char *pn = reinterpret_cast<const char *>(ap.t0 + ((long long)nx.seq * a.H + nx.h) * (long long)(kChunk * kChunk));
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)tid * 128));
+              asm volatile("prefetch.global.L2 [%0];" ::"l"(pn + (size_t)(tid + kComputeThreads) * 128));
+            }
           }
         }
       }
@@ -692,7 +711,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (split) {
           // the epilogue dots the output with this row of xrow, read from global memory: start
           // that fetch now (one 128-byte line per thread) so that it is in cache by then
-          if (i < L) {
+          if (F128 && i < L) {
             const char *xr = reinterpret_cast<const char *>(static_cast<const T *>(ap.xrow) + row_base +
                                                               (long long)n * kChunk * a.H * kChunk + 64 * wg);
             asm volatile("prefetch.global.L1 [%0];" ::"l"(xr));
@@ -822,7 +841,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         mbar_wait(bar_w, par, abort_flag, a.status, kStW);
         tc_fence_after();
         const bool full_chunk = (L == kChunk);
-        const long long row_off = row_base + (long long)n * kChunk * a.H * kChunk;
+        const int fz = F128 ? kChunk : ap.fz;
+        const long long row_off = row_base + (long long)n * kChunk * a.H * fz;
         const float s_i = cur.s;
         float rd = 0.f;
 #pragma unroll 1
@@ -844,6 +864,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             const uint4 *xp = reinterpret_cast<const uint4 *>(static_cast<const T *>(ap.xrow) + row_off + c0);
 #pragma unroll
             for (int pc = 0; pc < 4; ++pc) {
+              if (!F128 && c0 + pc * 8 >= fz) break;  // features beyond the real width are zero
               const uint4 xv = xp[pc];
               float2 f;
               f = Fmt<T>::unpack(xv.x); rd = fmaf(f.x, w[pc * 8 + 0], rd); rd = fmaf(f.y, w[pc * 8 + 1], rd);
@@ -862,7 +883,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
             if (full_chunk) {
               // staging = this stage's Z tile (dead once the MMAs above have completed)
               *reinterpret_cast<uint4 *>(stage + 2 * kTileBytes + wg * kBoxBytes + sw128_offset(i, b2 * 4 + pc)) = v;
-            } else if (i < L) {
+            } else if (i < L && (F128 || c0 + pc * 8 < fz)) {
               reinterpret_cast<uint4 *>(static_cast<T *>(ap.out) + row_off + c0)[pc] = v;
             }
           }
@@ -870,7 +891,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (split) {  // uniform over the CTA
           if (wg == 1) sm->rd[i] = rd;
           named_bar_sync(2, kComputeThreads);
-          if (wg == 0 && i < L) ap.rowdot[row_off >> 7] = rd + sm->rd[i];
+          if (wg == 0 && i < L) ap.rowdot[F128 ? (row_off >> 7) : (row_off / fz)] = rd + sm->rd[i];
         }
         if (full_chunk) fence_proxy_async();
         tc_fence_before();
@@ -886,14 +907,23 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
         if (tk.publishes || ap.tfinal != nullptr) {
           tc_fence_after();
           float *dst = tk.publishes ? sc.handoff + (size_t)blockIdx.x * (kChunk * kChunk)
-                                    : ap.tfinal + ((long long)tk.seq * a.H + tk.h) * (long long)(kChunk * kChunk);
+                                    : ap.tfinal + ((long long)tk.seq * a.H + tk.h) *
+                                                      (long long)(F128 ? kChunk * kChunk : ap.fx * ap.fz);
           const bool dst_tr = tk.publishes || ap.state_transposed != 0;
+          const bool narrow_out = !F128 && !tk.publishes;
           for (int b2 = 0; b2 < 2; ++b2) {
             const int bt = 2 * wg + b2;
             uint32_t r[32];
             tmem_ld32(tl + kColT + bt * 32, r);
             tmem_wait_ld();
-            if (dst_tr) {
+            if (narrow_out) {
+              const int fx = ap.fx, fzs = ap.fz;
+#pragma unroll
+              for (int kk = 0; kk < 32; ++kk) {
+                const int c = bt * 32 + kk;
+                if (i < fx && c < fzs) dst[ap.state_transposed ? c * fx + i : i * fzs + c] = __uint_as_float(r[kk]);
+              }
+            } else if (dst_tr) {
 #pragma unroll
               for (int kk = 0; kk < 32; ++kk) dst[(bt * 32 + kk) * kChunk + i] = __uint_as_float(r[kk]);
             } else {
@@ -962,7 +992,7 @@ __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wpre
 }
 
 struct DeviceInfo {
-  bool ready = false, attr_bf16 = false, attr_f16 = false, pool_tried = false;
+  bool ready = false, attr[4] = {false, false, false, false}, pool_tried = false;
   int sms = 0, dev = 0;
   cudaMemPool_t pool = nullptr;  // hand-off scratch; made on first need, null if that failed
 };
@@ -1011,10 +1041,10 @@ inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 template <typename T>
 int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   int rc;
-  if ((rc = make_map(&m.x, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&m.y, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&m.z, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&m.o, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&m.x, p.x, dtype, p.B, p.N, p.H, p.fx)) != LA_OK) return rc;
+  if ((rc = make_map(&m.y, p.y, dtype, p.B, p.N, p.H, p.fx)) != LA_OK) return rc;
+  if ((rc = make_map(&m.z, p.z, dtype, p.B, p.N, p.H, p.fz)) != LA_OK) return rc;
+  if ((rc = make_map(&m.o, p.out, dtype, p.B, p.N, p.H, p.fz)) != LA_OK) return rc;
   if (p.xrow != nullptr && (reinterpret_cast<uintptr_t>(p.xrow) & 15u)) return LA_ERR_MISALIGNED;
   if ((reinterpret_cast<uintptr_t>(p.t0) | reinterpret_cast<uintptr_t>(p.tfinal)) & 15u) return LA_ERR_MISALIGNED;
   a.xrow = p.xrow; a.rowdot = p.xrow ? p.rowdot : nullptr; a.out = p.out;
@@ -1022,6 +1052,7 @@ int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   a.t0 = p.t0; a.tfinal = p.tfinal; a.state_transposed = p.state_transposed; a.reverse = p.reverse;
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
+  a.fx = p.fx; a.fz = p.fz;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   return LA_OK;
@@ -1037,8 +1068,9 @@ int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t str
   if ((rc = fill_pass<T>(q ? *q : p, dtype, maps.p[1], lp.a[1])) != LA_OK) return rc;
   DeviceInfo *di = device_info();
   if (di == nullptr) return LA_ERR_CUDA;
-  auto kern = chunk_pass_kernel<T>;
-  bool &attr = (dtype == LA_BF16) ? di->attr_bf16 : di->attr_f16;  // the attribute is per device
+  const bool f128 = p.fx == 128 && p.fz == 128 && (q == nullptr || (q->fx == 128 && q->fz == 128));
+  auto kern = f128 ? chunk_pass_kernel<T, true> : chunk_pass_kernel<T, false>;
+  bool &attr = di->attr[(dtype == LA_BF16 ? 0 : 1) + (f128 ? 0 : 2)];  // the attribute is per device
   if (!attr) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return LA_ERR_CUDA;
@@ -1213,8 +1245,8 @@ template <typename T>
 int probe_t(int variant, const void *a, const void *b, float *d, int dtype, cudaStream_t stream) {
   alignas(64) CUtensorMap ma, mb;
   int rc;
-  if ((rc = make_map(&ma, a, dtype, 1, 128, 1)) != LA_OK) return rc;
-  if ((rc = make_map(&mb, b, dtype, 1, 128, 1)) != LA_OK) return rc;
+  if ((rc = make_map(&ma, a, dtype, 1, 128, 1, 128)) != LA_OK) return rc;
+  if ((rc = make_map(&mb, b, dtype, 1, 128, 1, 128)) != LA_OK) return rc;
   int *status = status_word_ptr();
   if (status == nullptr) return LA_ERR_CUDA;
   const int smem = 2 * kTileBytes + kSmallBytes + 1024;
@@ -1242,7 +1274,9 @@ int wait_probe(uint32_t limit_us, cudaStream_t stream) {
 }
 
 bool chunk_supported(int64_t N, int64_t D, int64_t E, int dtype) {
-  return (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
+  // head dimensions up to 128 in multiples of 8 (a row of a tensor must stay 16-byte aligned)
+  return (dtype == LA_BF16 || dtype == LA_F16) && D >= 8 && E >= 8 && D <= 128 && E <= 128 && D % 8 == 0 &&
+         E % 8 == 0 && N >= 128;
 }
 
 namespace {
@@ -1251,6 +1285,7 @@ int check_pass(const ChunkPass &p) {
     return LA_ERR_NULL_POINTER;
   const int nb = p.cu ? p.M : p.B;
   if (nb <= 0 || p.H <= 0 || p.N <= 0) return LA_ERR_BAD_SHAPE;
+  if (p.fx < 8 || p.fz < 8 || p.fx > 128 || p.fz > 128 || p.fx % 8 || p.fz % 8) return LA_ERR_UNSUPPORTED;
   if ((int64_t)nb * p.H * 2 > 0x7fffffff) return LA_ERR_TOO_LARGE;
   return LA_OK;
 }

@@ -74,9 +74,10 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (B, N, H, 128) tensor of 16-bit (dtype LA_BF16 / LA_F16) or fp32 (LA_F32) elements.  One box =
-// 128 tokens x 128 bytes of one head (64 16-bit or 32 fp32 features), 128-byte swizzle.
-inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H) {
+// (B, N, H, F) tensor of 16-bit (dtype LA_BF16 / LA_F16) or fp32 (LA_F32) elements, F <= 128
+// features per head.  One box = 128 tokens x 128 bytes of one head (64 16-bit or 32 fp32 features),
+// 128-byte swizzle; where a box reaches past feature F - 1 a load fills zeros and a store clips.
+inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, int H, int F = 128) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return LA_ERR_CUDA;
   // The encoder is a driver call and needs this thread to have the device's context current; a
@@ -89,8 +90,9 @@ inline int make_map(CUtensorMap *m, const void *ptr, int dtype, int B, int N, in
   }
   if (reinterpret_cast<uintptr_t>(ptr) & 15u) return LA_ERR_MISALIGNED;
   const cuuint64_t esz = dtype == LA_F32 ? 4 : 2;
-  const cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
-  const cuuint64_t strides[3] = {128 * esz, (cuuint64_t)H * 128 * esz, (cuuint64_t)N * H * 128 * esz};
+  const cuuint64_t f = (cuuint64_t)F;
+  const cuuint64_t dims[4] = {f, (cuuint64_t)H, (cuuint64_t)N, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {f * esz, (cuuint64_t)H * f * esz, (cuuint64_t)N * H * f * esz};
   const cuuint32_t box[4] = {(cuuint32_t)(128 / esz), 1, 128, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = dtype == LA_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32

@@ -63,7 +63,7 @@ def _segmentation(lib, q, ld32, strides, cu, b, n, h, d, e, flags):
     stream, its strides) or None.  Only for calls without cu_seqlens: the bounds must be known on
     the host without a device round trip."""
     from . import segmented as sg
-    if cu is not None or (flags & _lib.FLAG_FORCE_RECURRENCE):
+    if cu is not None or (flags & _lib.FLAG_FORCE_RECURRENCE) or d != 128 or e != 128:
         return None
     if lib.la_lasd_path(n, d, e, _lib.dtype_code(q), flags) != 1:
         return None

@@ -99,6 +99,7 @@ class _Plan:
         # state-only pass runs on finer pieces than the segments (there are few segments that need
         # it, and a piece per CTA walks its tokens serially), and the fold runs over the pieces.
         self.nseg, self.ndocs = nseg, len(doc_bounds)
+        self.cut = nseg > len(doc_bounds)
         i64 = lambda x: torch.tensor(x, dtype=torch.int64).to(dev)  # noqa: E731
         i32 = lambda x: torch.tensor(x, dtype=torch.int32).to(dev)  # noqa: E731
         self.cu_dev = i64(seg_cu)
@@ -187,7 +188,7 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
     with torch.cuda.device(dev):
         rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
                              _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
-                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, _lib.stream_of(q))
+                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR if pl.cut else 0, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd (segmented)")
     return o, st.index_select(0, pl.last_idx)
 
@@ -215,7 +216,8 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
         rc = lib.la_lasd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
                              _lib.ptr(do), _lib.ptr(ds_out), _lib.ptr(pl.cu_dev), _lib.ptr(dq), _lib.ptr(dk),
                              _lib.ptr(dv), _lib.ptr(dld), _lib.ptr(ds0), _lib.ptr(ws), ws_bytes, 1, t, h, d, e,
-                             pl.nseg, _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, _lib.stream_of(q))
+                             pl.nseg, _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR if pl.cut else 0,
+                             _lib.stream_of(q))
         _lib.check(rc, "la_lasd_bwd (segmented)")
     if want_ds0:
         ds0 = ds0.index_select(0, pl.first_idx)

@@ -89,7 +89,7 @@ def _cuda_local_forward(q, k, v, ld, local_cu):
     sms = sg.num_sms(q.device) if q.is_cuda else 148
     cap = sg.auto_cap(t, h, sms)
     lib = _lib.load()
-    if (q.is_cuda and lib.la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1
+    if (q.is_cuda and d == 128 and e == 128 and lib.la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1
             and sg.worth_segmenting(bounds, h, cap, sms)):
         # few long documents on this rank: cut them further so that every SM has a segment
         ld32, strides = _prep_ld(ld, 1, t, h)
@@ -238,7 +238,9 @@ def _cuda_local_backward(q, k, v, ld, do, local_cu, s0):
     bounds = [(local_cu[i], local_cu[i + 1]) for i in range(len(local_cu) - 1)]
     sms = sg.num_sms(q.device)
     cap = sg.auto_cap(t, h, sms)
-    if not sg.worth_segmenting(bounds, h, cap, sms):
+    e = v.shape[-1]
+    tensor = d == 128 and e == 128 and _lib.load().la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1
+    if not (tensor and sg.worth_segmenting(bounds, h, cap, sms)):
         cap = 1 << 40  # documents as they are
     ld32, strides = _prep_ld(ld, 1, t, h)
     with torch.no_grad():
