@@ -221,6 +221,20 @@ LA_API int la_lasd_fold_states(const float *local, const float *gsum, const int3
                                const int32_t *emit, const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H,
                                int64_t D, int64_t E, int reverse, void *stream);
 
+/* The same pair for vector decay on the features of y (ldk (B,N,H,128) fp32, contiguous):
+ *     states[s,h][d][e] = sum_j w_jd y_jd z_je ,  gsum[s,h][d] = the sequence's total log decay of feature d
+ * with w_jd = exp(sum of ldk[.,d] after token j) (reverse = 0) or exp(sum up to and including token j)
+ * (reverse = 1); (y,z) = (k,v) forward gives S, (q,do) reverse gives dS.  Every factor is <= 1, so
+ * this pass has no limit on the strength of the decay.  la_lavd_fold_states folds with the
+ * per-feature decay on the state's rows: s = local + exp(gsum[d]) (.) s.  No counterpart in the
+ * reference (its chunk-level states live in HBM, vector_decay/lavd_parallel_triton.py:25-316). */
+LA_API int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int64_t *cu_seqlens,
+                              float *states, float *gsum, int64_t B, int64_t N, int64_t H, int64_t D,
+                              int64_t E, int64_t M, int dtype, int reverse, int ranges, void *stream);
+LA_API int la_lavd_fold_states(const float *local, const float *gsum, const int32_t *seg_table,
+                               const int32_t *emit, const float *ext, float *incoming, int64_t nseg,
+                               int64_t H, int64_t D, int64_t E, int reverse, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Sequence-parallel scalar decay (no counterpart in the reference, which has no distributed code;
  * the math is lasd_torch's varlen recurrence, scalar_decay/lasd_torch.py:61-103, cut at a rank

@@ -186,3 +186,89 @@ def test_state_pass_and_fold_match_the_oracle(lib):
             want = [states[1] + dec[1] * ext[0], ext[0], states[3] + dec[3] * ext[1], ext[1]]
         for j in range(len(segs)):
             assert_close(f"incoming seg {j} reverse={reverse}", want[j], inc[j], 1e-6)
+
+
+@pytest.mark.parametrize("regime", ["weak", "reference_benchmark"])
+def test_vector_decay_state_pass_and_fold(lib, regime):
+    """la_lavd_state_pass / la_lavd_fold_states through the C ABI against the oracle's final states
+    (forward flow) and initial-state gradients (reverse flow) of the same token ranges; the strong
+    decay of the reference's benchmark script must be as exact as the weak one (no range limit)."""
+    from xopes_b200 import _lib
+    n, h, d = 900, 2, 128
+    g = torch.Generator().manual_seed(9)
+    cast = lambda t: t.bfloat16().float()  # noqa: E731
+    q = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    k = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(1, n, h, d, generator=g))
+    do = cast(torch.randn(1, n, h, d, generator=g))
+    x = torch.randn(1, n, h, d, generator=g)
+    ldk = torch.nn.functional.logsigmoid(x) / (16 if regime == "weak" else 1)
+    segs = [(0, 300), (300, 556), (556, 900)]
+    dev = "cuda"
+    qc, kc, vc, doc_, lc = (t.to(dev) for t in (q.bfloat16(), k.bfloat16(), v.bfloat16(), do.bfloat16(), ldk))
+    ranges = torch.tensor(segs, dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    for reverse, (y, z) in ((0, (kc, vc)), (1, (qc, doc_))):
+        states = torch.empty(len(segs), h, d, d, device=dev)
+        gsum = torch.empty(len(segs), h, d, device=dev)
+        assert lib.la_lavd_state_pass(y.data_ptr(), z.data_ptr(), lc.data_ptr(), ranges.data_ptr(), states.data_ptr(),
+                                      gsum.data_ptr(), 1, n, h, d, d, len(segs), _lib.LA_BF16, reverse, 1, stream) == 0
+        for j, (a, b) in enumerate(segs):
+            sl = slice(a, b)
+            if reverse == 0:
+                _, ref = orc.lavd_forward(q[:, sl], k[:, sl], v[:, sl], ldk[:, sl], None)
+            else:
+                zero = torch.zeros(1, h, d, d)
+                *_, ref = orc.lavd_backward(q[:, sl], k[:, sl], v[:, sl], ldk[:, sl], None, do[:, sl], zero)
+            assert_close(f"state seg {j} reverse={reverse}", ref[0], states[j], TOL_BF16)
+            assert_close(f"gsum seg {j}", ldk[0, sl].sum(0), gsum[j], 1e-5)
+        tab = torch.tensor([[0, 1, 0, 0], [0, 0, 0, 1], [0, 0, 1, 2]], dtype=torch.int32, device=dev)
+        ext = 0.1 * torch.randn(1, h, d, d, generator=g).to(dev)
+        inc = torch.empty_like(states)
+        assert lib.la_lavd_fold_states(states.data_ptr(), gsum.data_ptr(), tab.data_ptr(), None, ext.data_ptr(),
+                                       inc.data_ptr(), len(segs), h, d, d, reverse, stream) == 0
+        dec = torch.exp(gsum).view(len(segs), h, d, 1)
+        if reverse == 0:
+            s1 = states[0] + dec[0] * ext[0]
+            want = [ext[0], s1, states[1] + dec[1] * s1]
+        else:
+            s1 = states[2] + dec[2] * ext[0]
+            want = [states[1] + dec[1] * s1, s1, ext[0]]
+        for j in range(len(segs)):
+            assert_close(f"incoming seg {j} reverse={reverse}", want[j], inc[j], 1e-6)
+
+
+@pytest.mark.parametrize("regime", ["weak", "reference_benchmark"])
+@pytest.mark.parametrize("b,n,h", [(1, 4096, 2), (2, 2500, 1)])
+def test_vector_decay_segmented_passes(b, n, h, regime):
+    """Few long sequences with vector decay: lavd_fn cuts them into segments (state-only pass, fold,
+    varlen chunk passes) forward and backward; everything, the log-decay gradient and the gradient
+    of the initial state included, must match the oracle on the whole sequences."""
+    import xopes_b200 as xb
+    from xopes_b200.lightning_attn import vector_decay as vd
+    d = e = 128
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(5)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    x = torch.randn(b, n, h, d, generator=g)
+    ldk = torch.nn.functional.logsigmoid(x) / (16 if regime == "weak" else 1)
+    q = cast(torch.randn(b, n, h, d, generator=g))
+    k = cast((1 - torch.exp(ldk)) * torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(b, n, h, e, generator=g))
+    s0 = 0.1 * torch.randn(b, h, d, e, generator=g)
+    do = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = 0.1 * torch.randn(b, h, d, e, generator=g)
+    qc, kc, vc = (t.to(dtype).cuda().requires_grad_() for t in (q, k, v))
+    lc, s0c = ldk.cuda().requires_grad_(), s0.cuda().requires_grad_()
+    assert vd._segmentation(xb.load_library(), qc, lc, None, None, b, n, h, d, e, 0) is not None
+    o, sf = xb.lavd_fn(qc, kc, vc, ldk=lc, initial_state=s0c)
+    ro, rsf = orc.lavd_forward(q, k, v, ldk, None, s0)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * do.cuda()).sum() + (sf * dsf.cuda()).sum()).backward()
+    rq, rk, rv, rlk, _, rs0 = orc.lavd_backward(q, k, v, ldk, None, do, s0, dsf)
+    assert_close("dq", rq, qc.grad.float(), TOL_BF16)
+    assert_close("dk", rk, kc.grad.float(), TOL_BF16)
+    assert_close("dv", rv, vc.grad.float(), TOL_BF16)
+    assert_close("dldk", rlk, lc.grad, TOL_BF16)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)

@@ -47,6 +47,9 @@ SIGNATURES = {
     "la_lasd_state_pass": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp,
                                   _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "la_lasd_fold_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "la_lavd_state_pass": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
+                                  _i32, _vp]),
+    "la_lavd_fold_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_seqpar_fold": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_fold_segments": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_correct_multi": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),

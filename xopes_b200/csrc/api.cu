@@ -651,6 +651,30 @@ int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *se
                             reverse != 0, static_cast<cudaStream_t>(stream));
 }
 
+int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int64_t *cu_seqlens, float *states,
+                       float *gsum, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E, int64_t M, int dtype,
+                       int reverse, int ranges, void *stream) {
+  int rc = check_common(y, z, y, B, N, H, D, E, M, cu_seqlens, dtype);
+  if (rc == LA_OK && ranges != 0 && cu_seqlens == nullptr) rc = LA_ERR_NULL_POINTER;
+  if (rc != LA_OK) return rc;
+  if (ldk == nullptr || states == nullptr) return LA_ERR_NULL_POINTER;
+  if (D != 128 || E != 128 || !(dtype == LA_BF16 || dtype == LA_F16)) return LA_ERR_UNSUPPORTED;
+  StatePass p;
+  p.y = y; p.z = z; p.ldv = ldk; p.cu = cu_seqlens; p.states = states; p.gsum = gsum;
+  p.B = (int)B; p.N = (int)N; p.H = (int)H; p.M = (int)M; p.reverse = reverse != 0; p.ranges = ranges != 0;
+  return launch_state_pass_vec(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int la_lavd_fold_states(const float *local, const float *gsum, const int32_t *seg_table, const int32_t *emit,
+                        const float *ext, float *incoming, int64_t nseg, int64_t H, int64_t D, int64_t E, int reverse,
+                        void *stream) {
+  if (local == nullptr || gsum == nullptr || seg_table == nullptr || incoming == nullptr) return LA_ERR_NULL_POINTER;
+  if (nseg <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
+  if (nseg > 65535 || H * D * E > 0x7fffffff) return LA_ERR_TOO_LARGE;
+  return launch_fold_states_vec(local, gsum, seg_table, emit, ext, incoming, (int)nseg, (int)H, (int)D, (int)E,
+                                reverse != 0, static_cast<cudaStream_t>(stream));
+}
+
 int la_seqpar_fold(const float *gathered, float *s_in, int64_t rank, int64_t H, int64_t D, int64_t E,
                    void *stream) {
   if (gathered == nullptr || s_in == nullptr) return LA_ERR_NULL_POINTER;

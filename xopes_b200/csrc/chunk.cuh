@@ -74,15 +74,19 @@ int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream);
 // (inclusive) (state at the start, reverse flow).  16-bit, 128 features.
 struct StatePass {
   const void *y = nullptr, *z = nullptr;  // (B,N,H,128) dtype
-  const float *ld = nullptr;
+  const float *ld = nullptr;               // scalar decay: strided fp32
   int64_t ld_sb = 0, ld_sn = 0, ld_sh = 0;
+  const float *ldv = nullptr;              // vector decay: (B,N,H,128) fp32 on the features of y
   const int64_t *cu = nullptr;
   float *states = nullptr;                 // (nb,H,128,128) fp32
-  float *gsum = nullptr;                   // (nb,H) fp32, optional
+  float *gsum = nullptr;                   // (nb,H) fp32 (scalar) / (nb,H,128) (vector), optional
   int B = 0, N = 0, H = 0, M = 0, reverse = 0;
   int ranges = 0;  // 1: cu holds M (begin, end) token ranges instead of M + 1 boundaries
 };
 int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream);
+int launch_state_pass_vec(const StatePass &p, int dtype, cudaStream_t stream);
+int launch_fold_states_vec(const float *local, const float *gsum, const int *seg, const int *emit, const float *ext,
+                           float *out, int nseg, int H, int D, int E, int reverse, cudaStream_t st);
 int launch_fold_states(const float *local, const float *gsum, const int *seg, const int *emit, const float *ext,
                        float *out, float *ends, int nseg, int H, int DE, int reverse, cudaStream_t st);
 

@@ -222,3 +222,73 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
     if want_ds0:
         ds0 = ds0.index_select(0, pl.first_idx)
     return dq, dk, dv, dld, ds0
+
+
+# --------------------------------------------------------------------------------------------
+# vector decay (ldk): the same scheme with a per-feature decay on the state's rows
+# --------------------------------------------------------------------------------------------
+def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool):
+    _, t, h, d = y.shape
+    e = z.shape[-1]
+    dev = y.device
+    fl = pl.flow[reverse]
+    n_loc = fl["n_loc"]
+    stream = _lib.stream_of(y)
+    incoming = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    local = torch.empty(max(n_loc, 1), h, d, e, dtype=torch.float32, device=dev)
+    gsum = torch.empty(max(n_loc, 1), h, d, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        if n_loc:
+            rc = lib.la_lavd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ldk), _lib.ptr(fl["ranges"]),
+                                        _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
+                                        _lib.dtype_code(y), 1 if reverse else 0, 1, stream)
+            _lib.check(rc, "la_lavd_state_pass")
+        rc = lib.la_lavd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(fl["table"]), _lib.ptr(fl["emit"]),
+                                     _lib.ptr(ext), _lib.ptr(incoming), fl["nunits"], h, d, e,
+                                     1 if reverse else 0, stream)
+        _lib.check(rc, "la_lavd_fold_states")
+    return incoming
+
+
+def lavd_forward_segmented(q, k, v, ldk, initial_state, doc_bounds, cap, flags):
+    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32, all contiguous.  Returns (o, final
+    states per document)."""
+    lib = _lib.load()
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    pl = _plan(doc_bounds, cap, dev, h)
+    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False)
+    o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
+    st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.la_lavd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ldk), None, _lib.ptr(s_in),
+                             _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
+                             _lib.dtype_code(q), flags, _lib.stream_of(q))
+        _lib.check(rc, "la_lavd_fwd (segmented)")
+    return o, st.index_select(0, pl.last_idx)
+
+
+def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_bounds, cap, want_ds0, flags):
+    """Backward twin.  Returns (dq, dk, dv, dldk (1,T,H,128) fp32, dinitial_state (ndocs,...) or None)."""
+    lib = _lib.load()
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    pl = _plan(doc_bounds, cap, dev, h)
+    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False)
+    ds_out = _incoming_states_vec(lib, q, do, ldk, pl, dfinal_state, reverse=True)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dldk = torch.empty(1, t, h, d, dtype=torch.float32, device=dev)
+    ds0 = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev) if want_ds0 else None
+    ws_bytes = lib.la_lavd_bwd_workspace_bytes(1, t, h, d, e, pl.nseg)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.la_lavd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ldk), None, _lib.ptr(s_in),
+                             _lib.ptr(do), _lib.ptr(ds_out), _lib.ptr(pl.cu_dev), _lib.ptr(dq), _lib.ptr(dk),
+                             _lib.ptr(dv), _lib.ptr(dldk), None, _lib.ptr(ds0), _lib.ptr(ws), ws_bytes, 1, t, h, d, e,
+                             pl.nseg, _lib.dtype_code(q), flags, _lib.stream_of(q))
+        _lib.check(rc, "la_lavd_bwd (segmented)")
+    if want_ds0:
+        ds0 = ds0.index_select(0, pl.first_idx)
+    return dq, dk, dv, dldk, ds0

@@ -29,6 +29,23 @@ def _ld32(x):
     return (x if x.dtype == torch.float32 else x.float()).contiguous()
 
 
+def _segmentation(lib, q, lk, lv, cu, b, n, h, d, e, flags):
+    """Few long sequences on the tensor path (ldk only, D = E = 128): cut every sequence into as many
+    segments as keep one CTA per (segment, head) within the SM count, so that the chunk passes fill
+    the GPU (xopes_b200/lightning_attn/segmented.py).  Returns (bounds, cap) or None."""
+    from . import segmented as sg
+    if cu is not None or lk is None or lv is not None or d != 128 or e != 128:
+        return None
+    if lib.la_lavd_path(n, d, e, _lib.dtype_code(q), 1, 0, flags) != 1:
+        return None
+    parts = sg.num_sms(q.device) // max(1, b * h)
+    if parts < 2 or n < 2 * 1024:
+        return None
+    parts = min(parts, n // 1024)
+    cap = -(-(-(-n // parts)) // 128) * 128
+    return [(i * n, (i + 1) * n) for i in range(b)], cap
+
+
 class LavdFunction(torch.autograd.Function):
     """forward(q, k, v, ldk, ldv, initial_state, cu_seqlens, flags) -> (o, final_state)."""
 
@@ -45,6 +62,19 @@ class LavdFunction(torch.autograd.Function):
         nb = m if cu is not None else b
         lk, lv = _ld32(ldk), _ld32(ldv)
         s0 = None if initial_state is None else initial_state.detach().to(torch.float32).contiguous()
+        seg = _segmentation(lib, q, lk, lv, cu, b, n, h, d, e, flags)
+        if seg is not None:
+            from .segmented import lavd_forward_segmented
+            bounds, cap = seg
+            o, sf = lavd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e),
+                                           lk.view(1, b * n, h, d), s0, bounds, cap, flags)
+            ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu)
+            ctx.flags = flags
+            ctx.seg = seg
+            ctx.state_dtype = None if initial_state is None else initial_state.dtype
+            ctx.set_materialize_grads(False)
+            return o.view(b, n, h, e), sf
+        ctx.seg = None
         o = torch.empty(b, n, h, e, dtype=q.dtype, device=q.device)
         sf = torch.empty(nb, h, d, e, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
@@ -72,6 +102,16 @@ class LavdFunction(torch.autograd.Function):
         dsf = None if dfinal_state is None else dfinal_state.to(torch.float32).contiguous()
         lk, lv = _ld32(ldk), _ld32(ldv)
         want_ds0 = s0 is not None and ctx.needs_input_grad[5]
+        if ctx.seg is not None:
+            from .segmented import lavd_backward_segmented
+            bounds, cap = ctx.seg
+            dq, dk, dv, dldk, ds0 = lavd_backward_segmented(
+                q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), lk.view(1, b * n, h, d), s0,
+                do.view(1, b * n, h, e), dsf, bounds, cap, want_ds0, ctx.flags)
+            if want_ds0:
+                ds0 = ds0.to(ctx.state_dtype)
+            return (dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e),
+                    dldk.view(b, n, h, d).to(ldk.dtype), None, ds0, None, None)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dldk = None if ldk is None else torch.empty(b, n, h, d, dtype=torch.float32, device=q.device)
         dldv = None if ldv is None else torch.empty(b, n, h, e, dtype=torch.float32, device=q.device)
