@@ -176,6 +176,7 @@ def pin(t):
 class LasdStep:
     """Configuration 2: forward + backward of lasd through the public API."""
     launches_per_step = 3  # o pass, dq pass, one launch for the dk and dv passes together
+    main_launches = 3      # launches of the dominant kernel among them
     kernel = "chunk_pass_kernel"
 
     def __init__(self, w, dev):
@@ -257,7 +258,11 @@ class LasdStep:
 
 
 class LavdStep(LasdStep):
-    launches_per_step = 4  # o, dq, dk, dv chunk passes (plus skipped fallback scans and one reverse cumsum)
+    # forward: state-only pass, fold, chunk pass, and two launches that only run if the decay leaves
+    # the range of the one before (two-reference chunk pass, scan); backward: 2 state-only passes,
+    # 2 folds, 3 chunk passes, 3 + 3 such conditional launches, 1 reverse cumulative sum
+    launches_per_step = 19
+    main_launches = 4      # o, dq, dk, dv chunk passes
     kernel = "lavd_pass_kernel"
 
     def _fb(self, d):
@@ -298,7 +303,7 @@ class DecodeStep:
         self.state = w["state"].to(dev).clone()
         self.host_toks = [{k: pin(v) for k, v in t.items()} for t in w["steps"]]
         self.toks = [{k: v.to(dev) for k, v in t.items()} for t in self.host_toks]
-        self.launches_per_step = len(self.toks)
+        self.launches_per_step = self.main_launches = len(self.toks)
         b, _, h, e = self.toks[0]["v"].shape
         self.o = torch.empty(len(self.toks), b, 1, h, e, dtype=torch.bfloat16, device=dev)
         self.h2d = sum(v.numel() * v.element_size() for t in self.host_toks for v in t.values())
@@ -356,7 +361,11 @@ class VarlenStep:
         self.d["ld"] = self.d["ld"].to(dev)
         self.cu_host = w["cu_seqlens"]
         self.cu = self.cu_host.to(dev)
-        self.launches_per_step = 1 if world == 1 else 2
+        # one GPU: per-document weight prefix + chunk pass; a rank: state-only pass, fold, weight
+        # prefix, chunk pass, the fold of the gathered summaries and the correction (NCCL's own
+        # kernel is not counted)
+        self.launches_per_step = 2 if world == 1 else 6
+        self.main_launches = 1
         self.last = None
 
     def _fwd(self, d):
@@ -632,7 +641,7 @@ def measure(name, args, rank, world, local, dev, primary):
     launches = runner.launches_per_step
     per_rank_bytes = alg_bytes / world if strong else alg_bytes
     per_rank_flops = flops / world if strong else flops
-    kern_launches = 1 if strong else launches  # C5: the varlen forward kernel on this rank's share
+    kern_launches = runner.main_launches
     per_launch_bytes = per_rank_bytes / kern_launches
     per_launch_s = ms_step * 1e-3 / kern_launches
     achieved = per_launch_bytes / per_launch_s / 1e9

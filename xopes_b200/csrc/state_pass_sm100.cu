@@ -351,11 +351,12 @@ namespace la {
 namespace {
 
 namespace vec {
-constexpr int kStagesV = 2;
-constexpr int kOffYZ = 0;                                  // 2 stages x (Y 32 KB + Z 32 KB)
-constexpr int kOffCk = kStagesV * 2 * kTileBytes;           // 64 KB fp32 decay tile
+constexpr int kStagesV = 1;                                 // Y and Z: one stage (the product that reads them is short)
+constexpr int kStagesCk = 2;                                // decay tile: two, the next one loads during this chunk's sums
+constexpr int kOffYZ = 0;                                  // Y 32 KB + Z 32 KB
+constexpr int kOffCk = kStagesV * 2 * kTileBytes;           // 2 x 64 KB fp32 decay tiles
 constexpr int kCkBytes = 65536;
-constexpr int kOffSeg = kOffCk + kCkBytes;                  // [8][128] segment totals
+constexpr int kOffSeg = kOffCk + kStagesCk * kCkBytes;      // [8][128] segment totals
 constexpr int kOffRun = kOffSeg + 8 * 128 * 4;              // [128] running per-feature log2 decay
 constexpr int kOffSmallV = kOffRun + 512;
 constexpr int kSmemBytesV = kOffSmallV + 1024;
@@ -364,7 +365,7 @@ constexpr int kThreadsV = kComputeV + 64;
 constexpr int kStFullV = 421, kStEmptyV = 422, kStYV = 423, kStDoneV = 424, kStAlignV = 433;
 
 struct SmallV {
-  unsigned long long full_ck, empty_ck, full_yz[kStagesV], empty_yz[kStagesV], bar_y[kStagesV], done;
+  unsigned long long full_ck[kStagesCk], empty_ck[kStagesCk], full_yz[kStagesV], empty_yz[kStagesV], bar_y[kStagesV], done;
   uint32_t tmem_base;
   int abort_flag;
   int issued_ck, issued_yz;
@@ -409,13 +410,15 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
   const int nc = (len + kChunk - 1) / kChunk;
   const bool back = a.reverse == 0;
 
-  const uint32_t full_ck = smem_u32(&sm->full_ck), empty_ck = smem_u32(&sm->empty_ck);
+  const uint32_t full_ck = smem_u32(&sm->full_ck[0]), empty_ck = smem_u32(&sm->empty_ck[0]);
   const uint32_t full_yz = smem_u32(&sm->full_yz[0]), empty_yz = smem_u32(&sm->empty_yz[0]);
   const uint32_t bar_y = smem_u32(&sm->bar_y[0]), bar_done = smem_u32(&sm->done);
   volatile int *abort_flag = &sm->abort_flag;
   if (tid == 0) {
-    mbar_init(full_ck, 1);
-    mbar_init(empty_ck, kComputeV);
+    for (int s = 0; s < kStagesCk; ++s) {
+      mbar_init(full_ck + 8 * s, 1);
+      mbar_init(empty_ck + 8 * s, kComputeV);
+    }
     for (int s = 0; s < kStagesV; ++s) {
       mbar_init(full_yz + 8 * s, 1);
       mbar_init(empty_yz + 8 * s, 1);
@@ -442,13 +445,16 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
       for (int it = 0; it < nc; ++it) {
         const int n = back ? (nc - 1 - it) : it;
         const int s = it % kStagesV;
-        const uint32_t ph = (uint32_t)(it / kStagesV) & 1u, par = (uint32_t)it & 1u;
+        const uint32_t ph = (uint32_t)(it / kStagesV) & 1u;
+        const int sc = it % kStagesCk;
+        const uint32_t phc = (uint32_t)(it / kStagesCk) & 1u;
         const int tok0 = (int)t_begin + n * kChunk;
-        mbar_wait(empty_ck, par ^ 1u, abort_flag, a.status, kStEmptyV);
+        mbar_wait(empty_ck + 8 * sc, phc ^ 1u, abort_flag, a.status, kStEmptyV);
         if (*abort_flag) break;
-        mbar_arrive_expect_tx(full_ck, kCkBytes);
+        mbar_arrive_expect_tx(full_ck + 8 * sc, kCkBytes);
 #pragma unroll
-        for (int gq = 0; gq < 4; ++gq) tma_load_4d(base + kOffCk + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+        for (int gq = 0; gq < 4; ++gq)
+          tma_load_4d(base + kOffCk + sc * kCkBytes + gq * kBoxBytes, &map_ld, full_ck + 8 * sc, 32 * gq, h, tok0, bidx);
         n_ck = it + 1;
         mbar_wait(empty_yz + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmptyV);
         if (*abort_flag) break;
@@ -487,7 +493,6 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
     // ------------------------------------------------------------------ compute warps
     const int wg = warp >> 2, q4 = warp & 3;
     const int i = q4 * 32 + lane;  // row for the scaling phase
-    uint8_t *ck = gbase + kOffCk;
     float *segtot = reinterpret_cast<float *>(gbase + kOffSeg);
     float *run = reinterpret_cast<float *>(gbase + kOffRun);
     if (tid < kChunk) run[tid] = 0.f;
@@ -495,9 +500,12 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
     for (int it = 0; it < nc; ++it) {
       const int n = back ? (nc - 1 - it) : it;
       const int s = it % kStagesV;
-      const uint32_t ph = (uint32_t)(it / kStagesV) & 1u, par = (uint32_t)it & 1u;
+      const uint32_t ph = (uint32_t)(it / kStagesV) & 1u;
+      const int sc = it % kStagesCk;
+      const uint32_t phc = (uint32_t)(it / kStagesCk) & 1u;
+      uint8_t *ck = gbase + kOffCk + sc * kCkBytes;
       const int L = min(kChunk, len - n * kChunk);
-      mbar_wait(full_ck, par, abort_flag, a.status, kStFullV);
+      mbar_wait(full_ck + 8 * sc, phc, abort_flag, a.status, kStFullV);
       {
         const int dg = tid & 31, seg = tid >> 5, d0 = dg * 4;
         const uint32_t colbase = (uint32_t)(d0 >> 5) * kBoxBytes;
@@ -562,7 +570,7 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
       }
       fence_proxy_async();
       mbar_arrive(bar_y + 8 * s);
-      mbar_arrive(empty_ck);
+      mbar_arrive(empty_ck + 8 * sc);
     }
     // the state -> global memory; this warpgroup's 64 columns of row i
     if (nc > 0) mbar_wait(bar_done, 0, abort_flag, a.status, kStDoneV);
@@ -594,7 +602,8 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
   if (warp == 8) {
     if (lane == 0 && sm->abort_flag != 0) {
       int dummy = 0;
-      if (sm->issued_ck > 0) mbar_wait(full_ck, (uint32_t)(sm->issued_ck - 1) & 1u, &dummy, nullptr, 0, 1u << 20);
+      for (int it = max(0, sm->issued_ck - kStagesCk); it < sm->issued_ck; ++it)
+        mbar_wait(full_ck + 8 * (it % kStagesCk), (uint32_t)(it / kStagesCk) & 1u, &dummy, nullptr, 0, 1u << 20);
       for (int it = max(0, sm->issued_yz - kStagesV); it < sm->issued_yz; ++it)
         mbar_wait(full_yz + 8 * (it % kStagesV), (uint32_t)(it / kStagesV) & 1u, &dummy, nullptr, 0, 1u << 20);
     }
