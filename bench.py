@@ -679,6 +679,31 @@ def measure(name, args, rank, world, local, dev, primary):
     return res, cfg
 
 
+def measure_lasd_shape(b, n, h, dev, steps, world, seed=0):
+    """Forward and forward+backward ms of lasd (bf16, D = E = 128, per-head decay, initial state)
+    for one (B, N, H); the maximum over ranks."""
+    import xopes_b200 as xb
+    from xopes_b200 import workloads as W
+    w = W.lasd_inputs(b, n, h, 128, 128, torch.bfloat16, seed)
+    d = {k: v.to(dev) for k, v in w.items()}
+    q, k, v = (d[x].requires_grad_() for x in ("q", "k", "v"))
+
+    def fwd():
+        with torch.no_grad():
+            xb.lasd_fn(q, k, v, d["ld"], initial_state=d["initial_state"])
+
+    def fb():
+        o, _ = xb.lasd_fn(q, k, v, d["ld"], initial_state=d["initial_state"])
+        o.backward(d["do"])
+        q.grad = k.grad = v.grad = None
+
+    ms_f, _ = time_steps(fwd, steps, 3, world)
+    ms_fb, _ = time_steps(fb, steps, 3, world)
+    del d, w
+    torch.cuda.empty_cache()
+    return ms_f / steps, ms_fb / steps
+
+
 def measure_c5_single_gpu(args, rank, world, dev):
     """The whole configuration-5 stream on rank 0's GPU alone (the other ranks wait), so that a
     multi-GPU line carries the one-GPU time it is compared with."""
@@ -733,6 +758,25 @@ def main():
             r, _ = measure(name, args, rank, world, local, dev, primary=False)
             r.pop("e2e", None)
             secondary[name] = r
+        steps2 = max(3, min(args.steps, 10))
+        # the reference's few-pair benchmark row (benchmarks/lightning_attention/README.md:112,123:
+        # lasd_p B1 H16 D128 N32768, 1.222 ms forward / 4.174 ms backward on A100): few (sequence,
+        # head) pairs, served by the segmented passes
+        f, fb = measure_lasd_shape(1, 32768, 16, dev, steps2, world)
+        secondary["lasd_B1_N32768_H16"] = {
+            "fwd_ms": f, "bwd_ms": fb - f, "fwd_bwd_ms": fb,
+            "reference_published_A100_ms": {"fwd": 1.2220, "bwd": 4.1736,
+                                            "source": "benchmarks/lightning_attention/README.md:112,123"}}
+        # configuration 2 partitioned by batch x head over the ranks (strong scaling): every rank
+        # takes B / N of the batches of the same global problem
+        if cfg["B"] % world == 0:
+            f, fb = measure_lasd_shape(cfg["B"] // world, cfg["N"], cfg["H"], dev, steps2, world, seed=rank)
+            secondary["C2_strong"] = {
+                "scaling": "strong", "batches_per_rank": cfg["B"] // world, "fwd_bwd_ms": fb,
+                "value": cfg["B"] * cfg["N"] / (fb * 1e-3), "unit": "tokens/s",
+                # the headline step is one full batch on one GPU (every rank runs one), so this is
+                # the strong-scaling speed-up of the same global problem
+                "speedup_over_full_batch_on_one_gpu": res["ms_per_step"] / fb}
         if world > 1:
             one = measure_c5_single_gpu(args, rank, world, dev)
             if rank == 0:

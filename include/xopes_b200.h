@@ -285,6 +285,26 @@ LA_API int la_decode_vector(const void *q, const void *k, const void *v, const f
                      const float *ldv, const float *state_in, float *state_out, void *o,
                      int64_t B, int64_t H, int64_t D, int64_t E, int dtype, void *stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Fused normalisation + gate: the op that follows lightning attention in a model block.  Stands in
+ * for normalize_torch / normalize_triton with a gate and no residual
+ * (xopes/ops/normalize/normalize/normalize_torch.py:9-111):
+ *     a = act(gate);  z = x*a (gate_pos 0 = pre) or x;  zc = z - mean(z) if use_mean;
+ *     y = c * zc / sqrt(sum zc^2 + eps) * weight + bias   per group of e features;
+ *     o = y (pre / no gate) or y*a (gate_pos 1 = post).
+ * x, gate, out, d_out, dx, dgate are (rows, G*e) in `dtype`, contiguous; gate may be NULL (plain
+ * normalisation); weight, bias are fp32 (G*e) or NULL; act: 0 none, 1 relu, 2 sigmoid, 3 silu.
+ * e must be a multiple of 4 and at most 512.  dweight / dbias (fp32, G*e, or NULL) are ACCUMULATED
+ * into: zero them first.  One pass over the inputs each way, fp32 arithmetic.
+ * ------------------------------------------------------------------------------------------- */
+LA_API int la_normalize_gate_fwd(const void *x, const void *gate, const float *weight, const float *bias,
+                                 void *out, int64_t rows, int64_t G, int64_t e, int dtype, int act,
+                                 int gate_pos, float c, float eps, int use_mean, void *stream);
+LA_API int la_normalize_gate_bwd(const void *x, const void *gate, const float *weight, const float *bias,
+                                 const void *d_out, void *dx, void *dgate, float *dweight, float *dbias,
+                                 int64_t rows, int64_t G, int64_t e, int dtype, int act, int gate_pos,
+                                 float c, float eps, int use_mean, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -194,6 +194,59 @@ def chunk_fixture_case(ref_root, name, seed, b, n, h, d, e, block):
     save(name, **out)
 
 
+def normgate_case(ref_root, name, seed):
+    """Outputs and autograd gradients of the reference's normalize_torch with a gate
+    (xopes/ops/normalize/normalize/normalize_torch.py) for every activation, both gate positions,
+    with and without mean subtraction.  The file imports act_torch from the xopes package (not
+    importable without a GPU); the activation table it needs is loaded by path from
+    xopes/ops/act/_act_torch/act_torch.py and offered under that module name."""
+    import types
+    from oracle import normalize_oracle as norc
+    acts = load(ref_root, "xopes/ops/act/_act_torch/act_torch.py", "ref_act_table")
+    stub = types.ModuleType("xopes.ops.act")
+    stub.act_torch = lambda x, act, dim=None: acts.ACT_TORCH_DICT[act](x)
+    names = ("xopes", "xopes.ops", "xopes.ops.act")
+    saved = {m: sys.modules.get(m) for m in names}
+    sys.modules["xopes"], sys.modules["xopes.ops"] = types.ModuleType("xopes"), types.ModuleType("xopes.ops")
+    sys.modules["xopes.ops.act"] = stub
+    try:
+        nt = load(ref_root, "xopes/ops/normalize/normalize/normalize_torch.py", "ref_normalize_torch")
+    finally:
+        for m, old in saved.items():
+            if old is None:
+                sys.modules.pop(m, None)
+            else:
+                sys.modules[m] = old
+    gen = torch.Generator().manual_seed(seed)
+    rows, groups, e = 7, 3, 40
+    out = {}
+    x = g((2, rows, groups * e), gen)
+    gate = g((2, rows, groups * e), gen)
+    w = 1 + 0.1 * g((groups * e,), gen)
+    b = 0.1 * g((groups * e,), gen)
+    do = g((2, rows, groups * e), gen)
+    out.update(x=x, gate=gate, weight=w, bias=b, do=do, num_groups=torch.tensor(groups))
+    idx = 0
+    for act in ("none", "relu", "sigmoid", "silu"):
+        for pos in ("pre", "post"):
+            for use_mean in (False, True):
+                xs, gs, ws, bs = (t.clone().requires_grad_() for t in (x, gate, w, b))
+                o = nt.normalize_torch(xs, ws, bs, gate=gs, gate_act=act, gate_pos=pos, c=e ** 0.5, eps=1e-5,
+                                       use_mean=use_mean, num_groups=groups)
+                grads = torch.autograd.grad((o * do).sum(), [xs, gs, ws, bs])
+                xo, go, wo, bo = (t.clone().requires_grad_() for t in (x, gate, w, b))
+                oo = norc.normalize_gate(xo, wo, bo, go, act, pos, e ** 0.5, 1e-5, use_mean, groups)
+                og = torch.autograd.grad((oo * do.double()).sum(), [xo, go, wo, bo])
+                tag = f"{act}_{pos}_{int(use_mean)}"
+                check(f"{name}.{tag}.o", o, oo.float())
+                for nme, r, got in zip(("dx", "dgate", "dweight", "dbias"), grads, og):
+                    check(f"{name}.{tag}.{nme}", r, got.float())
+                    out[f"{tag}.{nme}"] = r
+                out[f"{tag}.o"] = o
+                idx += 1
+    save(name, **out)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("XOPES_REFERENCE_ROOT")
     if not ref_root:
@@ -211,6 +264,7 @@ def main():
     lasd_case(lasd, "lasd_decode", 16, 3, 1, 4, 64, 48, True, True)
     # chunk-level intermediates (ragged last chunk)
     chunk_fixture_case(ref_root, "chunkfx_lasd", 17, 1, 300, 2, 16, 24, 128)
+    normgate_case(ref_root, "normgate", 18)
     # vector decay
     lavd_case(lavd, "lavd_k_only", 21, 2, 41, 2, 16, 24, False, True, True)
     lavd_case(lavd, "lavd_kv", 22, 2, 35, 2, 24, 16, True, True, True)

@@ -69,3 +69,23 @@ def test_chunk_fixture_oracle_matches_reference_vectors():
     # the pieces add up: intra + inter is the full forward
     o, _ = orc.lasd_forward(q, k, v, ld, s0)
     assert_close("intra + inter", o, g["intra_fwd"] + g["inter"], TOL_FP32)
+
+
+def test_normalize_gate_oracle_matches_reference_vectors():
+    """oracle/normalize_oracle.py against outputs and autograd gradients of the reference's
+    normalize_torch with a gate (every activation, both gate positions, with / without mean)."""
+    import torch
+    from oracle import normalize_oracle as norc
+    g = load_golden("normgate")
+    groups = int(g["num_groups"])
+    e = g["x"].shape[-1] // groups
+    for act in ("none", "relu", "sigmoid", "silu"):
+        for pos in ("pre", "post"):
+            for use_mean in (False, True):
+                x, gate, w, b = (g[n].clone().requires_grad_() for n in ("x", "gate", "weight", "bias"))
+                o = norc.normalize_gate(x, w, b, gate, act, pos, e ** 0.5, 1e-5, use_mean, groups)
+                grads = torch.autograd.grad((o * g["do"].double()).sum(), [x, gate, w, b])
+                tag = f"{act}_{pos}_{int(use_mean)}"
+                assert_close(tag + ".o", g[tag + ".o"], o.float(), TOL_FP32)
+                for n, got in zip(("dx", "dgate", "dweight", "dbias"), grads):
+                    assert_close(f"{tag}.{n}", g[f"{tag}.{n}"], got.float(), TOL_FP32)

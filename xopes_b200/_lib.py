@@ -17,7 +17,7 @@ FLAG_REQUIRE_TENSOR = 2
 
 _DTYPES = {torch.float32: LA_F32, torch.bfloat16: LA_BF16, torch.float16: LA_F16}
 
-_vp, _i64, _i32, _u32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint
+_vp, _i64, _i32, _u32, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint, ctypes.c_float
 
 # name -> (restype, argtypes); mirrors include/xopes_b200.h one to one
 SIGNATURES = {
@@ -54,6 +54,10 @@ SIGNATURES = {
     "la_seqpar_fold_segments": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_correct_multi": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_seqpar_correct": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp]),
+    "la_normalize_gate_fwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _f32,
+                                     _i32, _vp]),
+    "la_normalize_gate_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32,
+                                     _i32, _f32, _f32, _i32, _vp]),
     "la_decode_scalar": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp,
                                 _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_decode_vector": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

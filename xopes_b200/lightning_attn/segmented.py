@@ -139,8 +139,9 @@ def _plan(doc_bounds, cap, dev, h) -> _Plan:
     if p is None:
         if len(_PLANS) >= 64:
             _PLANS.clear()
-        # about four state-pass pieces per SM: enough to fill the GPU and hide each CTA's ramp-up
-        p = _PLANS[key] = _Plan(doc_bounds, cap, dev, max(1, 4 * num_sms(dev) // max(1, h)))
+        # about one state-pass piece per SM: one wave fills the GPU, and every piece costs a CTA
+        # ramp-up, 64 KB of state and one step of the fold
+        p = _PLANS[key] = _Plan(doc_bounds, cap, dev, max(1, num_sms(dev) // max(1, h)))
     return p
 
 
