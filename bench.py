@@ -613,6 +613,12 @@ def measure(name, args, rank, world, local, dev, primary):
     """Times one configuration; returns the dict of its figures (on every rank)."""
     steps = args.steps if primary else max(3, min(args.steps, 10))
     warmup = max(args.warmup, 3)
+    # The parity figures of the previous workload ran the CPU oracle on several threads; their
+    # worker threads keep spinning for a while after the last parallel region and would compete
+    # with this process's launch thread (the multi-rank C5 step is a few hundred microseconds of
+    # many small launches).  One thread from here on, and a pause for the pool to go to sleep.
+    torch.set_num_threads(1)
+    time.sleep(0.5)
     cfg, w, tokens, alg_bytes, flops = make_workload(name, rank, world, dev, args.shape if primary else None)
     runner = make_runner(name, cfg, w, dev, world, rank)
     strong = name == "C5"
@@ -730,6 +736,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=["C2", "C3", "C4", "C4v", "C5"],
                     help="time this configuration only (default: C2 as the headline, the rest under `secondary`)")
     ap.add_argument("--no-secondary", action="store_true")
+    ap.add_argument("--secondary", default="C3,C4,C4v,C5,rows",
+                    help="which of the secondary measurements to take (comma-separated)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -754,7 +762,10 @@ def main():
     res, cfg = measure(args.workload, args, rank, world, local, dev, primary=True)
     secondary = {}
     if not only and not args.no_secondary and args.shape is None:
+        want = [x for x in args.secondary.split(",") if x]
         for name in ("C3", "C4", "C4v", "C5"):
+            if name not in want:
+                continue
             r, _ = measure(name, args, rank, world, local, dev, primary=False)
             r.pop("e2e", None)
             secondary[name] = r
@@ -762,14 +773,15 @@ def main():
         # the reference's few-pair benchmark row (benchmarks/lightning_attention/README.md:112,123:
         # lasd_p B1 H16 D128 N32768, 1.222 ms forward / 4.174 ms backward on A100): few (sequence,
         # head) pairs, served by the segmented passes
-        f, fb = measure_lasd_shape(1, 32768, 16, dev, steps2, world)
-        secondary["lasd_B1_N32768_H16"] = {
-            "fwd_ms": f, "bwd_ms": fb - f, "fwd_bwd_ms": fb,
-            "reference_published_A100_ms": {"fwd": 1.2220, "bwd": 4.1736,
-                                            "source": "benchmarks/lightning_attention/README.md:112,123"}}
+        f, fb = measure_lasd_shape(1, 32768, 16, dev, steps2, world) if "rows" in want else (None, None)
+        if f is not None:
+            secondary["lasd_B1_N32768_H16"] = {
+                "fwd_ms": f, "bwd_ms": fb - f, "fwd_bwd_ms": fb,
+                "reference_published_A100_ms": {"fwd": 1.2220, "bwd": 4.1736,
+                                                "source": "benchmarks/lightning_attention/README.md:112,123"}}
         # configuration 2 partitioned by batch x head over the ranks (strong scaling): every rank
         # takes B / N of the batches of the same global problem
-        if cfg["B"] % world == 0:
+        if cfg["B"] % world == 0 and "rows" in want:
             f, fb = measure_lasd_shape(cfg["B"] // world, cfg["N"], cfg["H"], dev, steps2, world, seed=rank)
             secondary["C2_strong"] = {
                 "scaling": "strong", "batches_per_rank": cfg["B"] // world, "fwd_bwd_ms": fb,
@@ -777,7 +789,7 @@ def main():
                 # the headline step is one full batch on one GPU (every rank runs one), so this is
                 # the strong-scaling speed-up of the same global problem
                 "speedup_over_full_batch_on_one_gpu": res["ms_per_step"] / fb}
-        if world > 1:
+        if world > 1 and "C5" in secondary:
             one = measure_c5_single_gpu(args, rank, world, dev)
             if rank == 0:
                 secondary["C5"]["single_gpu_ms_per_step_same_job"] = one
