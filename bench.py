@@ -407,6 +407,15 @@ class VarlenStep:
                 "document_tokens_before_this_rank": max(0, start - a)}
 
 
+def quiet_cpu():
+    """The parity figures of the previous workload ran the CPU oracle on several threads; their
+    worker threads keep spinning for a while after the last parallel region and would compete with
+    this process's launch thread (the multi-rank C5 step is a few hundred microseconds of many small
+    launches).  One thread from here on, and a pause for the pool to go to sleep."""
+    torch.set_num_threads(1)
+    time.sleep(0.5)
+
+
 def time_steps(fn, steps, warmup, world, sampler=None, drain=None):
     import torch.distributed as dist
     for _ in range(warmup):
@@ -613,12 +622,7 @@ def measure(name, args, rank, world, local, dev, primary):
     """Times one configuration; returns the dict of its figures (on every rank)."""
     steps = args.steps if primary else max(3, min(args.steps, 10))
     warmup = max(args.warmup, 3)
-    # The parity figures of the previous workload ran the CPU oracle on several threads; their
-    # worker threads keep spinning for a while after the last parallel region and would compete
-    # with this process's launch thread (the multi-rank C5 step is a few hundred microseconds of
-    # many small launches).  One thread from here on, and a pause for the pool to go to sleep.
-    torch.set_num_threads(1)
-    time.sleep(0.5)
+    quiet_cpu()
     cfg, w, tokens, alg_bytes, flops = make_workload(name, rank, world, dev, args.shape if primary else None)
     runner = make_runner(name, cfg, w, dev, world, rank)
     strong = name == "C5"
@@ -690,6 +694,7 @@ def measure_lasd_shape(b, n, h, dev, steps, world, seed=0):
     for one (B, N, H); the maximum over ranks."""
     import xopes_b200 as xb
     from xopes_b200 import workloads as W
+    quiet_cpu()
     w = W.lasd_inputs(b, n, h, 128, 128, torch.bfloat16, seed)
     d = {k: v.to(dev) for k, v in w.items()}
     q, k, v = (d[x].requires_grad_() for x in ("q", "k", "v"))
@@ -715,6 +720,7 @@ def measure_c5_single_gpu(args, rank, world, dev):
     multi-GPU line carries the one-GPU time it is compared with."""
     import torch.distributed as dist
     ms_step = None
+    quiet_cpu()
     if rank == 0:
         steps = max(3, min(args.steps, 10))
         cfg, w, tokens, _, _ = make_workload("C5", 0, 1, dev)
