@@ -50,6 +50,12 @@ enum la_dtype { LA_F32 = 0, LA_BF16 = 1, LA_F16 = 2 };
 /* flags for the lasd/lavd entry points */
 #define LA_FLAG_FORCE_RECURRENCE 1u /* never take the tcgen05 chunk kernels                       */
 #define LA_FLAG_REQUIRE_TENSOR 2u   /* fail with LA_ERR_UNSUPPORTED instead of taking the scan     */
+/* The decay tensors (ld; ldk, ldv) hold PRE-ACTIVATIONS x and the log decay is logsigmoid(x), the
+ * usual producer of these decays (benchmarks/lightning_attention/benchmark.py:308-317): the
+ * kernels apply it where they read the decay, and the backward returns d/dx in dld / dldk / dldv
+ * (the chain-rule factor sigmoid(-x) is applied where the log-decay gradient is finished).  Saves
+ * the producer's pass over the decay tensor and the elementwise pass of its backward. */
+#define LA_FLAG_LD_LOGSIGMOID 4u
 
 /* Library identification; bumps when the ABI changes. */
 LA_API int la_abi_version(void);
@@ -199,7 +205,7 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
  * (state at the sequence's end, forward flow: (y,z) = (k,v) gives S, (v,k) gives S^T);
  * reverse = 1: w_j = exp(sum of ld up to and including token j) (state at the sequence's start for
  * the backward recurrences: (q,do) gives dS, (do,q) gives dS^T).  y, z are (B,N,H,128) 16-bit; ld as
- * in la_lasd_fwd; with cu_seqlens the "sequences" are its M segments (ranges = 0: M + 1 boundaries;
+ * in la_lasd_fwd (flags: LA_FLAG_LD_LOGSIGMOID only); with cu_seqlens the "sequences" are its M segments (ranges = 0: M + 1 boundaries;
  * ranges = 1: M explicit (begin, end) token pairs, so that a subset of segments can be given).
  * Reads 512 B per token and head.  D = E = 128, 16-bit only.
  *
@@ -216,7 +222,7 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
 LA_API int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld_sb,
                               int64_t ld_sn, int64_t ld_sh, const int64_t *cu_seqlens, float *states,
                               float *gsum, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
-                              int64_t M, int dtype, int reverse, int ranges, void *stream);
+                              int64_t M, int dtype, int reverse, int ranges, unsigned flags, void *stream);
 LA_API int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *seg_table,
                                const int32_t *emit, const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H,
                                int64_t D, int64_t E, int reverse, void *stream);
@@ -230,7 +236,8 @@ LA_API int la_lasd_fold_states(const float *local, const float *gsum, const int3
  * reference (its chunk-level states live in HBM, vector_decay/lavd_parallel_triton.py:25-316). */
 LA_API int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int64_t *cu_seqlens,
                               float *states, float *gsum, int64_t B, int64_t N, int64_t H, int64_t D,
-                              int64_t E, int64_t M, int dtype, int reverse, int ranges, void *stream);
+                              int64_t E, int64_t M, int dtype, int reverse, int ranges, unsigned flags,
+                              void *stream);
 LA_API int la_lavd_fold_states(const float *local, const float *gsum, const int32_t *seg_table,
                                const int32_t *emit, const float *ext, float *incoming, int64_t nseg,
                                int64_t H, int64_t D, int64_t E, int reverse, void *stream);

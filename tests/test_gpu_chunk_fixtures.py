@@ -48,7 +48,7 @@ def test_local_and_scanned_states(lib):
         gsum = torch.empty(L, h, device=dev)
         assert lib.la_lasd_state_pass(kc.data_ptr(), vc.data_ptr(), ldc.data_ptr(), 0, h, 1, cu.data_ptr(),
                                       local.data_ptr(), gsum.data_ptr(), 1, n, h, d, d, L, _lib.LA_BF16, reverse, 0,
-                                      stream) == 0
+                                      0, stream) == 0
         inc, ends = torch.empty_like(local), torch.empty_like(local)
         assert lib.la_lasd_fold_states(local.data_ptr(), gsum.data_ptr(), tab.data_ptr(), None, s0.to(dev).data_ptr(),
                                        inc.data_ptr(), ends.data_ptr(), L, h, d, d, reverse, stream) == 0

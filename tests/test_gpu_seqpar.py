@@ -161,7 +161,7 @@ def test_state_pass_and_fold_match_the_oracle(lib):
         gsum = torch.empty(len(segs), h, device=dev)
         rc = lib.la_lasd_state_pass(y.data_ptr(), z.data_ptr(), ldc.data_ptr(), 0, h, 1, ranges.data_ptr(),
                                     states.data_ptr(), gsum.data_ptr(), 1, n, h, d, d, len(segs), _lib.LA_BF16,
-                                    reverse, 1, stream)
+                                    reverse, 1, 0, stream)
         assert rc == 0
         for j, (a, b) in enumerate(segs):
             sl = slice(a, b)
@@ -212,7 +212,7 @@ def test_vector_decay_state_pass_and_fold(lib, regime):
         states = torch.empty(len(segs), h, d, d, device=dev)
         gsum = torch.empty(len(segs), h, d, device=dev)
         assert lib.la_lavd_state_pass(y.data_ptr(), z.data_ptr(), lc.data_ptr(), ranges.data_ptr(), states.data_ptr(),
-                                      gsum.data_ptr(), 1, n, h, d, d, len(segs), _lib.LA_BF16, reverse, 1, stream) == 0
+                                      gsum.data_ptr(), 1, n, h, d, d, len(segs), _lib.LA_BF16, reverse, 1, 0, stream) == 0
         for j, (a, b) in enumerate(segs):
             sl = slice(a, b)
             if reverse == 0:

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libxopes_b200.so")
 LA_F32, LA_BF16, LA_F16 = 0, 1, 2
 FLAG_FORCE_RECURRENCE = 1
 FLAG_REQUIRE_TENSOR = 2
+FLAG_LD_LOGSIGMOID = 4
 
 _DTYPES = {torch.float32: LA_F32, torch.bfloat16: LA_BF16, torch.float16: LA_F16}
 
@@ -45,10 +46,10 @@ SIGNATURES = {
     "la_lavd_bwd": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                            _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _vp]),
     "la_lasd_state_pass": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp, _vp,
-                                  _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
+                                  _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _u32, _vp]),
     "la_lasd_fold_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_lavd_state_pass": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i32, _i32,
-                                  _i32, _vp]),
+                                  _i32, _u32, _vp]),
     "la_lavd_fold_states": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp]),
     "la_seqpar_fold": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     "la_seqpar_fold_segments": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),

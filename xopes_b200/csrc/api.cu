@@ -138,9 +138,10 @@ void rows_d(ScanParams &p, const Seq &s, const float *ldk, const float *ldv) {
 int scan_forward(const Seq &s, const void *q, const void *k, const void *v, const float *ld,
                  int64_t sb, int64_t sn, int64_t sh, const float *ldk, const float *ldv,
                  const float *s0, void *o, float *sfin, int dtype, cudaStream_t st,
-                 const int *enable = nullptr) {
+                 const int *enable = nullptr, int ld_act = 0) {
   ScanParams p = base_params(s, ld, sb, sn, sh);
   p.enable = enable;
+  p.ld_act = ld_act;
   rows_e(p, s, ldk, ldv);
   p.a = v; p.b = k; p.w = q; p.out = o; p.t0 = s0; p.tfinal = sfin;
   return launch_scan(p, dtype, st);
@@ -238,10 +239,11 @@ int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, in
     c.t0 = initial_state; c.tfinal = final_state; c.state_transposed = 0; c.reverse = 0;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens;
     c.fx = s.D; c.fz = s.E;
+    c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
     return launch_chunk_pass(c, dtype, st);
   }
   return scan_forward(s, q, k, v, ld, ld_sb, ld_sn, ld_sh, nullptr, nullptr, initial_state, o,
-                      final_state, dtype, st);
+                      final_state, dtype, st, nullptr, (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0);
 }
 
 // Workspace layout: [recomputed final state, rounded up to 16 bytes][row dots of q.dq][row dots of
@@ -288,9 +290,11 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     slots_k = slots_q + (int64_t)nt * bnh;
   }
   const bool state_term = want_dld && dfinal_state != nullptr;
+  const int ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
 
   if (path == 1) {
     ChunkPass c;
+    c.ld_act = ld_act;
     c.ld = ld; c.ld_sb = ld_sb; c.ld_sn = ld_sn; c.ld_sh = ld_sh;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.no_scratch = no_scratch;
     // dq: (X,Y,Z) = (do, v, k), state S^T, forward direction
@@ -328,6 +332,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
   } else {
     // dq: T = S (rows D): a = k, b = v, w = do
     ScanParams p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    p.ld_act = ld_act;
     rows_d(p, s, nullptr, nullptr);
     p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state;
     p.tfinal = state_term ? ws_state : nullptr;
@@ -335,6 +340,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
     // dk: T = dS (rows D), reverse: a = q, b = do, w = v
     p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    p.ld_act = ld_act;
     rows_d(p, s, nullptr, nullptr);
     p.reverse = 1;
     p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
@@ -342,6 +348,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
     if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
     // dv: T = dS^T (rows E), reverse: a = do, b = q, w = k
     p = base_params(s, ld, ld_sb, ld_sn, ld_sh);
+    p.ld_act = ld_act;
     rows_e(p, s, nullptr, nullptr);
     p.reverse = 1;
     p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;
@@ -349,7 +356,8 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
   }
   if (want_dld) {
     rc = launch_dld_scalar(slots_q, nt, slots_k, nt, state_term ? ws_state : nullptr,
-                           dfinal_state, cu_seqlens, dld, s.B, s.N, s.H, s.D * s.E, s.M, st);
+                           dfinal_state, cu_seqlens, dld, s.B, s.N, s.H, s.D * s.E, s.M, st,
+                           ld_act ? ld : nullptr, ld_sb, ld_sn, ld_sh);
     if (rc != LA_OK) return rc;
   }
   return LA_OK;
@@ -434,6 +442,7 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
     LavdPass c;
     c.x = q; c.y = k; c.z = v; c.ldk = ldk; c.out = o; c.t0 = initial_state; c.tfinal = final_state;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
+    c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
     if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
     // the two-reference kernels run only if a chunk left the one-reference range ...
     c.ref2 = 1; c.enable = unsafe; c.unsafe = unsafe + 1;
@@ -441,7 +450,7 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
     enable = unsafe + 1;  // ... and the scan below only if one left theirs too
   }
   return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype, st,
-                      enable);
+                      enable, (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0);
 }
 
 int64_t la_lavd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
@@ -478,6 +487,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     if (unsafe == nullptr) return LA_ERR_CUDA;
     if (cudaMemsetAsync(unsafe, 0, 2 * sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
+    c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
     // with the other two passes, so while one CTA per (sequence, head) leaves SMs idle it runs
@@ -546,11 +556,13 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     enable = unsafe + 1;
   }
   ScanParams p;
+  const int ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
   if (ldv != nullptr) {
     // recompute o only to form o*do for dldv (the reference's optional dldv_o pass,
     // vector_decay/lavd_parallel_triton.py:1104-1127)
     p = base_params(s, nullptr, 0, 0, 0);
-  p.enable = enable;
+    p.enable = enable;
+    p.ld_act = ld_act;
     rows_e(p, s, ldk, ldv);
     p.a = v; p.b = k; p.w = q; p.out = nullptr; p.t0 = initial_state;
     p.x = d_o; p.xout = dldv; p.xmode = 2;
@@ -559,6 +571,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   // dq
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
+  p.ld_act = ld_act;
   rows_d(p, s, ldk, ldv);
   p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state; p.tfinal = ws_state;
   if (ldk != nullptr) { p.x = q; p.xout = dldk; p.xmode = 2; }
@@ -566,6 +579,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   // dk
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
+  p.ld_act = ld_act;
   rows_d(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
@@ -574,6 +588,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   // dv
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
+  p.ld_act = ld_act;
   rows_e(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;
@@ -581,12 +596,12 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
   if (ldk != nullptr) {
     rc = launch_revcumsum_vec(dldk, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.D, s.D,
-                              s.E, 1, s.M, st);
+                              s.E, 1, s.M, st, ld_act ? ldk : nullptr);
     if (rc != LA_OK) return rc;
   }
   if (ldv != nullptr) {
     rc = launch_revcumsum_vec(dldv, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.E, s.D,
-                              s.E, 0, s.M, st);
+                              s.E, 0, s.M, st, ld_act ? ldv : nullptr);
     if (rc != LA_OK) return rc;
   }
   return LA_OK;
@@ -628,7 +643,8 @@ int la_seqpar_correct_multi(const void *q, void *o, const float *cum, const floa
 
 int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld_sb, int64_t ld_sn, int64_t ld_sh,
                        const int64_t *cu_seqlens, float *states, float *gsum, int64_t B, int64_t N, int64_t H,
-                       int64_t D, int64_t E, int64_t M, int dtype, int reverse, int ranges, void *stream) {
+                       int64_t D, int64_t E, int64_t M, int dtype, int reverse, int ranges, unsigned flags,
+                       void *stream) {
   int rc = check_common(y, z, y, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc == LA_OK && ranges != 0 && cu_seqlens == nullptr) rc = LA_ERR_NULL_POINTER;
   if (rc != LA_OK) return rc;
@@ -638,6 +654,7 @@ int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld
   p.y = y; p.z = z; p.ld = ld; p.ld_sb = ld_sb; p.ld_sn = ld_sn; p.ld_sh = ld_sh; p.cu = cu_seqlens;
   p.states = states; p.gsum = gsum; p.B = (int)B; p.N = (int)N; p.H = (int)H; p.M = (int)M; p.reverse = reverse != 0;
   p.ranges = ranges != 0;
+  p.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
   return launch_state_pass(p, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -653,7 +670,7 @@ int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *se
 
 int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int64_t *cu_seqlens, float *states,
                        float *gsum, int64_t B, int64_t N, int64_t H, int64_t D, int64_t E, int64_t M, int dtype,
-                       int reverse, int ranges, void *stream) {
+                       int reverse, int ranges, unsigned flags, void *stream) {
   int rc = check_common(y, z, y, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc == LA_OK && ranges != 0 && cu_seqlens == nullptr) rc = LA_ERR_NULL_POINTER;
   if (rc != LA_OK) return rc;
@@ -662,6 +679,7 @@ int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int
   StatePass p;
   p.y = y; p.z = z; p.ldv = ldk; p.cu = cu_seqlens; p.states = states; p.gsum = gsum;
   p.B = (int)B; p.N = (int)N; p.H = (int)H; p.M = (int)M; p.reverse = reverse != 0; p.ranges = ranges != 0;
+  p.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
   return launch_state_pass_vec(p, dtype, static_cast<cudaStream_t>(stream));
 }
 

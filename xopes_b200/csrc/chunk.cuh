@@ -27,6 +27,7 @@ struct ChunkPass {
   int reverse = 0;
   const int64_t *cu = nullptr;
   int B = 0, N = 0, H = 0, M = 0;
+  int ld_act = 0;          // 1: ld holds pre-activations, the log decay is logsigmoid(ld)
   int fx = 128, fz = 128;  // features per head of x, y (the contraction of X Y^T) and of z, out, xrow
   int no_scratch = 0;  // 1: never take hand-off scratch from the library's pool (one CTA per pair)
 };
@@ -61,6 +62,7 @@ struct LavdPass {
   const int64_t *cu = nullptr;
   int B = 0, N = 0, H = 0, M = 0;
   int *unsafe = nullptr;
+  int ld_act = 0;    // 1: ldk holds pre-activations, the log decay is logsigmoid(ldk)
   int ref2 = 0;
   const int *enable = nullptr;  // optional device word: the launch does nothing while it reads 0
 };
@@ -81,6 +83,7 @@ struct StatePass {
   float *states = nullptr;                 // (nb,H,128,128) fp32
   float *gsum = nullptr;                   // (nb,H) fp32 (scalar) / (nb,H,128) (vector), optional
   int B = 0, N = 0, H = 0, M = 0, reverse = 0;
+  int ld_act = 0;  // 1: ld / ldv hold pre-activations, the log decay is their logsigmoid
   int ranges = 0;  // 1: cu holds M (begin, end) token ranges instead of M + 1 boundaries
 };
 int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream);

@@ -106,6 +106,7 @@ struct ChunkArgs {
   int state_transposed, reverse;
   const long long *cu;
   int B, N, H, M;
+  int ld_act;  // 1: ld holds pre-activations x and the log decay is logsigmoid(x)
   int fx, fz;  // features of X and Y (the contraction of X Y^T) and of Z, the output and xrow; <= 128
   int *status;
 };
@@ -486,7 +487,8 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       if (it >= t_cnt) return 0.f;
       const int n = chunk_of(it);
       if (i >= t_len - n * kChunk) return 0.f;
-      return ld_row[(long long)n * kChunk * a.ld_sn] * kLog2e;
+      const float raw = ld_row[(long long)n * kChunk * a.ld_sn];
+      return a.ld_act ? log2_sigmoid(raw) : raw * kLog2e;
     };
 
     // Per-chunk decay quantities of this thread's row.
@@ -1053,6 +1055,7 @@ int fill_pass(const ChunkPass &p, int dtype, PassMaps &m, ChunkArgs &a) {
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M;
   a.fx = p.fx; a.fz = p.fz;
+  a.ld_act = p.ld_act;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   return LA_OK;
@@ -1304,7 +1307,7 @@ int launch_chunk_pass_pair(const ChunkPass &p, const ChunkPass &q, int dtype, cu
   if (rc == LA_OK) rc = check_pass(q);
   if (rc != LA_OK) return rc;
   if (p.B != q.B || p.N != q.N || p.H != q.H || p.M != q.M || p.cu != q.cu || p.reverse != q.reverse ||
-      p.ld != q.ld || p.ld_sb != q.ld_sb || p.ld_sn != q.ld_sn || p.ld_sh != q.ld_sh)
+      p.ld != q.ld || p.ld_sb != q.ld_sb || p.ld_sn != q.ld_sn || p.ld_sh != q.ld_sh || p.ld_act != q.ld_act)
     return LA_ERR_BAD_SHAPE;
   if (dtype == LA_BF16) return launch_t<__nv_bfloat16>(p, &q, dtype, stream);
   if (dtype == LA_F16) return launch_t<__half>(p, &q, dtype, stream);

@@ -133,6 +133,7 @@ struct LavdArgs {
   int *status;
   int *unsafe;
   const int *enable;  // optional device word: the kernel does nothing while it reads 0
+  int ld_act;         // 1: the decay tensor holds pre-activations x and the log decay is logsigmoid(x)
 };
 
 // byte offset of the float4 holding features [d, d+4) of row i in the 128B-swizzled fp32 decay tile
@@ -616,8 +617,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           const int row = seg * 16 + r;  // row & 7 == r & 7
           if (row < L) {
             const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-            run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
-            run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
+            if (a.ld_act) {
+              run.x += log2_sigmoid(v.x); run.y += log2_sigmoid(v.y);
+              run.z += log2_sigmoid(v.z); run.w += log2_sigmoid(v.w);
+            } else {
+              run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
+              run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
+            }
           }
           acc16[r] = run;
         }
@@ -1077,6 +1083,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   a.status = status_word_ptr();
   a.unsafe = p.unsafe;
   a.enable = p.enable;
+  a.ld_act = p.ld_act;
   if (a.status == nullptr || a.unsafe == nullptr) return LA_ERR_CUDA;
   auto kern = lavd_pass_kernel<T, TMODE, REF2>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
       if (gr < R) {
         av = Cvt<T>::to_f(a[base]);
         if (x != nullptr) xv = Cvt<T>::to_f(x[base]);
-        if (has_ldr) dv = expf(p.ldr[base]);
+        if (has_ldr) dv = p.ld_act ? 1.f / (1.f + expf(-p.ldr[base])) : expf(p.ldr[base]);
       }
       a_s[idx] = av;
       x_s[idx] = xv;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
       if (c < C) {
         bv = Cvt<T>::to_f(b[base]);
         wv = Cvt<T>::to_f(w[base]);
-        if (has_ldc) dv = expf(p.ldc[base]);
+        if (has_ldc) dv = p.ld_act ? 1.f / (1.f + expf(-p.ldc[base])) : expf(p.ldc[base]);
       }
       b_s[idx] = bv;
       w_s[idx] = wv;
@@ -117,7 +117,10 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
       float lam = 1.f;
       // exp in double, rounded once: a per-head constant decay is applied at every token, so an
       // ulp of error in it compounds linearly with the sequence length
-      if (has_ld) lam = (float)exp((double)p.ld[bidx * p.ld_sb + tok(tid) * p.ld_sn + h * p.ld_sh]);
+      if (has_ld) {
+        const double raw = (double)p.ld[bidx * p.ld_sb + tok(tid) * p.ld_sn + h * p.ld_sh];
+        lam = (float)(p.ld_act ? 1.0 / (1.0 + exp(-raw)) : exp(raw));
+      }
       lam_s[tid] = lam;
     }
     __syncthreads();
@@ -296,7 +299,8 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
                                                          const float *slots_k, int ntk,
                                                          const float *sfin, const float *dsfin,
                                                          const int64_t *cu, float *dld, int B, int N,
-                                                         int H, int DE) {
+                                                         int H, int DE, const float *act_x, int64_t x_sb,
+                                                         int64_t x_sn, int64_t x_sh) {
   __shared__ float red[32];
   __shared__ float wsum[8];
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
@@ -331,7 +335,12 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
     __syncthreads();
     float pre = carry;
     for (int i = 0; i < wid; ++i) pre += wsum[i];
-    if (t >= t_begin) dld[(bidx * N + t) * H + h] = sc + pre;
+    if (t >= t_begin) {
+      float val = sc + pre;
+      // d logsigmoid(x) / dx = sigmoid(-x)
+      if (act_x != nullptr) val *= 1.f / (1.f + expf(act_x[bidx * x_sb + t * x_sn + h * x_sh]));
+      dld[(bidx * N + t) * H + h] = val;
+    }
     float tot = 0.f;
     for (int i = 0; i < 8; ++i) tot += wsum[i];
     carry += tot;
@@ -346,7 +355,7 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
 // of 32) so that the launch still fills the GPU.
 __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
                                                              const int64_t *cu, int N, int H, int F, int Fpad,
-                                                             int D, int E, int f_is_row) {
+                                                             int D, int E, int f_is_row, const float *act_x) {
   extern __shared__ float part[];  // [lanes + 1][Fpad]; row `lanes` holds the state term
   const int h = blockIdx.x, seq = blockIdx.y;
   const int lanes = blockDim.x / Fpad;
@@ -359,6 +368,7 @@ __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const f
   const int64_t p0 = t_begin + ln * per, p1 = min(t_end, p0 + per);
   const int64_t stride = (int64_t)H * F;
   float *ptr = buf + ((bidx * N) * H + h) * (int64_t)F + f;
+  const float *xptr = act_x != nullptr ? act_x + ((bidx * N) * H + h) * (int64_t)F + f : nullptr;
   const bool on = f < F;
 
   float s = 0.f;
@@ -395,27 +405,39 @@ __global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const f
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = ptr[(t - i) * stride];
+    if (xptr == nullptr) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run; }
+      for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run; }
+    } else {  // d logsigmoid(x) / dx = sigmoid(-x)
+      float xs[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xs[i] = xptr[(t - i) * stride];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run / (1.f + expf(xs[i])); }
+    }
   }
-  for (; t >= p0; --t) { run += ptr[t * stride]; ptr[t * stride] = run; }
+  for (; t >= p0; --t) {
+    run += ptr[t * stride];
+    ptr[t * stride] = xptr == nullptr ? run : run / (1.f + expf(xptr[t * stride]));
+  }
 }
 
 }  // namespace
 
 int launch_dld_scalar(const float *slots_q, int ntq, const float *slots_k, int ntk,
                       const float *final_state, const float *dfinal_state, const int64_t *cu,
-                      float *dld, int B, int N, int H, int DE, int M, cudaStream_t stream) {
+                      float *dld, int B, int N, int H, int DE, int M, cudaStream_t stream, const float *act_x,
+                      int64_t x_sb, int64_t x_sn, int64_t x_sh) {
   const int nb = cu ? M : B;
   dim3 grid(H, nb);
   dld_scalar_kernel<<<grid, 256, 0, stream>>>(slots_q, ntq, slots_k, ntk, final_state, dfinal_state,
-                                              cu, dld, B, N, H, DE);
+                                              cu, dld, B, N, H, DE, act_x, x_sb, x_sn, x_sh);
   return launch_status();
 }
 
 int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfinal_state,
                          const int64_t *cu, int B, int N, int H, int F, int D, int E, int f_is_row,
-                         int M, cudaStream_t stream) {
+                         int M, cudaStream_t stream, const float *act_x) {
   const int nb = cu ? M : B;
   int fpad = ((F + 31) / 32) * 32;
   if (fpad > 1024) return LA_ERR_UNSUPPORTED;
@@ -426,7 +448,7 @@ int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfin
   const int lanes = 1024 / fpad;
   const size_t smem = sizeof(float) * (size_t)(lanes + 1) * fpad;
   revcumsum_vec_kernel<<<grid, lanes * fpad, smem, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, fpad,
-                                                             D, E, f_is_row);
+                                                             D, E, f_is_row, act_x);
   return launch_status();
 }
 

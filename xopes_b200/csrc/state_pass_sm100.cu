@@ -62,6 +62,7 @@ struct StateArgs {
   float *gsum;    // (nb, H) total log decay of each sequence (natural log), optional
   int B, N, H, M, reverse;
   int ranges;  // 1: cu holds M (begin, end) pairs instead of M + 1 boundaries
+  int ld_act;  // 1: the log decay is logsigmoid(ld)
   int *status;
 };
 
@@ -166,7 +167,8 @@ state_pass_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_consta
       if (it >= nc) return 0.f;
       const int n = back ? (nc - 1 - it) : it;
       if (i >= len - n * kChunk) return 0.f;
-      return ld_row[(long long)n * kChunk * a.ld_sn] * kLog2e;
+      const float raw = ld_row[(long long)n * kChunk * a.ld_sn];
+      return a.ld_act ? log2_sigmoid(raw) : raw * kLog2e;
     };
     float run = 0.f;          // log2 decay between this chunk and the far end of the sequence
     float ld_next = load_ld(0);
@@ -269,6 +271,7 @@ int launch_t(const StatePass &p, int dtype, cudaStream_t stream) {
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.states = p.states; a.gsum = p.gsum;
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M; a.reverse = p.reverse; a.ranges = p.ranges;
+  a.ld_act = p.ld_act;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   auto kern = state_pass_kernel<T>;
@@ -375,7 +378,7 @@ struct StateVecArgs {
   const long long *cu;
   float *states;  // (nb, H, 128, 128)
   float *gsum;    // (nb, H, 128) total log decay per feature (natural log)
-  int B, N, H, M, reverse, ranges;
+  int B, N, H, M, reverse, ranges, ld_act;
   int *status;
 };
 
@@ -517,8 +520,13 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
           const int row = seg * 16 + r;
           if (row < L) {
             const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-            runv.x = fmaf(v.x, kLog2e, runv.x); runv.y = fmaf(v.y, kLog2e, runv.y);
-            runv.z = fmaf(v.z, kLog2e, runv.z); runv.w = fmaf(v.w, kLog2e, runv.w);
+            if (a.ld_act) {
+              runv.x += log2_sigmoid(v.x); runv.y += log2_sigmoid(v.y);
+              runv.z += log2_sigmoid(v.z); runv.w += log2_sigmoid(v.w);
+            } else {
+              runv.x = fmaf(v.x, kLog2e, runv.x); runv.y = fmaf(v.y, kLog2e, runv.y);
+              runv.z = fmaf(v.z, kLog2e, runv.z); runv.w = fmaf(v.w, kLog2e, runv.w);
+            }
           }
           acc16[r] = runv;
         }
@@ -624,6 +632,7 @@ int launch_vec_t(const StatePass &p, int dtype, cudaStream_t stream) {
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.states = p.states; a.gsum = p.gsum;
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M; a.reverse = p.reverse; a.ranges = p.ranges;
+  a.ld_act = p.ld_act;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   auto kern = state_pass_vec_kernel<T>;

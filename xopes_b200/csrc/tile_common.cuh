@@ -56,6 +56,21 @@ __device__ __forceinline__ float ex2(float x) {  // 2^x, one MUFU op; 2^(-inf) =
   return y;
 }
 
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// log2(sigmoid(x)) = min(x, 0) log2(e) - log2(1 + 2^(-|x| log2(e))): the log decay, in log2 units, of a
+// decay that is given as the pre-activation of a logsigmoid (no overflow for any x).
+__device__ __forceinline__ float log2_sigmoid(float x) {
+  const float l2e = 1.4426950408889634f;
+  const float t = ex2(-fabsf(x) * l2e);
+  // log2(1 + t): the series where 1 + t would round t away (decays close to 1)
+  const float l1p = t < 0.00390625f ? t * l2e * (1.f - t * (0.5f - t * 0.33333334f)) : lg2(1.f + t);
+  return fminf(x, 0.f) * l2e - l1p;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,

@@ -35,7 +35,7 @@ def lightning_attn_func(q: torch.Tensor, k: Optional[torch.Tensor] = None,
         raise ValueError(f"Invalid decay type: {decay_type}")
     return fn(q=q, k=k, v=v, ld=ld, ldk=ldk, ldv=ldv, initial_state=initial_state,
               cu_seqlens=cu_seqlens, save_states=save_states, save_ld=save_ld, save_a=save_a,
-              use_chunk_loop=use_chunk_loop)
+              use_chunk_loop=use_chunk_loop, **kwargs)
 
 
 __all__ = [

@@ -17,6 +17,8 @@ def lacd_fn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: Optional[torc
             initial_state: Optional[torch.Tensor] = None,
             cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
             use_chunk_loop: bool = False, **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+    if kwargs.get("decay_activation") is not None:
+        raise ValueError("decay_activation applies to data-dependent decays (scalar, vector), not to a constant one")
     h = q.shape[2]
     if ld is None:
         ld = torch.zeros(h, dtype=torch.float32, device=q.device)

@@ -13,7 +13,11 @@ Differences, all deliberate:
     (lightning_attn/__init__.py:35);
   * cu_seqlens is honoured by the chunk-parallel path too, with lasd_torch's semantics
     (scalar_decay/lasd_torch.py:61-103);
-  * save_states / use_chunk_loop are accepted and ignored: states are never materialised.
+  * save_states / use_chunk_loop are accepted and ignored: states are never materialised;
+  * decay_activation="logsigmoid" (an addition): ld then holds the pre-activations x of the usual
+    decay producer ld = logsigmoid(x) (benchmarks/lightning_attention/benchmark.py:308-317), the
+    kernels apply the activation where they read the decay and the gradient returned for ld is
+    d/dx.  Same result as passing F.logsigmoid(x), without the two elementwise passes.
 """
 from typing import Optional, Tuple
 
@@ -48,6 +52,14 @@ def _prep_state(state: Optional[torch.Tensor], nb: int, h: int, d: int, e: int):
     if tuple(s.shape) != (nb, h, d, e):
         raise ValueError(f"initial_state has shape {tuple(state.shape)}, expected ({nb},{h},{d},{e})")
     return s
+
+
+def _act_flag(decay_activation: Optional[str]) -> int:
+    if decay_activation is None:
+        return 0
+    if decay_activation != "logsigmoid":
+        raise ValueError(f"decay_activation must be None or 'logsigmoid', got {decay_activation!r}")
+    return _lib.FLAG_LD_LOGSIGMOID
 
 
 def _cu(cu_seqlens, device):
@@ -103,7 +115,7 @@ class LasdFunction(torch.autograd.Function):
             from .segmented import lasd_forward_segmented
             bounds, cap, ld_flat, strides = seg
             o, sf = lasd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e),
-                                           ld_flat, strides, s0, bounds, cap)
+                                           ld_flat, strides, s0, bounds, cap, flags & _lib.FLAG_LD_LOGSIGMOID)
             o = o.view(b, n, h, e)
             ctx.save_for_backward(q, k, v, ld, s0, cu)
             ctx.flags = flags
@@ -146,7 +158,8 @@ class LasdFunction(torch.autograd.Function):
             bounds, cap, strides = ctx.seg
             dq, dk, dv, dld, ds0 = lasd_backward_segmented(
                 q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), ld32, strides, s0,
-                do.view(1, b * n, h, e), dsf, bounds, cap, want_dld, want_ds0)
+                do.view(1, b * n, h, e), dsf, bounds, cap, want_dld, want_ds0,
+                ctx.flags & _lib.FLAG_LD_LOGSIGMOID)
             dq, dk, dv = dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e)
             if want_dld:
                 dld = dld.view(b, n, h)
@@ -192,30 +205,34 @@ def lasd_parallel_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                        ld: Optional[torch.Tensor] = None,
                        initial_state: Optional[torch.Tensor] = None,
                        cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
-                       use_chunk_loop: bool = False, **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+                       use_chunk_loop: bool = False, decay_activation: Optional[str] = None,
+                       **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Chunk-parallel lasd (signature of lasd_parallel_triton, lasd_parallel_triton.py:824-834).
     Runs the tcgen05 chunk kernels where they apply (16-bit inputs, D = E = 128), the fp32 scan
     kernels otherwise."""
-    return _lasd(q, k, v, ld, initial_state, cu_seqlens, 0)
+    return _lasd(q, k, v, ld, initial_state, cu_seqlens, _act_flag(decay_activation))
 
 
 def lasd_recurrence_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: torch.Tensor,
                          initial_state: Optional[torch.Tensor] = None,
                          cu_seqlens: Optional[torch.LongTensor] = None,
+                         decay_activation: Optional[str] = None,
                          **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Token-by-token lasd (signature of lasd_recurrence_triton, lasd_recurrence_triton.py:555-563):
     always the fp32 scan kernels."""
-    return _lasd(q, k, v, ld, initial_state, cu_seqlens, _lib.FLAG_FORCE_RECURRENCE)
+    return _lasd(q, k, v, ld, initial_state, cu_seqlens,
+                 _lib.FLAG_FORCE_RECURRENCE | _act_flag(decay_activation))
 
 
 def lasd_fn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: Optional[torch.Tensor] = None,
             initial_state: Optional[torch.Tensor] = None,
             cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
-            use_chunk_loop: bool = False, **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+            use_chunk_loop: bool = False, decay_activation: Optional[str] = None,
+            **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dispatch of scalar_decay/__init__.py:38-52: chunk-parallel for N > 1, recurrence for N == 1."""
     fn = lasd_parallel_cuda if v.shape[1] > 1 else lasd_recurrence_cuda
     return fn(q=q, k=k, v=v, ld=ld, initial_state=initial_state, cu_seqlens=cu_seqlens,
-              save_states=save_states, use_chunk_loop=use_chunk_loop)
+              save_states=save_states, use_chunk_loop=use_chunk_loop, decay_activation=decay_activation)
 
 
 def lasd_decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: torch.Tensor,

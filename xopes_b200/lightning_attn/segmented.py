@@ -145,7 +145,7 @@ def _plan(doc_bounds, cap, dev, h) -> _Plan:
     return p
 
 
-def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool):
+def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool, act: int = 0):
     """State entering every segment (forward flow: at its first token from ext = the documents'
     initial states; reverse flow: after its last token from ext = their final-state gradients),
     (nseg, H, 128, 128) fp32."""
@@ -163,7 +163,7 @@ def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool)
         if n_loc:
             rc = lib.la_lasd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(fl["ranges"]),
                                         _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
-                                        _lib.dtype_code(y), 1 if reverse else 0, 1, stream)
+                                        _lib.dtype_code(y), 1 if reverse else 0, 1, act, stream)
             _lib.check(rc, "la_lasd_state_pass")
         rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(fl["table"]), _lib.ptr(fl["emit"]),
                                      _lib.ptr(ext), _lib.ptr(incoming), None, fl["nunits"], h, d, e,
@@ -172,30 +172,31 @@ def _incoming_states(lib, y, z, ld32, ld_strides, pl: _Plan, ext, reverse: bool)
     return incoming
 
 
-def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds, cap):
+def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds, cap, act: int = 0):
     """q, k, v: (1, T, H, 128) contiguous 16-bit CUDA tensors (a batch flattened to one stream);
     ld32 fp32 with element strides over (stream token, head) = ld_strides[1:]; doc_bounds the
-    sequences [(a, b), ...] in stream order; initial_state (ndocs, H, 128, 128) fp32 or None.
+    sequences [(a, b), ...] in stream order; initial_state (ndocs, H, 128, 128) fp32 or None;
+    act = FLAG_LD_LOGSIGMOID when ld32 holds pre-activations of a logsigmoid, else 0.
     Returns (o (1,T,H,128), final states (ndocs,H,128,128) fp32)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
+    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False, act=act)
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
     st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
     _, sn, sh = ld_strides
     with torch.cuda.device(dev):
         rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
                              _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
-                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR if pl.cut else 0, _lib.stream_of(q))
+                             _lib.dtype_code(q), (_lib.FLAG_REQUIRE_TENSOR if pl.cut else 0) | act, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd (segmented)")
     return o, st.index_select(0, pl.last_idx)
 
 
 def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal_state, doc_bounds, cap,
-                            want_dld: bool, want_ds0: bool):
+                            want_dld: bool, want_ds0: bool, act: int = 0):
     """Backward twin: q, k, v, do (1, T, H, 128); initial_state / dfinal_state (ndocs, H, 128, 128)
     fp32 or None.  Returns (dq, dk, dv, dld (1,T,H) fp32 or None, dinitial_state (ndocs,...) or None)."""
     lib = _lib.load()
@@ -203,8 +204,8 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False)
-    ds_out = _incoming_states(lib, q, do, ld32, ld_strides, pl, dfinal_state, reverse=True)
+    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False, act=act)
+    ds_out = _incoming_states(lib, q, do, ld32, ld_strides, pl, dfinal_state, reverse=True, act=act)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dld = torch.empty(1, t, h, dtype=torch.float32, device=dev) if want_dld else None
     ds0 = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev) if want_ds0 else None
@@ -217,7 +218,7 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
         rc = lib.la_lasd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(s_in),
                              _lib.ptr(do), _lib.ptr(ds_out), _lib.ptr(pl.cu_dev), _lib.ptr(dq), _lib.ptr(dk),
                              _lib.ptr(dv), _lib.ptr(dld), _lib.ptr(ds0), _lib.ptr(ws), ws_bytes, 1, t, h, d, e,
-                             pl.nseg, _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR if pl.cut else 0,
+                             pl.nseg, _lib.dtype_code(q), (_lib.FLAG_REQUIRE_TENSOR if pl.cut else 0) | act,
                              _lib.stream_of(q))
         _lib.check(rc, "la_lasd_bwd (segmented)")
     if want_ds0:
@@ -228,7 +229,7 @@ def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal
 # --------------------------------------------------------------------------------------------
 # vector decay (ldk): the same scheme with a per-feature decay on the state's rows
 # --------------------------------------------------------------------------------------------
-def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool):
+def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool, act: int = 0):
     _, t, h, d = y.shape
     e = z.shape[-1]
     dev = y.device
@@ -242,7 +243,7 @@ def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool):
         if n_loc:
             rc = lib.la_lavd_state_pass(_lib.ptr(y), _lib.ptr(z), _lib.ptr(ldk), _lib.ptr(fl["ranges"]),
                                         _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
-                                        _lib.dtype_code(y), 1 if reverse else 0, 1, stream)
+                                        _lib.dtype_code(y), 1 if reverse else 0, 1, act, stream)
             _lib.check(rc, "la_lavd_state_pass")
         rc = lib.la_lavd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(fl["table"]), _lib.ptr(fl["emit"]),
                                      _lib.ptr(ext), _lib.ptr(incoming), fl["nunits"], h, d, e,
@@ -252,14 +253,16 @@ def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool):
 
 
 def lavd_forward_segmented(q, k, v, ldk, initial_state, doc_bounds, cap, flags):
-    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32, all contiguous.  Returns (o, final
-    states per document)."""
+    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32, all contiguous; flags as for
+    la_lavd_fwd (FLAG_LD_LOGSIGMOID reaches the state-only pass too).  Returns (o, final states per
+    document)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False)
+    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False,
+                                act=flags & _lib.FLAG_LD_LOGSIGMOID)
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
     st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
@@ -277,8 +280,9 @@ def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_b
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False)
-    ds_out = _incoming_states_vec(lib, q, do, ldk, pl, dfinal_state, reverse=True)
+    act = flags & _lib.FLAG_LD_LOGSIGMOID
+    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False, act=act)
+    ds_out = _incoming_states_vec(lib, q, do, ldk, pl, dfinal_state, reverse=True, act=act)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dldk = torch.empty(1, t, h, d, dtype=torch.float32, device=dev)
     ds0 = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev) if want_ds0 else None

@@ -12,14 +12,17 @@ Differences, all deliberate:
     lavd_torch ignores the argument (vector_decay/lavd_torch.py:16);
   * k=None / v=None ("share" mode: k = 1-exp(ldk), v = 1-exp(ldv), lavd_torch.py:55-63) is
     expanded here with torch elementwise ops, so autograd adds the chain-rule term
-    dldk += dk * (-exp(ldk)) of lavd_recurrence_triton.py:701-709 by itself.
+    dldk += dk * (-exp(ldk)) of lavd_recurrence_triton.py:701-709 by itself;
+  * decay_activation="logsigmoid" (an addition): ldk / ldv then hold the pre-activations x of
+    ld = logsigmoid(x), applied inside the kernels, and their gradients come back as d/dx
+    (not with k=None / v=None, which need the log decay itself).
 """
 from typing import Optional, Tuple
 
 import torch
 
 from .. import _lib
-from .scalar_decay import _cu, _prep_state
+from .scalar_decay import _act_flag, _cu, _prep_state
 
 
 def _ld32(x):
@@ -139,6 +142,8 @@ class LavdFunction(torch.autograd.Function):
 def _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, flags):
     if ldk is None and ldv is None:
         raise AssertionError("At least one of ldk or ldv must be used")
+    if (flags & _lib.FLAG_LD_LOGSIGMOID) and (k is None or v is None):
+        raise ValueError("decay_activation needs explicit k and v (the share mode derives them from the log decay)")
     if k is None:
         if ldk is None:
             raise AssertionError("ldk must be provided when k is None")
@@ -159,10 +164,11 @@ def lavd_parallel_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
                        use_ldv: bool = False, initial_state: Optional[torch.Tensor] = None,
                        cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
                        save_ld: bool = True, save_a: bool = True, use_chunk_loop: bool = False,
+                       decay_activation: Optional[str] = None,
                        **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Signature of lavd_parallel_triton (lavd_parallel_triton.py:1415-1430); use_ldk / use_ldv are
     derived from ldk / ldv being given, as there (:1462-1470)."""
-    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, 0)
+    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, _act_flag(decay_activation))
 
 
 def lavd_recurrence_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
@@ -170,9 +176,11 @@ def lavd_recurrence_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
                          ldv: Optional[torch.Tensor] = None, use_ldk: bool = True,
                          use_ldv: bool = False, initial_state: Optional[torch.Tensor] = None,
                          cu_seqlens: Optional[torch.LongTensor] = None,
+                         decay_activation: Optional[str] = None,
                          **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Signature of lavd_recurrence_triton: always the fp32 scan kernels."""
-    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, _lib.FLAG_FORCE_RECURRENCE)
+    return _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens,
+                 _lib.FLAG_FORCE_RECURRENCE | _act_flag(decay_activation))
 
 
 def lavd_fn(q: torch.Tensor, k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
@@ -180,12 +188,12 @@ def lavd_fn(q: torch.Tensor, k: Optional[torch.Tensor] = None, v: Optional[torch
             initial_state: Optional[torch.Tensor] = None,
             cu_seqlens: Optional[torch.LongTensor] = None, save_states: bool = True,
             save_ld: bool = True, save_a: bool = True, use_chunk_loop: bool = False,
-            **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+            decay_activation: Optional[str] = None, **kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dispatch of vector_decay/__init__.py:44-64."""
     fn = lavd_parallel_cuda if q.shape[1] > 1 else lavd_recurrence_cuda
     return fn(q=q, k=k, v=v, ldk=ldk, ldv=ldv, initial_state=initial_state, cu_seqlens=cu_seqlens,
               save_states=save_states, save_ld=save_ld, save_a=save_a,
-              use_chunk_loop=use_chunk_loop)
+              use_chunk_loop=use_chunk_loop, decay_activation=decay_activation)
 
 
 def lavd_decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
