@@ -612,20 +612,28 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // store per row and no read-back
         float4 acc16[16];
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!a.ld_act) {
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const int row = seg * 16 + r;  // row & 7 == r & 7
-          if (row < L) {
-            const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-            if (a.ld_act) {
-              run.x += log2_sigmoid(v.x); run.y += log2_sigmoid(v.y);
-              run.z += log2_sigmoid(v.z); run.w += log2_sigmoid(v.w);
-            } else {
+          for (int r = 0; r < 16; ++r) {
+            const int row = seg * 16 + r;  // row & 7 == r & 7
+            if (row < L) {
+              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
               run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
               run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
             }
+            acc16[r] = run;
           }
-          acc16[r] = run;
+        } else {  // the tile holds pre-activations of a logsigmoid
+#pragma unroll
+          for (int r = 0; r < 16; ++r) {
+            const int row = seg * 16 + r;
+            if (row < L) {
+              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
+              run.x += log2_sigmoid(v.x); run.y += log2_sigmoid(v.y);
+              run.z += log2_sigmoid(v.z); run.w += log2_sigmoid(v.w);
+            }
+            acc16[r] = run;
+          }
         }
         *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = run;
         named_bar_sync(1, kComputeThreads);

@@ -348,77 +348,117 @@ __global__ void __launch_bounds__(256) dld_scalar_kernel(const float *slots_q, i
 }
 
 // One CTA per (sequence, head): in-place reverse cumulative sum over tokens of every feature f,
-// plus the state term (sum_option 0 / 1 of the reference kernel named above).  The sequence is cut
-// into `lanes` contiguous parts, one per group of Fpad threads: part sums, suffix offsets across
-// parts, then the running sum inside each part -- two reads and one write of the buffer.  With few
+// plus the state term (sum_option 0 / 1 of the reference kernel named above), in ONE read and one
+// write of the buffer.  The CTA walks the sequence from its end in tiles of lanes x kRcRows tokens;
+// group ln of Fpad threads owns kRcRows consecutive tokens of the tile (group 0 the latest), keeps
+// them in registers, the groups' sums meet in shared memory, and every thread then writes its
+// running sums.  The next tile is loaded before the current one is finished.  With few
 // (sequence, head) pairs the features are split over blockIdx.z (Fpad features per CTA, a multiple
 // of 32) so that the launch still fills the GPU.
-__global__ void __launch_bounds__(1024) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
+constexpr int kRcRows = 16;
+
+__global__ void __launch_bounds__(512, 2) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
                                                              const int64_t *cu, int N, int H, int F, int Fpad,
                                                              int D, int E, int f_is_row, const float *act_x) {
-  extern __shared__ float part[];  // [lanes + 1][Fpad]; row `lanes` holds the state term
+  extern __shared__ float part[];  // [2][lanes][Fpad] + [Fpad]
   const int h = blockIdx.x, seq = blockIdx.y;
   const int lanes = blockDim.x / Fpad;
   const int fl = threadIdx.x % Fpad, ln = threadIdx.x / Fpad;
   const int f = blockIdx.z * Fpad + fl;  // feature of this thread
   int64_t t_begin = 0, t_end = N, bidx = seq;
   if (cu != nullptr) { t_begin = cu[seq]; t_end = cu[seq + 1]; bidx = 0; }
-  const int64_t len = t_end - t_begin;
-  const int64_t per = (len + lanes - 1) / lanes;
-  const int64_t p0 = t_begin + ln * per, p1 = min(t_end, p0 + per);
   const int64_t stride = (int64_t)H * F;
-  float *ptr = buf + ((bidx * N) * H + h) * (int64_t)F + f;
-  const float *xptr = act_x != nullptr ? act_x + ((bidx * N) * H + h) * (int64_t)F + f : nullptr;
   const bool on = f < F;
+  const int fc = on ? f : 0;
+  float *ptr = buf + ((bidx * N) * H + h) * (int64_t)F + fc;
+  const float *xptr = act_x != nullptr ? act_x + ((bidx * N) * H + h) * (int64_t)F + fc : nullptr;
 
-  float s = 0.f;
-  if (on) {
-    int64_t t = p0;
-    for (; t + 7 < p1; t += 8) {
-      float v[8];
+  // the state term starts the running sum: sum over the other index of final_state * d final_state,
+  // formed by the whole CTA with coalesced reads and left in term[Fpad]
+  float *term = part + 2 * lanes * Fpad;
+  float carry = 0.f;
+  if (sfin != nullptr && dsfin != nullptr) {
+    const int64_t base = ((int64_t)seq * H + h) * (int64_t)D * E;
+    if (f_is_row) {  // a warp per row f: E contiguous elements
+      const int lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+      for (int r = threadIdx.x >> 5; r < Fpad; r += nwarps) {
+        const int fr = blockIdx.z * Fpad + r;
+        float a = 0.f;
+        if (fr < F)
+          for (int e = lane; e < E; e += 32) a = fmaf(sfin[base + (int64_t)fr * E + e], dsfin[base + (int64_t)fr * E + e], a);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = ptr[(t + i) * stride];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) s += v[i];
+        for (int off = 16; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        if (lane == 0) term[r] = a;
+      }
+      __syncthreads();
+    } else {  // column f: group ln takes rows ln, ln + lanes, ...
+      float a = 0.f;
+      if (on)
+        for (int d = ln; d < D; d += lanes) a = fmaf(sfin[base + (int64_t)d * E + f], dsfin[base + (int64_t)d * E + f], a);
+      part[ln * Fpad + fl] = a;
+      __syncthreads();
+      if (ln == 0) {
+        float t = 0.f;
+        for (int l = 0; l < lanes; ++l) t += part[l * Fpad + fl];
+        term[fl] = t;
+      }
+      __syncthreads();
     }
-    for (; t < p1; ++t) s += ptr[t * stride];
+    carry = term[fl];
   }
-  part[ln * Fpad + fl] = s;
-  if (ln == 0) {
-    float st = 0.f;
-    if (on && sfin != nullptr && dsfin != nullptr) {
-      const int64_t base = ((int64_t)seq * H + h) * (int64_t)D * E;
-      if (f_is_row) {
-        for (int e = 0; e < E; ++e) st = fmaf(sfin[base + (int64_t)f * E + e], dsfin[base + (int64_t)f * E + e], st);
-      } else {
-        for (int d = 0; d < D; ++d) st = fmaf(sfin[base + (int64_t)d * E + f], dsfin[base + (int64_t)d * E + f], st);
+
+  // token positions are counted from t_begin in 32 bits; this thread's tokens of the tile that ends
+  // at position `hi` are hi - 1 - ln kRcRows - i, i = 0 .. kRcRows - 1
+  const int len = (int)(t_end - t_begin);
+  const int tile = lanes * kRcRows;
+  float *base = ptr + t_begin * stride;
+  const float *xbase = xptr != nullptr ? xptr + t_begin * stride : nullptr;
+  auto load = [&](int r0, float (&v)[kRcRows]) {
+    const float *pc = base + (int64_t)r0 * stride;
+#pragma unroll
+    for (int i = 0; i < kRcRows; ++i, pc -= stride) v[i] = (on && r0 - i >= 0) ? *pc : 0.f;
+  };
+  float cur[kRcRows], nxt[kRcRows];
+  if (len > 0) load(len - 1 - ln * kRcRows, cur);
+  int phase = 0;
+  for (int hi = len; hi > 0; hi -= tile, phase ^= 1) {
+    const int r0 = hi - 1 - ln * kRcRows;
+    const bool more = hi > tile;
+    if (more) load(r0 - tile, nxt);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRcRows; ++i) s += cur[i];
+    float *pp = part + phase * lanes * Fpad;
+    pp[ln * Fpad + fl] = s;
+    __syncthreads();  // the other buffer is written next, so one barrier per tile is enough
+    float run = carry, tot = 0.f;
+    for (int l = 0; l < lanes; ++l) {
+      const float pv = pp[l * Fpad + fl];
+      if (l < ln) run += pv;
+      tot += pv;
+    }
+    carry += tot;
+    if (on) {
+      float *pc = base + (int64_t)r0 * stride;
+      if (xbase == nullptr) {
+#pragma unroll
+        for (int i = 0; i < kRcRows; ++i, pc -= stride) {
+          run += cur[i];
+          if (r0 - i >= 0) *pc = run;
+        }
+      } else {  // d logsigmoid(x) / dx = sigmoid(-x)
+        const float *xc = xbase + (int64_t)r0 * stride;
+#pragma unroll
+        for (int i = 0; i < kRcRows; ++i, pc -= stride, xc -= stride) {
+          run += cur[i];
+          if (r0 - i >= 0) *pc = run / (1.f + expf(*xc));
+        }
       }
     }
-    part[lanes * Fpad + fl] = st;
-  }
-  __syncthreads();
-  if (!on) return;
-  float run = part[lanes * Fpad + fl];
-  for (int l = lanes - 1; l > ln; --l) run += part[l * Fpad + fl];
-  int64_t t = p1 - 1;
-  for (; t - 7 >= p0; t -= 8) {
-    float v[8];
+    if (more) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = ptr[(t - i) * stride];
-    if (xptr == nullptr) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run; }
-    } else {  // d logsigmoid(x) / dx = sigmoid(-x)
-      float xs[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) xs[i] = xptr[(t - i) * stride];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { run += v[i]; ptr[(t - i) * stride] = run / (1.f + expf(xs[i])); }
+      for (int i = 0; i < kRcRows; ++i) cur[i] = nxt[i];
     }
-  }
-  for (; t >= p0; --t) {
-    run += ptr[t * stride];
-    ptr[t * stride] = xptr == nullptr ? run : run / (1.f + expf(xptr[t * stride]));
   }
 }
 
@@ -441,12 +481,14 @@ int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfin
   const int nb = cu ? M : B;
   int fpad = ((F + 31) / 32) * 32;
   if (fpad > 1024) return LA_ERR_UNSUPPORTED;
-  // about two CTAs per SM: split the features while (sequence, head) pairs alone are too few
+  // two CTAs of 512 threads per SM: split the features while the (sequence, head) pairs alone would
+  // leave room in one wave of 296
   int fsplit = 1;
-  while (fpad % (2 * 32) == 0 && (int64_t)H * nb * fsplit < 296 && fsplit < 8) { fpad /= 2; fsplit *= 2; }
+  while (fpad % (2 * 32) == 0 && (int64_t)H * nb * fsplit * 2 <= 296 && fsplit < 8) { fpad /= 2; fsplit *= 2; }
+  while (fpad > 512) { fpad = ((fpad / 2 + 31) / 32) * 32; fsplit *= 2; }  // wide features: more CTAs
   dim3 grid(H, nb, fsplit);
-  const int lanes = 1024 / fpad;
-  const size_t smem = sizeof(float) * (size_t)(lanes + 1) * fpad;
+  const int lanes = 512 / fpad;
+  const size_t smem = sizeof(float) * (2 * (size_t)lanes + 1) * fpad;
   revcumsum_vec_kernel<<<grid, lanes * fpad, smem, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, fpad,
                                                              D, E, f_is_row, act_x);
   return launch_status();

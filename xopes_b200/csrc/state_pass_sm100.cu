@@ -515,20 +515,28 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
         const uint32_t c4 = (uint32_t)((d0 & 31) >> 2);
         float4 acc16[16];
         float4 runv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!a.ld_act) {
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const int row = seg * 16 + r;
-          if (row < L) {
-            const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-            if (a.ld_act) {
-              runv.x += log2_sigmoid(v.x); runv.y += log2_sigmoid(v.y);
-              runv.z += log2_sigmoid(v.z); runv.w += log2_sigmoid(v.w);
-            } else {
+          for (int r = 0; r < 16; ++r) {
+            const int row = seg * 16 + r;
+            if (row < L) {
+              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
               runv.x = fmaf(v.x, kLog2e, runv.x); runv.y = fmaf(v.y, kLog2e, runv.y);
               runv.z = fmaf(v.z, kLog2e, runv.z); runv.w = fmaf(v.w, kLog2e, runv.w);
             }
+            acc16[r] = runv;
           }
-          acc16[r] = runv;
+        } else {  // the tile holds pre-activations of a logsigmoid
+#pragma unroll
+          for (int r = 0; r < 16; ++r) {
+            const int row = seg * 16 + r;
+            if (row < L) {
+              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
+              runv.x += log2_sigmoid(v.x); runv.y += log2_sigmoid(v.y);
+              runv.z += log2_sigmoid(v.z); runv.w += log2_sigmoid(v.w);
+            }
+            acc16[r] = runv;
+          }
         }
         *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = runv;
         const float4 far = *reinterpret_cast<const float4 *>(&run[d0]);  // decay between this chunk and the far end
