@@ -217,7 +217,9 @@ LA_API int la_lavd_bwd(const void *q, const void *k, const void *v, const float 
  * of `local` / gsum with the segment's own state, or -1 if none was computed (counts as zero)}.
  * emit (optional, int32 (nseg)) names the row of `incoming` each segment's entering state goes to,
  * -1 for none: the state-only pass may run on finer pieces than the segments that need an entering
- * state.  `ends` (optional, (nseg,H,D,E)) receives the state after each segment.
+ * state.  `ends` (optional, one (H,D,E) row per document) receives the state after each
+ * document's last segment in walking order: its end state (forward flow), the state before its first
+ * token (reverse flow).  `incoming` may be NULL when only `ends` is wanted.
  * ------------------------------------------------------------------------------------------- */
 LA_API int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld_sb,
                               int64_t ld_sn, int64_t ld_sh, const int64_t *cu_seqlens, float *states,

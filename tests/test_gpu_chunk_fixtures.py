@@ -49,7 +49,7 @@ def test_local_and_scanned_states(lib):
         assert lib.la_lasd_state_pass(kc.data_ptr(), vc.data_ptr(), ldc.data_ptr(), 0, h, 1, cu.data_ptr(),
                                       local.data_ptr(), gsum.data_ptr(), 1, n, h, d, d, L, _lib.LA_BF16, reverse, 0,
                                       0, stream) == 0
-        inc, ends = torch.empty_like(local), torch.empty_like(local)
+        inc, ends = torch.empty_like(local), torch.empty(1, h, d, d, device=dev)   # one document
         assert lib.la_lasd_fold_states(local.data_ptr(), gsum.data_ptr(), tab.data_ptr(), None, s0.to(dev).data_ptr(),
                                        inc.data_ptr(), ends.data_ptr(), L, h, d, d, reverse, stream) == 0
         rloc, rglob = cfx.lasd_chunk_states(k, v, ld, s0, block, bool(reverse))
@@ -57,7 +57,7 @@ def test_local_and_scanned_states(lib):
         if not reverse:
             assert_close("local states", rloc, local, TOL_BF16)
             assert_close("scanned states (entering each chunk)", rglob[:L], inc, TOL_BF16)
-            assert_close("final state", rglob[L], ends[L - 1], TOL_BF16)
+            assert_close("final state", rglob[L], ends[0], TOL_BF16)
         else:
             # the kernel's reverse state includes the decay of the chunk's first token, the
             # reference applies it one step later (oracle/chunk_fixtures.py)

@@ -51,6 +51,53 @@ def test_emulated_ranks_match_whole_stream(world, lens, h, d, e, dtype, tol, per
                 assert_close(f"state doc {doc}", rs[doc], states[j], tol)
 
 
+@pytest.mark.parametrize("world,lens,h,per_head", [
+    (4, [100, 700, 400, 336], 2, True),
+    (4, [100, 700, 400, 336], 2, False),
+    (4, [300, 3000, 796], 2, True),          # one document covers two whole ranks
+    (2, [5000, 11000, 384], 2, False),       # long documents: the ranks cut them into segments
+    (2, [64, 64, 128], 2, True),             # nothing crosses the cut
+])
+def test_emulated_ranks_exchange_before_the_chunk_pass(world, lens, h, per_head):
+    """forward_exchange_first (what lasd_seqpar_forward runs on CUDA with the all-gather exchange):
+    state-only pass -> exchange -> one chunk pass from true states, no correction.  Ranks are
+    emulated in order, the gather handing each rank the summaries of the ranks before it."""
+    from xopes_b200.lightning_attn import seq_parallel as sp
+    d = e = 128
+    n = sum(lens)
+    g = torch.Generator().manual_seed(13)
+    cast = lambda t: t.bfloat16().float()  # noqa: E731
+    q = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    k = cast(torch.randn(1, n, h, d, generator=g) * d ** -0.5)
+    v = cast(torch.randn(1, n, h, e, generator=g))
+    if per_head:
+        ld = torch.log(1 - 2.0 ** (-5 - torch.arange(h, dtype=torch.float32) / 2))
+        ld_full = ld.view(1, 1, h).expand(1, n, h)
+    else:
+        ld_full = torch.nn.functional.logsigmoid(torch.randn(1, n, h, generator=g) + 4)
+    cu = [0] + [int(x) for x in torch.tensor(lens).cumsum(0)]
+    dev = "cuda"
+    ro, rs = orc.lasd_forward(q, k, v, ld_full, None, torch.tensor(cu))
+    published = []
+    for r in range(world):
+        a, b = sp.token_range(n, r, world)
+        plan = sp.shard_documents(cu, a, b)
+        ql, kl, vl = (t[:, a:b].bfloat16().to(dev).contiguous() for t in (q, k, v))
+        ldl = ld.to(dev) if per_head else ld_full[:, a:b].to(dev).contiguous()
+
+        def gather(summary):
+            published.append(summary)
+            rows = published + [torch.zeros_like(summary)] * (world - len(published))
+            return torch.stack(rows)
+
+        o, states, plan = sp.forward_exchange_first(ql, kl, vl, ldl, plan, r, gather)
+        assert (plan.s_in is not None) == plan.open_start
+        assert_close(f"o rank {r}", ro[:, a:b], o.float(), TOL_BF16)
+        for j, doc in enumerate(plan.doc_ids):
+            if cu[doc + 1] <= b:
+                assert_close(f"state doc {doc}", rs[doc], states[j], TOL_BF16)
+
+
 @pytest.mark.parametrize("world,lens,per_head", [(4, [100, 700, 400, 336], True), (3, [900, 1400, 772], False),
                                                   (2, [2048, 2048], True)])
 def test_emulated_ranks_backward_matches_whole_stream(world, lens, per_head):

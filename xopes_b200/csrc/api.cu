@@ -661,7 +661,8 @@ int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld
 int la_lasd_fold_states(const float *local, const float *gsum, const int32_t *seg_table, const int32_t *emit,
                         const float *ext, float *incoming, float *ends, int64_t nseg, int64_t H, int64_t D, int64_t E, int reverse,
                         void *stream) {
-  if (local == nullptr || gsum == nullptr || seg_table == nullptr || incoming == nullptr) return LA_ERR_NULL_POINTER;
+  if (local == nullptr || gsum == nullptr || seg_table == nullptr) return LA_ERR_NULL_POINTER;
+  if (incoming == nullptr && ends == nullptr) return LA_ERR_NULL_POINTER;  // at least one output
   if (nseg <= 0 || H <= 0 || D <= 0 || E <= 0) return LA_ERR_BAD_SHAPE;
   if (nseg > 65535 || H * D * E > 0x7fffffff) return LA_ERR_TOO_LARGE;
   return launch_fold_states(local, gsum, seg_table, emit, ext, incoming, ends, (int)nseg, (int)H, (int)(D * E),

@@ -114,9 +114,11 @@ struct ChunkArgs {
 // How the (sequence, head) pairs of a launch are spread over its CTAs.
 //
 // balanced = 0: CTA r owns pair r whole.
-// balanced = 1: every pair is a run of w = max(chunks, 1) units in processing order; the pairs'
-//   runs are laid end to end (pair = sequence * H + head) and CTA r of R owns units
-//   [total r / R, total (r+1) / R).  A pair cut by a boundary is worked on by two neighbouring
+// balanced = 1: every pair is a run of chunks + kTaskUnits units in processing order (the extra
+//   units stand for the cost of switching to the pair and are left out when all pairs have the
+//   same length); the pairs' runs are laid end to end
+//   (pair = sequence * H + head) and CTA r of R owns units [total r / R, total (r+1) / R), a
+//   boundary inside a pair's switch units moving to the pair's start.  A pair cut by a boundary is worked on by two neighbouring
 //   CTAs: the one that owns its first part publishes the running state to its hand-off slot, the
 //   one that owns the rest picks it up there.  A CTA works on the part it publishes first and on
 //   the part it has to wait for last, so with pairs shorter than a CTA's share nobody waits.
@@ -125,8 +127,8 @@ struct ChunkArgs {
 //   fetched from HBM once and found in L2 by the other.
 struct Sched {
   int balanced, npass;
-  long long total;           // sum of w over all pairs (fixed-length launches; else H * wprefix[M])
-  const long long *wprefix;  // cu_seqlens launches: exclusive prefix sum of w over sequences (M + 1)
+  long long total;           // sum of the units of all pairs (fixed-length launches; else H * wprefix[M])
+  const long long *wprefix;  // cu_seqlens launches: exclusive prefix sum of units over sequences (M + 1)
   float *handoff;            // [gridDim.x][128 * 128] fp32, element (i, c) of T at c * 128 + i
   int *flags;                // [gridDim.x], zero before the launch; 1 = slot written
 };
@@ -156,11 +158,24 @@ struct Task {
   bool waits, publishes;
 };
 
-__device__ __forceinline__ void locate(const ChunkArgs &a, const Sched &sc, long long x, int &p, int &off) {
-  if (a.cu == nullptr) {
+// A task switch (drain, new starting state, pipeline refill) costs about as much as two chunks, so
+// a pair weighs its chunks plus kTaskUnits: a CTA that is handed many short pairs gets fewer chunks.
+constexpr int kTaskUnits = 2;
+
+// Position x of the weighted unit space -> (pair, processing step).  The first kTaskUnits units of a
+// pair stand for its switch and map to step 0, so a boundary that falls there moves to the pair's
+// start.  x = total maps to (number of pairs, 0).
+__device__ __forceinline__ void locate(const ChunkArgs &a, const Sched &sc, long long x, long long total, int &p,
+                                       int &step) {
+  if (x >= total) {
+    p = (a.cu != nullptr ? a.M : a.B) * a.H;
+    step = 0;
+    return;
+  }
+  if (a.cu == nullptr) {  // equal pairs: nothing to weigh, the split is even in chunks
     const int w = (a.N + kChunk - 1) / kChunk;
     p = (int)(x / w);
-    off = (int)(x - (long long)p * w);
+    step = (int)(x - (long long)p * w);
     return;
   }
   int lo = 0, hi = a.M - 1;  // largest seq with H * wprefix[seq] <= x
@@ -172,9 +187,11 @@ __device__ __forceinline__ void locate(const ChunkArgs &a, const Sched &sc, long
   const long long w = sc.wprefix[lo + 1] - sc.wprefix[lo];
   const int h = (int)(rem / w);
   p = lo * a.H + h;
-  off = (int)(rem - (long long)h * w);
+  step = max(0, (int)(rem - (long long)h * w) - kTaskUnits);
 }
 
+// CTA r owns the positions [start(r), start(r + 1)) in (pair, step) order, start(r) = the position
+// of unit total r / R.
 __device__ __forceinline__ Range cta_range(const ChunkArgs &a, const Sched &sc, int r, int R) {
   Range g;
   if (!sc.balanced) {
@@ -184,10 +201,16 @@ __device__ __forceinline__ Range cta_range(const ChunkArgs &a, const Sched &sc, 
     return g;
   }
   const long long total = a.cu != nullptr ? (long long)a.H * sc.wprefix[a.M] : sc.total;
-  const long long lo = total * r / R, hi = total * (r + 1) / R;
-  locate(a, sc, lo, g.p_a, g.off_a);
-  locate(a, sc, hi - 1, g.p_b, g.end_b);
-  g.end_b += 1;
+  int p_e, step_e;
+  locate(a, sc, total * r / R, total, g.p_a, g.off_a);
+  locate(a, sc, total * (r + 1) / R, total, p_e, step_e);
+  if (step_e == 0) {  // ends with a whole pair
+    g.p_b = p_e - 1;
+    g.end_b = 0x7fffffff;
+  } else {
+    g.p_b = p_e;
+    g.end_b = step_e;
+  }
   return g;
 }
 
@@ -245,7 +268,9 @@ __device__ __forceinline__ uint32_t kslice(int ks) { return (uint32_t)(ks >> 2) 
 // box holds, TMA fills the rest of the box with zeros on load and clips it on store, and the zero
 // features add nothing to any product; only the accesses that bypass TMA (states, ragged last
 // chunks, the row-dot operand) look at the real widths.
-template <typename T, bool F128>
+// ACT = true: ld holds pre-activations of a logsigmoid (an instantiation of its own: the extra
+// arithmetic sits on the decay scan at the top of every chunk, which the plain path should not carry).
+template <typename T, bool F128, bool ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Launch lp) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -488,7 +513,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
       const int n = chunk_of(it);
       if (i >= t_len - n * kChunk) return 0.f;
       const float raw = ld_row[(long long)n * kChunk * a.ld_sn];
-      return a.ld_act ? log2_sigmoid(raw) : raw * kLog2e;
+      return ACT ? log2_sigmoid(raw) : raw * kLog2e;
     };
 
     // Per-chunk decay quantities of this thread's row.
@@ -966,7 +991,7 @@ chunk_pass_kernel(const __grid_constant__ Maps maps, const __grid_constant__ Lau
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-// wprefix[s] = sum over sequences before s of max(chunks, 1); one block
+// wprefix[s] = sum over sequences before s of (chunks + kTaskUnits); one block
 __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wprefix) {
   __shared__ long long part[1024];
   const int tid = threadIdx.x, per = (M + 1023) / 1024;
@@ -974,7 +999,7 @@ __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wpre
   long long sum = 0;
   for (int s = lo; s < hi; ++s) {
     const long long len = cu[s + 1] - cu[s];
-    sum += max((len + kChunk - 1) / kChunk, 1LL);
+    sum += (len + kChunk - 1) / kChunk + kTaskUnits;
   }
   part[tid] = sum;
   __syncthreads();
@@ -988,13 +1013,13 @@ __global__ void weight_prefix_kernel(const long long *cu, int M, long long *wpre
   for (int s = lo; s < hi; ++s) {
     wprefix[s] = run;
     const long long len = cu[s + 1] - cu[s];
-    run += max((len + kChunk - 1) / kChunk, 1LL);
+    run += (len + kChunk - 1) / kChunk + kTaskUnits;
   }
   if (tid == 1023) wprefix[M] = part[1023];
 }
 
 struct DeviceInfo {
-  bool ready = false, attr[4] = {false, false, false, false}, pool_tried = false;
+  bool ready = false, attr[8] = {false, false, false, false, false, false, false, false}, pool_tried = false;
   int sms = 0, dev = 0;
   cudaMemPool_t pool = nullptr;  // hand-off scratch; made on first need, null if that failed
 };
@@ -1072,8 +1097,10 @@ int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t str
   DeviceInfo *di = device_info();
   if (di == nullptr) return LA_ERR_CUDA;
   const bool f128 = p.fx == 128 && p.fz == 128 && (q == nullptr || (q->fx == 128 && q->fz == 128));
-  auto kern = f128 ? chunk_pass_kernel<T, true> : chunk_pass_kernel<T, false>;
-  bool &attr = di->attr[(dtype == LA_BF16 ? 0 : 1) + (f128 ? 0 : 2)];  // the attribute is per device
+  const bool act = p.ld_act != 0;
+  auto kern = f128 ? (act ? chunk_pass_kernel<T, true, true> : chunk_pass_kernel<T, true, false>)
+                   : (act ? chunk_pass_kernel<T, false, true> : chunk_pass_kernel<T, false, false>);
+  bool &attr = di->attr[(dtype == LA_BF16 ? 0 : 1) + (f128 ? 0 : 2) + (act ? 4 : 0)];  // the attribute is per device
   if (!attr) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return LA_ERR_CUDA;

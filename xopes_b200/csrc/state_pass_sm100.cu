@@ -291,7 +291,8 @@ int launch_t(const StatePass &p, int dtype, cudaStream_t stream) {
 //   reverse:  s = last(k)  ? ext[doc(k)] : s ;  out[k] = s ;  s = local[k] + e^{gsum[k]} s   (k descending)
 // seg rows are {document, first-of-document, last-of-document, row of `local` holding the segment's
 // own state or -1 if it was not computed (then it counts as zero: fine for a segment nothing
-// follows)}.  ends[k] (optional) receives the state after folding segment k.
+// follows)}.  ends[doc] (optional, one row per document) receives the state after the document's
+// last segment in fold order: its end state (forward) or the state before its first token (reverse).
 __global__ void fold_states_kernel(const float *__restrict__ local, const float *__restrict__ gsum,
                                    const int *__restrict__ seg, const int *__restrict__ emit,
                                    const float *__restrict__ ext, float *__restrict__ out,
@@ -306,10 +307,10 @@ __global__ void fold_states_kernel(const float *__restrict__ local, const float 
     const bool fresh = seg[4 * k + (reverse ? 2 : 1)] != 0;
     if (fresh) s = ext != nullptr ? ext[(long long)seg[4 * k] * hde + idx] : 0.f;
     const int slot = emit != nullptr ? emit[k] : k;  // -1: nobody needs the state entering this piece
-    if (slot >= 0) out[slot * hde + idx] = s;
+    if (slot >= 0 && out != nullptr) out[slot * hde + idx] = s;
     const int li = seg[4 * k + 3];
     s = li >= 0 ? local[li * hde + idx] + expf(gsum[(long long)li * H + h]) * s : 0.f;
-    if (ends != nullptr) ends[k * hde + idx] = s;
+    if (ends != nullptr && seg[4 * k + (reverse ? 1 : 2)] != 0) ends[(long long)seg[4 * k] * hde + idx] = s;
   }
 }
 

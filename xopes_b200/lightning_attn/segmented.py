@@ -83,7 +83,7 @@ def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
 class _Plan:
     """Host lists and device tables of one segmentation; built once per (documents, cap, device)."""
 
-    def __init__(self, doc_bounds, cap, dev, piece_target):
+    def __init__(self, doc_bounds, cap, dev, piece_target, tail=False):
         seg_cu, first, last_of_doc = plan_segments(doc_bounds, cap)
         nseg = len(first)
         last = [0] * nseg
@@ -98,6 +98,8 @@ class _Plan:
         # reverse flow: every segment that another one precedes needs its own start state.  The
         # state-only pass runs on finer pieces than the segments (there are few segments that need
         # it, and a piece per CTA walks its tokens serially), and the fold runs over the pieces.
+        # tail: the forward flow also covers the last segment of the last document, whose end
+        # state a sequence-parallel rank publishes before its chunk pass has run.
         self.nseg, self.ndocs = nseg, len(doc_bounds)
         self.cut = nseg > len(doc_bounds)
         i64 = lambda x: torch.tensor(x, dtype=torch.int64).to(dev)  # noqa: E731
@@ -107,7 +109,7 @@ class _Plan:
         self.last_idx = i64(last_of_doc)
         self.flow = {}
         for reverse in (False, True):
-            need = [(not first[s]) if reverse else (not last[s]) for s in range(nseg)]
+            need = [(not first[s]) if reverse else (not last[s] or (tail and s == nseg - 1)) for s in range(nseg)]
             need_tokens = sum(seg_cu[s + 1] - seg_cu[s] for s in range(nseg) if need[s])
             piece = max(512, -(-need_tokens // max(1, piece_target)) // 128 * 128 + 128) if need_tokens else 512
             ranges, table, emit = [], [], []
@@ -128,20 +130,24 @@ class _Plan:
                     emit.append(s if (j == (len(cuts) - 1 if reverse else 0)) else -1)
             self.flow[reverse] = dict(n_loc=len(ranges), ranges=i64(ranges or [[0, 0]]), table=i32(table),
                                       emit=i32(emit), nunits=len(table))
+            if tail and not reverse:
+                # the units of the last document alone, as document 0 of a table of their own
+                rows = [[0] + r[1:] for r in table if r[0] == doc_of[nseg - 1]]
+                self.tail_table, self.tail_units = i32(rows), len(rows)
 
 
 _PLANS = {}
 
 
-def _plan(doc_bounds, cap, dev, h) -> _Plan:
-    key = (tuple(doc_bounds), cap, dev.type, dev.index, h)
+def _plan(doc_bounds, cap, dev, h, tail=False) -> _Plan:
+    key = (tuple(doc_bounds), cap, dev.type, dev.index, h, tail)
     p = _PLANS.get(key)
     if p is None:
         if len(_PLANS) >= 64:
             _PLANS.clear()
         # about one state-pass piece per SM: one wave fills the GPU, and every piece costs a CTA
         # ramp-up, 64 KB of state and one step of the fold
-        p = _PLANS[key] = _Plan(doc_bounds, cap, dev, max(1, num_sms(dev) // max(1, h)))
+        p = _PLANS[key] = _Plan(doc_bounds, cap, dev, max(1, num_sms(dev) // max(1, h)), tail)
     return p
 
 
@@ -193,6 +199,59 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
                              _lib.dtype_code(q), (_lib.FLAG_REQUIRE_TENSOR if pl.cut else 0) | act, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd (segmented)")
     return o, st.index_select(0, pl.last_idx)
+
+
+def lasd_forward_exchange_first(q, k, v, ld32, ld_strides, doc_bounds, cap, open_start: bool, open_end: bool,
+                                exchange):
+    """The local forward of a sequence-parallel rank with the exchange BEFORE the chunk pass.
+
+    The state-only pass also covers the end of the last document (when it continues on the next
+    rank), a fold over that document's pieces gives its end state under a zero incoming state,
+    `exchange(that state or None)` returns the true state entering the rank's first document (or
+    None), a second fold seeds every segment from true states, and the one chunk pass then writes
+    final outputs: no correction pass afterwards, and the ranks meet after the short state-only
+    pass instead of after the long chunk pass.  Arguments as lasd_forward_segmented.
+    Returns (o, end states per document, state that entered the rank or None)."""
+    lib = _lib.load()
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    pl = _plan(doc_bounds, cap, dev, h, tail=open_end)
+    fl = pl.flow[False]
+    n_loc = fl["n_loc"]
+    _, sn, sh = ld_strides
+    stream = _lib.stream_of(q)
+    local = torch.empty(max(n_loc, 1), h, d, e, dtype=torch.float32, device=dev)
+    gsum = torch.empty(max(n_loc, 1), h, dtype=torch.float32, device=dev)
+    s_end = None
+    with torch.cuda.device(dev):
+        if n_loc:
+            rc = lib.la_lasd_state_pass(_lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(fl["ranges"]),
+                                        _lib.ptr(local), _lib.ptr(gsum), 1, t, h, d, e, n_loc,
+                                        _lib.dtype_code(k), 0, 1, 0, stream)
+            _lib.check(rc, "la_lasd_state_pass")
+        if open_end:
+            s_end = torch.empty(1, h, d, e, dtype=torch.float32, device=dev)
+            rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(pl.tail_table), None, None, None,
+                                         _lib.ptr(s_end), pl.tail_units, h, d, e, 0, stream)
+            _lib.check(rc, "la_lasd_fold_states (tail)")
+    s_first = exchange(None if s_end is None else s_end[0])
+    ext = None
+    if open_start and s_first is not None:
+        ext = torch.zeros(pl.ndocs, h, d, e, dtype=torch.float32, device=dev)
+        ext[0].copy_(s_first)
+    incoming = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
+    st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.la_lasd_fold_states(_lib.ptr(local), _lib.ptr(gsum), _lib.ptr(fl["table"]), _lib.ptr(fl["emit"]),
+                                     _lib.ptr(ext), _lib.ptr(incoming), None, fl["nunits"], h, d, e, 0, stream)
+        _lib.check(rc, "la_lasd_fold_states")
+        rc = lib.la_lasd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ld32), 0, sn, sh, _lib.ptr(incoming),
+                             _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
+                             _lib.dtype_code(q), _lib.FLAG_REQUIRE_TENSOR, _lib.stream_of(q))
+        _lib.check(rc, "la_lasd_fwd (segmented)")
+    return o, st.index_select(0, pl.last_idx), (s_first if open_start else None)
 
 
 def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal_state, doc_bounds, cap,

@@ -16,6 +16,10 @@ into contiguous ranges, one per rank, and a document that crosses a cut is stitc
                          o_t += exp(cum_t) q_t^T S_in        (la_seqpar_correct)
                      to that document's local tokens and exp(G_first) S_in to its end state.
 
+On CUDA with the all-gather exchange the forward runs in another order (forward_exchange_first):
+a state-only pass over k and v yields S_loc first, the exchange follows at once, and the chunk
+pass then starts from true states, so phase 3 disappears.
+
 The backward mirrors it in the other direction (lasd_seqpar_backward): every rank runs the local
 backward with the forward state S_in it received and a zero incoming state gradient, publishes the
 state gradient leaving its FIRST document towards the previous rank (d initial_state of that
@@ -200,6 +204,12 @@ def lasd_seqpar_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: t
     plan = shard_documents(cu, start, end)
     _, _, h, d = q.shape
     e = v.shape[-1]
+    if exchange == "all_gather" and local_forward is None and correct is None and _tensor_path(q, v):
+        def gather(summary):
+            gathered = torch.empty(world * summary.numel(), dtype=torch.float32, device=summary.device)
+            exchange_summaries(gathered, summary, group)
+            return gathered.view(world, -1)
+        return forward_exchange_first(q, k, v, ld, plan, rank, gather)
     o, states, summary = local_phase(q, k, v, ld, plan, local_forward)
     if exchange == "all_gather":
         gathered = torch.empty(world * summary.numel(), dtype=torch.float32, device=summary.device)
@@ -216,6 +226,57 @@ def lasd_seqpar_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ld: t
         raise ValueError(f"unknown exchange {exchange!r}")
     correct_phase(q, o, states, ld, s_in, plan, correct)
     plan.s_in = s_in if plan.open_start else None
+    return o, states, plan
+
+
+def _tensor_path(q, v) -> bool:
+    """The local tokens can run on the tensor-core chunk kernels with 128-wide heads (what the
+    state-only pass supports)."""
+    _, t, _, d = q.shape
+    e = v.shape[-1]
+    return (q.is_cuda and d == 128 and e == 128 and t >= 128
+            and _lib.load().la_lasd_path(t, d, e, _lib.dtype_code(q), 0) == 1)
+
+
+def forward_exchange_first(q, k, v, ld, plan: ShardPlan, rank: int, gather: Callable):
+    """The forward with the ranks meeting BEFORE the chunk pass (CUDA, tensor path): a state-only
+    pass gives the end state of the rank's last document under a zero incoming state, the summaries
+    are exchanged (gather(summary) -> (world, len) tensor of all ranks' summaries), the prefix
+    fold gives the true state entering the rank, and the one chunk pass starts every local document
+    and segment from true states.  Against the three phases above this drops the correction pass,
+    and the ranks wait for each other after ~0.1 ms of local work instead of after the whole local
+    forward, so that they differ less when they meet.  Returns what lasd_seqpar_forward returns."""
+    from . import segmented as sg
+    from .scalar_decay import _prep_ld
+    _, t, h, d = q.shape
+    e = v.shape[-1]
+    dev = q.device
+    local_cu = plan.local_cu
+    bounds = [(local_cu[i], local_cu[i + 1]) for i in range(len(local_cu) - 1)]
+    sms = sg.num_sms(dev)
+    cap = sg.auto_cap(t, h, sms)
+    if not sg.worth_segmenting(bounds, h, cap, sms):
+        cap = 1 << 40  # documents as they are; only the open last one gets a state-only pass
+    ld32, strides = _prep_ld(ld, 1, t, h)
+    s_in_box = []
+
+    def exchange(s_end):
+        if plan.open_end:
+            last0 = local_cu[-2]
+            g = ld.float() * float(t - last0) if ld.dim() == 1 else _ld_local(ld, t, h)[last0:].sum(0)
+            spans = 1.0 if (plan.open_start and len(plan.doc_ids) == 1) else 0.0
+            flags = torch.tensor([1.0, spans], dtype=torch.float32).to(dev, non_blocking=True)
+            summary = torch.cat([s_end.reshape(-1), g, flags])
+        else:
+            summary = torch.zeros(h * d * e + h + 2, dtype=torch.float32, device=dev)
+        s_in = fold_incoming_state(gather(summary), rank, h, d, e)
+        s_in_box.append(s_in)
+        return s_in if plan.open_start else None
+
+    with torch.no_grad():
+        o, states, _ = sg.lasd_forward_exchange_first(q.contiguous(), k.contiguous(), v.contiguous(), ld32, strides,
+                                                      bounds, cap, plan.open_start, plan.open_end, exchange)
+    plan.s_in = s_in_box[0] if plan.open_start else None
     return o, states, plan
 
 
