@@ -56,6 +56,13 @@ enum la_dtype { LA_F32 = 0, LA_BF16 = 1, LA_F16 = 2 };
  * (the chain-rule factor sigmoid(-x) is applied where the log-decay gradient is finished).  Saves
  * the producer's pass over the decay tensor and the elementwise pass of its backward. */
 #define LA_FLAG_LD_LOGSIGMOID 4u
+/* Vector decay only: ldk / ldv point to 16-bit values of the type of q, k, v (what the reference's
+ * benchmark passes, benchmarks/lightning_attention/benchmark.py:315-316) although the parameters
+ * are declared `const float *`; the kernels widen them where they read them, so the decay tensor
+ * costs 2 bytes per value in every pass instead of a conversion pass plus 4.  dldk / dldv stay
+ * fp32.  Rejected with LA_ERR_UNSUPPORTED for fp32 inputs.  The decode entry points take fp32
+ * decays only. */
+#define LA_FLAG_LD_16BIT 8u
 
 /* Library identification; bumps when the ABI changes. */
 LA_API int la_abi_version(void);

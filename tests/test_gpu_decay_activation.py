@@ -141,3 +141,62 @@ def test_decay_activation_argument_checks():
     with pytest.raises(ValueError):
         xb.lightning_attn_func(q, q, q, ld=torch.zeros(2, device=DEV), decay_type="constant",
                                decay_activation="logsigmoid")
+
+
+# ------------------------------------------------------------------------------------------------
+# decays given in the 16-bit type of q, k, v (benchmarks/lightning_attention/benchmark.py:315-316):
+# the kernels read them as they are.  Oracle: the same (exactly representable) values in fp32.
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,dtype,use_ldv,act,mild", [
+    ((2, 130, 2, 64, 32), torch.bfloat16, True, False, True),      # scan kernels, ldk and ldv
+    ((2, 130, 2, 64, 32), torch.float16, True, True, True),        # scan kernels, activation fused
+    ((1, 515, 2, 128, 128), torch.bfloat16, False, False, True),   # tensor path, ragged last chunk
+    ((1, 515, 2, 128, 128), torch.float16, False, True, True),     # tensor path, activation fused
+    ((2, 2048, 2, 128, 128), torch.bfloat16, False, False, False), # the benchmark's decay: two reference rows
+    ((1, 4096, 2, 128, 128), torch.bfloat16, False, False, True),  # cut into segments (state-only pass)
+])
+def test_lavd_decays_in_16_bit(shape, dtype, use_ldv, act, mild):
+    import xopes_b200 as xb
+    b, n, h, d, e = shape
+    g, qf, kf, vf, dof = _qkv(b, n, h, d, e, dtype, 73)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    if act:   # pre-activations, rounded to the 16-bit type
+        xk = cast(2.0 * torch.randn(b, n, h, d, generator=g) + 4.0)
+        xv = cast(2.0 * torch.randn(b, n, h, e, generator=g) + 4.0) if use_ldv else None
+        ldk = F.logsigmoid(xk.double()).float()
+        ldv = F.logsigmoid(xv.double()).float() if use_ldv else None
+    else:
+        xk = cast(F.logsigmoid(torch.randn(b, n, h, d, generator=g)) / (16.0 if mild else 1.0))
+        xv = cast(F.logsigmoid(torch.randn(b, n, h, e, generator=g) + 1) / 4.0) if use_ldv else None
+        ldk, ldv = xk, xv
+    s0 = 0.1 * torch.randn(b, h, d, e, generator=g)
+    dsf = torch.randn(b, h, d, e, generator=g)
+    q, k, v, xkc, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(xk, dtype), leaf(s0)
+    xvc = leaf(xv, dtype) if use_ldv else None
+    o, sf = xb.lavd_fn(q, k, v, ldk=xkc, ldv=xvc, initial_state=s0c,
+                       decay_activation="logsigmoid" if act else None)
+    ro, rsf = orc.lavd_forward(qf, kf, vf, ldk, ldv, s0)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rlk, rlv, rs0 = orc.lavd_backward(qf, kf, vf, ldk, ldv, dof, s0, dsf)
+    assert xkc.grad.dtype == dtype
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    chain = (lambda r, x: (r.double() * torch.sigmoid(-x.double())).float()) if act else (lambda r, x: r)
+    assert_close("dldk", chain(rlk, xk), xkc.grad.float(), TOL_BF16)
+    if use_ldv:
+        assert_close("dldv", chain(rlv, xv), xvc.grad.float(), TOL_BF16)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
+def test_16_bit_decays_are_rejected_for_fp32_inputs_at_the_c_abi():
+    from xopes_b200 import _lib
+    lib = _lib.load()
+    t = torch.zeros(1, 128, 1, 128, device=DEV)
+    o, sf = torch.empty_like(t), torch.empty(1, 1, 128, 128, device=DEV)
+    rc = lib.la_lavd_fwd(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), None, None, None, o.data_ptr(),
+                         sf.data_ptr(), 1, 128, 1, 128, 128, 0, _lib.LA_F32, _lib.FLAG_LD_16BIT,
+                         torch.cuda.current_stream().cuda_stream)
+    assert rc == -3  # LA_ERR_UNSUPPORTED

@@ -15,6 +15,7 @@ LA_F32, LA_BF16, LA_F16 = 0, 1, 2
 FLAG_FORCE_RECURRENCE = 1
 FLAG_REQUIRE_TENSOR = 2
 FLAG_LD_LOGSIGMOID = 4
+FLAG_LD_16BIT = 8
 
 _DTYPES = {torch.float32: LA_F32, torch.bfloat16: LA_BF16, torch.float16: LA_F16}
 

@@ -138,10 +138,11 @@ void rows_d(ScanParams &p, const Seq &s, const float *ldk, const float *ldv) {
 int scan_forward(const Seq &s, const void *q, const void *k, const void *v, const float *ld,
                  int64_t sb, int64_t sn, int64_t sh, const float *ldk, const float *ldv,
                  const float *s0, void *o, float *sfin, int dtype, cudaStream_t st,
-                 const int *enable = nullptr, int ld_act = 0) {
+                 const int *enable = nullptr, int ld_act = 0, int ld16 = 0) {
   ScanParams p = base_params(s, ld, sb, sn, sh);
   p.enable = enable;
   p.ld_act = ld_act;
+  p.ld16 = ld16;
   rows_e(p, s, ldk, ldv);
   p.a = v; p.b = k; p.w = q; p.out = o; p.t0 = s0; p.tfinal = sfin;
   return launch_scan(p, dtype, st);
@@ -430,6 +431,8 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
   int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc != LA_OK) return rc;
   if (o == nullptr || (ldk == nullptr && ldv == nullptr)) return LA_ERR_NULL_POINTER;
+  const int ld16 = (flags & LA_FLAG_LD_16BIT) ? 1 : 0;
+  if (ld16 && dtype == LA_F32) return LA_ERR_UNSUPPORTED;  // the decays take the 16-bit type of q, k, v
   const int path = la_lavd_path(N, D, E, dtype, ldk != nullptr, ldv != nullptr, flags);
   if (path < 0) return path;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -443,6 +446,7 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
     c.x = q; c.y = k; c.z = v; c.ldk = ldk; c.out = o; c.t0 = initial_state; c.tfinal = final_state;
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
+    c.ld16 = ld16;
     if ((rc = launch_lavd_pass(c, dtype, st)) != LA_OK) return rc;
     // the two-reference kernels run only if a chunk left the one-reference range ...
     c.ref2 = 1; c.enable = unsafe; c.unsafe = unsafe + 1;
@@ -450,7 +454,7 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
     enable = unsafe + 1;  // ... and the scan below only if one left theirs too
   }
   return scan_forward(s, q, k, v, nullptr, 0, 0, 0, ldk, ldv, initial_state, o, final_state, dtype, st,
-                      enable, (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0);
+                      enable, (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0, ld16);
 }
 
 int64_t la_lavd_bwd_workspace_bytes(int64_t B, int64_t N, int64_t H, int64_t D, int64_t E,
@@ -471,6 +475,8 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return LA_ERR_NULL_POINTER;
   if (ldk == nullptr && ldv == nullptr) return LA_ERR_NULL_POINTER;
   if ((ldk != nullptr && dldk == nullptr) || (ldv != nullptr && dldv == nullptr)) return LA_ERR_NULL_POINTER;
+  const int ld16 = (flags & LA_FLAG_LD_16BIT) ? 1 : 0;
+  if (ld16 && dtype == LA_F32) return LA_ERR_UNSUPPORTED;  // the decays take the 16-bit type of q, k, v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Seq s{(int)B, (int)N, (int)H, (int)D, (int)E, (int)M, cu_seqlens};
   float *ws_state = nullptr;
@@ -488,6 +494,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     if (cudaMemsetAsync(unsafe, 0, 2 * sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
     c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
+    c.ld16 = ld16;
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
     // with the other two passes, so while one CTA per (sequence, head) leaves SMs idle it runs
@@ -563,6 +570,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     p = base_params(s, nullptr, 0, 0, 0);
     p.enable = enable;
     p.ld_act = ld_act;
+    p.ld16 = ld16;
     rows_e(p, s, ldk, ldv);
     p.a = v; p.b = k; p.w = q; p.out = nullptr; p.t0 = initial_state;
     p.x = d_o; p.xout = dldv; p.xmode = 2;
@@ -572,6 +580,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
   p.ld_act = ld_act;
+  p.ld16 = ld16;
   rows_d(p, s, ldk, ldv);
   p.a = k; p.b = v; p.w = d_o; p.out = dq; p.t0 = initial_state; p.tfinal = ws_state;
   if (ldk != nullptr) { p.x = q; p.xout = dldk; p.xmode = 2; }
@@ -580,6 +589,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
   p.ld_act = ld_act;
+  p.ld16 = ld16;
   rows_d(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = q; p.b = d_o; p.w = v; p.out = dk; p.t0 = dfinal_state; p.tfinal = dinitial_state;
@@ -589,6 +599,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   p = base_params(s, nullptr, 0, 0, 0);
   p.enable = enable;
   p.ld_act = ld_act;
+  p.ld16 = ld16;
   rows_e(p, s, ldk, ldv);
   p.reverse = 1;
   p.a = d_o; p.b = q; p.w = k; p.out = dv; p.t0 = dfinal_state;
@@ -596,12 +607,12 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
   if ((rc = launch_scan(p, dtype, st)) != LA_OK) return rc;
   if (ldk != nullptr) {
     rc = launch_revcumsum_vec(dldk, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.D, s.D,
-                              s.E, 1, s.M, st, ld_act ? ldk : nullptr);
+                              s.E, 1, s.M, st, ld_act ? ldk : nullptr, ld16 ? dtype : LA_F32);
     if (rc != LA_OK) return rc;
   }
   if (ldv != nullptr) {
     rc = launch_revcumsum_vec(dldv, ws_state, dfinal_state, cu_seqlens, s.B, s.N, s.H, s.E, s.D,
-                              s.E, 0, s.M, st, ld_act ? ldv : nullptr);
+                              s.E, 0, s.M, st, ld_act ? ldv : nullptr, ld16 ? dtype : LA_F32);
     if (rc != LA_OK) return rc;
   }
   return LA_OK;
@@ -681,6 +692,7 @@ int la_lavd_state_pass(const void *y, const void *z, const float *ldk, const int
   p.y = y; p.z = z; p.ldv = ldk; p.cu = cu_seqlens; p.states = states; p.gsum = gsum;
   p.B = (int)B; p.N = (int)N; p.H = (int)H; p.M = (int)M; p.reverse = reverse != 0; p.ranges = ranges != 0;
   p.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
+  p.ld16 = (flags & LA_FLAG_LD_16BIT) ? 1 : 0;
   return launch_state_pass_vec(p, dtype, static_cast<cudaStream_t>(stream));
 }
 

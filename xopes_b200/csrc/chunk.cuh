@@ -63,6 +63,7 @@ struct LavdPass {
   int B = 0, N = 0, H = 0, M = 0;
   int *unsafe = nullptr;
   int ld_act = 0;    // 1: ldk holds pre-activations, the log decay is logsigmoid(ldk)
+  int ld16 = 0;      // 1: ldk points to 16-bit values of the type of x, y, z
   int ref2 = 0;
   const int *enable = nullptr;  // optional device word: the launch does nothing while it reads 0
 };
@@ -84,6 +85,7 @@ struct StatePass {
   float *gsum = nullptr;                   // (nb,H) fp32 (scalar) / (nb,H,128) (vector), optional
   int B = 0, N = 0, H = 0, M = 0, reverse = 0;
   int ld_act = 0;  // 1: ld / ldv hold pre-activations, the log decay is their logsigmoid
+  int ld16 = 0;    // 1 (vector pass only): ldv points to 16-bit values of the type of y, z
   int ranges = 0;  // 1: cu holds M (begin, end) token ranges instead of M + 1 boundaries
 };
 int launch_state_pass(const StatePass &p, int dtype, cudaStream_t stream);

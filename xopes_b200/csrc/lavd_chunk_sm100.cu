@@ -134,6 +134,7 @@ struct LavdArgs {
   int *unsafe;
   const int *enable;  // optional device word: the kernel does nothing while it reads 0
   int ld_act;         // 1: the decay tensor holds pre-activations x and the log decay is logsigmoid(x)
+  int ld16;           // 1: the decay tensor has the 16-bit type of x, y, z (half the bytes per chunk)
 };
 
 // byte offset of the float4 holding features [d, d+4) of row i in the 128B-swizzled fp32 decay tile
@@ -362,9 +363,15 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       auto load_ck = [&](int tok0, uint32_t par, uint32_t dst) {
         mbar_wait(empty_ck, par ^ 1u, abort_flag, a.status, kStEmpty);
         if (*abort_flag) return false;
-        mbar_arrive_expect_tx(full_ck, TMODE ? kCkBytes + kTileBytes : kCkBytes);
+        const int ck_bytes = a.ld16 ? kCkBytes / 2 : kCkBytes;
+        mbar_arrive_expect_tx(full_ck, TMODE ? ck_bytes + kTileBytes : ck_bytes);
+        if (a.ld16) {  // two boxes of 64 16-bit features into the first half of the slot
+          tma_load_4d(dst, &map_ld, full_ck, 0, h, tok0, bidx);
+          tma_load_4d(dst + kBoxBytes, &map_ld, full_ck, 64, h, tok0, bidx);
+        } else {
 #pragma unroll
-        for (int gq = 0; gq < 4; ++gq) tma_load_4d(dst + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+          for (int gq = 0; gq < 4; ++gq) tma_load_4d(dst + gq * kBoxBytes, &map_ld, full_ck, 32 * gq, h, tok0, bidx);
+        }
         if (TMODE) {
           // T mode keeps Z in a tile of its own (free like the decay slot once the previous
           // chunk's products are done), so the rescale of the next chunk never waits for the store
@@ -409,8 +416,13 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tma_prefetch_4d(&map_y, 64, h, tokp, bidx);
           tma_prefetch_4d(&map_z, 0, h, tokp, bidx);
           tma_prefetch_4d(&map_z, 64, h, tokp, bidx);
+          if (a.ld16) {
+            tma_prefetch_4d(&map_ld, 0, h, tokp, bidx);
+            tma_prefetch_4d(&map_ld, 64, h, tokp, bidx);
+          } else {
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq) tma_prefetch_4d(&map_ld, 32 * gq, h, tokp, bidx);
+            for (int gq = 0; gq < 4; ++gq) tma_prefetch_4d(&map_ld, 32 * gq, h, tokp, bidx);
+          }
         }
       }
       sm->issued[0] = n_ck;
@@ -612,28 +624,32 @@ lavd_pass_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         // store per row and no read-back
         float4 acc16[16];
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!a.ld_act) {
+        // first sweep, one instantiation per (16-bit input, activation): the plain fp32 path keeps
+        // its two instructions per value.  A 16-bit tile fills the first half of the slot only; the
+        // second sweep below overwrites the whole slot with fp32 sums after every thread has read.
+        auto sweep = [&](auto mode) {
+          constexpr int kMode = decltype(mode)::value;
 #pragma unroll
           for (int r = 0; r < 16; ++r) {
             const int row = seg * 16 + r;  // row & 7 == r & 7
             if (row < L) {
-              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-              run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
-              run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
+              const float4 v = decay_quad<T, (kMode & 2) != 0>(ck, row, d0, kBoxBytes);
+              if (kMode & 1) {  // the tile holds pre-activations of a logsigmoid
+                run.x += log2_sigmoid(v.x); run.y += log2_sigmoid(v.y);
+                run.z += log2_sigmoid(v.z); run.w += log2_sigmoid(v.w);
+              } else {
+                run.x = fmaf(v.x, kLog2e, run.x); run.y = fmaf(v.y, kLog2e, run.y);
+                run.z = fmaf(v.z, kLog2e, run.z); run.w = fmaf(v.w, kLog2e, run.w);
+              }
             }
             acc16[r] = run;
           }
-        } else {  // the tile holds pre-activations of a logsigmoid
-#pragma unroll
-          for (int r = 0; r < 16; ++r) {
-            const int row = seg * 16 + r;
-            if (row < L) {
-              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-              run.x += log2_sigmoid(v.x); run.y += log2_sigmoid(v.y);
-              run.z += log2_sigmoid(v.z); run.w += log2_sigmoid(v.w);
-            }
-            acc16[r] = run;
-          }
+        };
+        switch ((a.ld16 ? 2 : 0) | (a.ld_act ? 1 : 0)) {
+          case 0: sweep(std::integral_constant<int, 0>{}); break;
+          case 1: sweep(std::integral_constant<int, 1>{}); break;
+          case 2: sweep(std::integral_constant<int, 2>{}); break;
+          default: sweep(std::integral_constant<int, 3>{}); break;
         }
         *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = run;
         named_bar_sync(1, kComputeThreads);
@@ -1075,7 +1091,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   if ((rc = make_map(&mx, p.x, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&mz, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&ml, p.ldk, LA_F32, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&ml, p.ldk, p.ld16 ? dtype : LA_F32, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&mo, p.out, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if (p.dld != nullptr && ((reinterpret_cast<uintptr_t>(p.xrow) | reinterpret_cast<uintptr_t>(p.dld)) & 15u))
     return LA_ERR_MISALIGNED;
@@ -1092,6 +1108,7 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
   a.unsafe = p.unsafe;
   a.enable = p.enable;
   a.ld_act = p.ld_act;
+  a.ld16 = p.ld16;
   if (a.status == nullptr || a.unsafe == nullptr) return LA_ERR_CUDA;
   auto kern = lavd_pass_kernel<T, TMODE, REF2>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)

@@ -94,7 +94,10 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
       if (gr < R) {
         av = Cvt<T>::to_f(a[base]);
         if (x != nullptr) xv = Cvt<T>::to_f(x[base]);
-        if (has_ldr) dv = p.ld_act ? 1.f / (1.f + expf(-p.ldr[base])) : expf(p.ldr[base]);
+        if (has_ldr) {
+          const float raw = p.ld16 ? Cvt<T>::to_f(reinterpret_cast<const T *>(p.ldr)[base]) : p.ldr[base];
+          dv = p.ld_act ? 1.f / (1.f + expf(-raw)) : expf(raw);
+        }
       }
       a_s[idx] = av;
       x_s[idx] = xv;
@@ -107,7 +110,10 @@ __global__ void __launch_bounds__(256) scan_kernel(ScanParams p, int TB) {
       if (c < C) {
         bv = Cvt<T>::to_f(b[base]);
         wv = Cvt<T>::to_f(w[base]);
-        if (has_ldc) dv = p.ld_act ? 1.f / (1.f + expf(-p.ldc[base])) : expf(p.ldc[base]);
+        if (has_ldc) {
+          const float raw = p.ld16 ? Cvt<T>::to_f(reinterpret_cast<const T *>(p.ldc)[base]) : p.ldc[base];
+          dv = p.ld_act ? 1.f / (1.f + expf(-raw)) : expf(raw);
+        }
       }
       b_s[idx] = bv;
       w_s[idx] = wv;
@@ -359,7 +365,8 @@ constexpr int kRcRows = 16;
 
 __global__ void __launch_bounds__(512, 2) revcumsum_vec_kernel(float *buf, const float *sfin, const float *dsfin,
                                                              const int64_t *cu, int N, int H, int F, int Fpad,
-                                                             int D, int E, int f_is_row, const float *act_x) {
+                                                             int D, int E, int f_is_row, const float *act_x,
+                                                             int act_dtype) {
   extern __shared__ float part[];  // [2][lanes][Fpad] + [Fpad]
   const int h = blockIdx.x, seq = blockIdx.y;
   const int lanes = blockDim.x / Fpad;
@@ -371,7 +378,13 @@ __global__ void __launch_bounds__(512, 2) revcumsum_vec_kernel(float *buf, const
   const bool on = f < F;
   const int fc = on ? f : 0;
   float *ptr = buf + ((bidx * N) * H + h) * (int64_t)F + fc;
-  const float *xptr = act_x != nullptr ? act_x + ((bidx * N) * H + h) * (int64_t)F + fc : nullptr;
+  // element offset; the pre-activations may be fp32 or 16-bit
+  const int64_t xoff = ((bidx * N) * H + h) * (int64_t)F + fc;
+  auto xval = [&](int64_t idx) -> float {
+    if (act_dtype == LA_F32) return act_x[idx];
+    if (act_dtype == LA_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(act_x)[idx]);
+    return __half2float(reinterpret_cast<const __half *>(act_x)[idx]);
+  };
 
   // the state term starts the running sum: sum over the other index of final_state * d final_state,
   // formed by the whole CTA with coalesced reads and left in term[Fpad]
@@ -412,7 +425,7 @@ __global__ void __launch_bounds__(512, 2) revcumsum_vec_kernel(float *buf, const
   const int len = (int)(t_end - t_begin);
   const int tile = lanes * kRcRows;
   float *base = ptr + t_begin * stride;
-  const float *xbase = xptr != nullptr ? xptr + t_begin * stride : nullptr;
+  const int64_t xbase = xoff + t_begin * stride;
   auto load = [&](int r0, float (&v)[kRcRows]) {
     const float *pc = base + (int64_t)r0 * stride;
 #pragma unroll
@@ -440,18 +453,18 @@ __global__ void __launch_bounds__(512, 2) revcumsum_vec_kernel(float *buf, const
     carry += tot;
     if (on) {
       float *pc = base + (int64_t)r0 * stride;
-      if (xbase == nullptr) {
+      if (act_x == nullptr) {
 #pragma unroll
         for (int i = 0; i < kRcRows; ++i, pc -= stride) {
           run += cur[i];
           if (r0 - i >= 0) *pc = run;
         }
       } else {  // d logsigmoid(x) / dx = sigmoid(-x)
-        const float *xc = xbase + (int64_t)r0 * stride;
+        int64_t xc = xbase + (int64_t)r0 * stride;
 #pragma unroll
         for (int i = 0; i < kRcRows; ++i, pc -= stride, xc -= stride) {
           run += cur[i];
-          if (r0 - i >= 0) *pc = run / (1.f + expf(*xc));
+          if (r0 - i >= 0) *pc = run / (1.f + expf(xval(xc)));
         }
       }
     }
@@ -477,7 +490,7 @@ int launch_dld_scalar(const float *slots_q, int ntq, const float *slots_k, int n
 
 int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfinal_state,
                          const int64_t *cu, int B, int N, int H, int F, int D, int E, int f_is_row,
-                         int M, cudaStream_t stream, const float *act_x) {
+                         int M, cudaStream_t stream, const float *act_x, int act_dtype) {
   const int nb = cu ? M : B;
   int fpad = ((F + 31) / 32) * 32;
   if (fpad > 1024) return LA_ERR_UNSUPPORTED;
@@ -490,7 +503,7 @@ int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfin
   const int lanes = 512 / fpad;
   const size_t smem = sizeof(float) * (2 * (size_t)lanes + 1) * fpad;
   revcumsum_vec_kernel<<<grid, lanes * fpad, smem, stream>>>(buf, final_state, dfinal_state, cu, N, H, F, fpad,
-                                                             D, E, f_is_row, act_x);
+                                                             D, E, f_is_row, act_x, act_dtype);
   return launch_status();
 }
 

@@ -34,6 +34,7 @@ struct ScanParams {
   int B = 0, N = 0, H = 0, R = 0, C = 0, M = 0;
   int reverse = 0;
   int ld_act = 0;  // 1: ld / ldr / ldc hold pre-activations x and the decay factor is sigmoid(x) = exp(logsigmoid(x))
+  int ld16 = 0;    // 1: ldr / ldc point to 16-bit values of the kernel's element type (ld stays fp32)
   const int *enable = nullptr;  // optional device word: the kernel does nothing while it is 0
 };
 
@@ -52,11 +53,11 @@ int launch_dld_scalar(const float *slots_q, int ntq, const float *slots_k, int n
 
 // In place: buf[b,t,h,f] <- sum_{s>=t} buf[b,s,h,f] + sum over the other state axis of S_fin*dS_fin.
 // f_is_row: f indexes the state's D axis (sum over E) else its E axis (sum over D).
-// act_x (optional, same layout as buf): the decay was logsigmoid(act_x); the result is then the
-// gradient with respect to act_x.
+// act_x (optional, same layout as buf, elements of type act_dtype): the decay was
+// logsigmoid(act_x); the result is then the gradient with respect to act_x.
 int launch_revcumsum_vec(float *buf, const float *final_state, const float *dfinal_state,
                          const int64_t *cu, int B, int N, int H, int F, int D, int E, int f_is_row,
-                         int M, cudaStream_t stream, const float *act_x = nullptr);
+                         int M, cudaStream_t stream, const float *act_x = nullptr, int act_dtype = LA_F32);
 
 int launch_decode(const void *q, const void *k, const void *v, const float *ld, int64_t ld_sb,
                   int64_t ld_sh, const float *ldk, const float *ldv, const float *state_in,

@@ -379,7 +379,7 @@ struct StateVecArgs {
   const long long *cu;
   float *states;  // (nb, H, 128, 128)
   float *gsum;    // (nb, H, 128) total log decay per feature (natural log)
-  int B, N, H, M, reverse, ranges, ld_act;
+  int B, N, H, M, reverse, ranges, ld_act, ld16;
   int *status;
 };
 
@@ -455,10 +455,15 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
         const int tok0 = (int)t_begin + n * kChunk;
         mbar_wait(empty_ck + 8 * sc, phc ^ 1u, abort_flag, a.status, kStEmptyV);
         if (*abort_flag) break;
-        mbar_arrive_expect_tx(full_ck + 8 * sc, kCkBytes);
+        mbar_arrive_expect_tx(full_ck + 8 * sc, a.ld16 ? kCkBytes / 2 : kCkBytes);
+        if (a.ld16) {  // two boxes of 64 16-bit features into the first half of the slot
+          tma_load_4d(base + kOffCk + sc * kCkBytes, &map_ld, full_ck + 8 * sc, 0, h, tok0, bidx);
+          tma_load_4d(base + kOffCk + sc * kCkBytes + kBoxBytes, &map_ld, full_ck + 8 * sc, 64, h, tok0, bidx);
+        } else {
 #pragma unroll
-        for (int gq = 0; gq < 4; ++gq)
-          tma_load_4d(base + kOffCk + sc * kCkBytes + gq * kBoxBytes, &map_ld, full_ck + 8 * sc, 32 * gq, h, tok0, bidx);
+          for (int gq = 0; gq < 4; ++gq)
+            tma_load_4d(base + kOffCk + sc * kCkBytes + gq * kBoxBytes, &map_ld, full_ck + 8 * sc, 32 * gq, h, tok0, bidx);
+        }
         n_ck = it + 1;
         mbar_wait(empty_yz + 8 * s, ph ^ 1u, abort_flag, a.status, kStEmptyV);
         if (*abort_flag) break;
@@ -516,28 +521,31 @@ state_pass_vec_kernel(const __grid_constant__ CUtensorMap map_y, const __grid_co
         const uint32_t c4 = (uint32_t)((d0 & 31) >> 2);
         float4 acc16[16];
         float4 runv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!a.ld_act) {
+        // one instantiation per (16-bit input, activation); a 16-bit tile fills the first half of
+        // the slot, the second sweep overwrites the whole slot after every thread has read
+        auto sweep = [&](auto mode) {
+          constexpr int kMode = decltype(mode)::value;
 #pragma unroll
           for (int r = 0; r < 16; ++r) {
             const int row = seg * 16 + r;
             if (row < L) {
-              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-              runv.x = fmaf(v.x, kLog2e, runv.x); runv.y = fmaf(v.y, kLog2e, runv.y);
-              runv.z = fmaf(v.z, kLog2e, runv.z); runv.w = fmaf(v.w, kLog2e, runv.w);
+              const float4 v = decay_quad<T, (kMode & 2) != 0>(ck, row, d0, kBoxBytes);
+              if (kMode & 1) {  // the tile holds pre-activations of a logsigmoid
+                runv.x += log2_sigmoid(v.x); runv.y += log2_sigmoid(v.y);
+                runv.z += log2_sigmoid(v.z); runv.w += log2_sigmoid(v.w);
+              } else {
+                runv.x = fmaf(v.x, kLog2e, runv.x); runv.y = fmaf(v.y, kLog2e, runv.y);
+                runv.z = fmaf(v.z, kLog2e, runv.z); runv.w = fmaf(v.w, kLog2e, runv.w);
+              }
             }
             acc16[r] = runv;
           }
-        } else {  // the tile holds pre-activations of a logsigmoid
-#pragma unroll
-          for (int r = 0; r < 16; ++r) {
-            const int row = seg * 16 + r;
-            if (row < L) {
-              const float4 v = *reinterpret_cast<const float4 *>(ck + colbase + (uint32_t)row * 128u + ((c4 ^ (uint32_t)(r & 7)) << 4));
-              runv.x += log2_sigmoid(v.x); runv.y += log2_sigmoid(v.y);
-              runv.z += log2_sigmoid(v.z); runv.w += log2_sigmoid(v.w);
-            }
-            acc16[r] = runv;
-          }
+        };
+        switch ((a.ld16 ? 2 : 0) | (a.ld_act ? 1 : 0)) {
+          case 0: sweep(std::integral_constant<int, 0>{}); break;
+          case 1: sweep(std::integral_constant<int, 1>{}); break;
+          case 2: sweep(std::integral_constant<int, 2>{}); break;
+          default: sweep(std::integral_constant<int, 3>{}); break;
         }
         *reinterpret_cast<float4 *>(&segtot[seg * 128 + d0]) = runv;
         const float4 far = *reinterpret_cast<const float4 *>(&run[d0]);  // decay between this chunk and the far end
@@ -635,13 +643,14 @@ int launch_vec_t(const StatePass &p, int dtype, cudaStream_t stream) {
   int rc;
   if ((rc = make_map(&my, p.y, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
   if ((rc = make_map(&mz, p.z, dtype, p.B, p.N, p.H)) != LA_OK) return rc;
-  if ((rc = make_map(&ml, p.ldv, LA_F32, p.B, p.N, p.H)) != LA_OK) return rc;
+  if ((rc = make_map(&ml, p.ldv, p.ld16 ? dtype : LA_F32, p.B, p.N, p.H)) != LA_OK) return rc;
   if (reinterpret_cast<uintptr_t>(p.states) & 15u) return LA_ERR_MISALIGNED;
   vec::StateVecArgs a;
   a.cu = reinterpret_cast<const long long *>(p.cu);
   a.states = p.states; a.gsum = p.gsum;
   a.B = p.B; a.N = p.N; a.H = p.H; a.M = p.M; a.reverse = p.reverse; a.ranges = p.ranges;
   a.ld_act = p.ld_act;
+  a.ld16 = p.ld16;
   a.status = status_word_ptr();
   if (a.status == nullptr) return LA_ERR_CUDA;
   auto kern = state_pass_vec_kernel<T>;

@@ -2,6 +2,7 @@
 // construction.
 #pragma once
 #include <cuda.h>
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -44,6 +45,22 @@ template <> struct Fmt<__half> {
     return *reinterpret_cast<const uint32_t *>(&r);
   }
 };
+
+// Four consecutive features of one row of a decay tile as TMA left it in shared memory (128-byte
+// swizzle, rows of 128 bytes): fp32 tiles are four boxes of 32 features, 16-bit tiles two boxes of
+// 64.  d0 is a multiple of 4; box_bytes is the size of one box (128 rows x 128 B).
+template <typename T, bool LD16>
+__device__ __forceinline__ float4 decay_quad(const uint8_t *tile, int row, int d0, uint32_t box_bytes) {
+  if (!LD16) {
+    return *reinterpret_cast<const float4 *>(tile + (uint32_t)(d0 >> 5) * box_bytes + (uint32_t)row * 128u +
+                                             ((uint32_t)(((d0 & 31) >> 2) ^ (row & 7)) << 4));
+  }
+  const uint2 raw = *reinterpret_cast<const uint2 *>(tile + (uint32_t)(d0 >> 6) * box_bytes + (uint32_t)row * 128u +
+                                                     ((uint32_t)(((d0 & 63) >> 3) ^ (row & 7)) << 4) +
+                                                     (uint32_t)((d0 & 4) << 1));
+  const float2 lo = Fmt<T>::unpack(raw.x), hi = Fmt<T>::unpack(raw.y);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
 
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }

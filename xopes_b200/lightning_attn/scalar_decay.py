@@ -114,10 +114,12 @@ class LasdFunction(torch.autograd.Function):
         if seg is not None:
             from .segmented import lasd_forward_segmented
             bounds, cap, ld_flat, strides = seg
-            o, sf = lasd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e),
-                                           ld_flat, strides, s0, bounds, cap, flags & _lib.FLAG_LD_LOGSIGMOID)
+            o, sf, s_seg = lasd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d),
+                                                  v.view(1, b * n, h, e), ld_flat, strides, s0, bounds, cap,
+                                                  flags & _lib.FLAG_LD_LOGSIGMOID)
             o = o.view(b, n, h, e)
-            ctx.save_for_backward(q, k, v, ld, s0, cu)
+            # the states entering the segments (64 KB per segment and head) are kept for the backward
+            ctx.save_for_backward(q, k, v, ld, s0, cu, s_seg)
             ctx.flags = flags
             ctx.seg = (bounds, cap, strides)
             ctx.state_dtype = None if initial_state is None else initial_state.dtype
@@ -130,7 +132,7 @@ class LasdFunction(torch.autograd.Function):
                                  _lib.ptr(s0), _lib.ptr(cu), _lib.ptr(o), _lib.ptr(sf),
                                  b, n, h, d, e, m, _lib.dtype_code(q), flags, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd")
-        ctx.save_for_backward(q, k, v, ld, s0, cu)
+        ctx.save_for_backward(q, k, v, ld, s0, cu, None)
         ctx.flags = flags
         ctx.seg = None
         ctx.state_dtype = None if initial_state is None else initial_state.dtype
@@ -140,7 +142,7 @@ class LasdFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dfinal_state):
         lib = _lib.load()
-        q, k, v, ld, s0, cu = ctx.saved_tensors
+        q, k, v, ld, s0, cu, s_seg = ctx.saved_tensors
         b, n, h, d = q.shape
         e = v.shape[-1]
         m = 0 if cu is None else cu.numel() - 1
@@ -159,7 +161,7 @@ class LasdFunction(torch.autograd.Function):
             dq, dk, dv, dld, ds0 = lasd_backward_segmented(
                 q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), ld32, strides, s0,
                 do.view(1, b * n, h, e), dsf, bounds, cap, want_dld, want_ds0,
-                ctx.flags & _lib.FLAG_LD_LOGSIGMOID)
+                ctx.flags & _lib.FLAG_LD_LOGSIGMOID, s_in=s_seg)
             dq, dk, dv = dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e)
             if want_dld:
                 dld = dld.view(b, n, h)

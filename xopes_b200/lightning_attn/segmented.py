@@ -183,7 +183,8 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
     ld32 fp32 with element strides over (stream token, head) = ld_strides[1:]; doc_bounds the
     sequences [(a, b), ...] in stream order; initial_state (ndocs, H, 128, 128) fp32 or None;
     act = FLAG_LD_LOGSIGMOID when ld32 holds pre-activations of a logsigmoid, else 0.
-    Returns (o (1,T,H,128), final states (ndocs,H,128,128) fp32)."""
+    Returns (o (1,T,H,128), final states (ndocs,H,128,128) fp32, the states entering the segments:
+    the backward takes them back as s_in instead of running the state-only pass again)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
@@ -198,7 +199,7 @@ def lasd_forward_segmented(q, k, v, ld32, ld_strides, initial_state, doc_bounds,
                              _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
                              _lib.dtype_code(q), (_lib.FLAG_REQUIRE_TENSOR if pl.cut else 0) | act, _lib.stream_of(q))
         _lib.check(rc, "la_lasd_fwd (segmented)")
-    return o, st.index_select(0, pl.last_idx)
+    return o, st.index_select(0, pl.last_idx), s_in
 
 
 def lasd_forward_exchange_first(q, k, v, ld32, ld_strides, doc_bounds, cap, open_start: bool, open_end: bool,
@@ -255,15 +256,17 @@ def lasd_forward_exchange_first(q, k, v, ld32, ld_strides, doc_bounds, cap, open
 
 
 def lasd_backward_segmented(q, k, v, ld32, ld_strides, initial_state, do, dfinal_state, doc_bounds, cap,
-                            want_dld: bool, want_ds0: bool, act: int = 0):
+                            want_dld: bool, want_ds0: bool, act: int = 0, s_in=None):
     """Backward twin: q, k, v, do (1, T, H, 128); initial_state / dfinal_state (ndocs, H, 128, 128)
-    fp32 or None.  Returns (dq, dk, dv, dld (1,T,H) fp32 or None, dinitial_state (ndocs,...) or None)."""
+    fp32 or None; s_in: the forward's segment-entering states if it kept them.
+    Returns (dq, dk, dv, dld (1,T,H) fp32 or None, dinitial_state (ndocs,...) or None)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False, act=act)
+    if s_in is None:
+        s_in = _incoming_states(lib, k, v, ld32, ld_strides, pl, initial_state, reverse=False, act=act)
     ds_out = _incoming_states(lib, q, do, ld32, ld_strides, pl, dfinal_state, reverse=True, act=act)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dld = torch.empty(1, t, h, dtype=torch.float32, device=dev) if want_dld else None
@@ -312,16 +315,16 @@ def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool, act: int
 
 
 def lavd_forward_segmented(q, k, v, ldk, initial_state, doc_bounds, cap, flags):
-    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32, all contiguous; flags as for
-    la_lavd_fwd (FLAG_LD_LOGSIGMOID reaches the state-only pass too).  Returns (o, final states per
-    document)."""
+    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32 (or 16-bit with FLAG_LD_16BIT), all
+    contiguous; flags as for la_lavd_fwd (the decay flags reach the state-only pass too).  Returns (o, final states per
+    document, states entering the segments)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
     s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False,
-                                act=flags & _lib.FLAG_LD_LOGSIGMOID)
+                                act=flags & (_lib.FLAG_LD_LOGSIGMOID | _lib.FLAG_LD_16BIT))
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
     st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
@@ -329,18 +332,21 @@ def lavd_forward_segmented(q, k, v, ldk, initial_state, doc_bounds, cap, flags):
                              _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
                              _lib.dtype_code(q), flags, _lib.stream_of(q))
         _lib.check(rc, "la_lavd_fwd (segmented)")
-    return o, st.index_select(0, pl.last_idx)
+    return o, st.index_select(0, pl.last_idx), s_in
 
 
-def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_bounds, cap, want_ds0, flags):
-    """Backward twin.  Returns (dq, dk, dv, dldk (1,T,H,128) fp32, dinitial_state (ndocs,...) or None)."""
+def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_bounds, cap, want_ds0, flags,
+                            s_in=None):
+    """Backward twin (s_in: the forward's segment-entering states if it kept them).
+    Returns (dq, dk, dv, dldk (1,T,H,128) fp32, dinitial_state (ndocs,...) or None)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    act = flags & _lib.FLAG_LD_LOGSIGMOID
-    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False, act=act)
+    act = flags & (_lib.FLAG_LD_LOGSIGMOID | _lib.FLAG_LD_16BIT)
+    if s_in is None:
+        s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False, act=act)
     ds_out = _incoming_states_vec(lib, q, do, ldk, pl, dfinal_state, reverse=True, act=act)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dldk = torch.empty(1, t, h, d, dtype=torch.float32, device=dev)

@@ -99,7 +99,7 @@ def _cuda_local_forward(q, k, v, ld, local_cu):
         ld32, strides = _prep_ld(ld, 1, t, h)
         with torch.no_grad():
             return sg.lasd_forward_segmented(q.contiguous(), k.contiguous(), v.contiguous(), ld32, strides,
-                                             None, bounds, cap)
+                                             None, bounds, cap)[:2]
     cu = torch.tensor(local_cu, dtype=torch.int64, device=q.device)
     with torch.no_grad():
         return lasd_fn(q, k, v, ld, cu_seqlens=cu)

@@ -32,6 +32,18 @@ def _ld32(x):
     return (x if x.dtype == torch.float32 else x.float()).contiguous()
 
 
+def _prep_decays(q, ldk, ldv):
+    """The decays as the library reads them, and the flag that says how: contiguous fp32, or - when
+    every decay given already has q's 16-bit dtype (as in the reference's benchmark,
+    benchmarks/lightning_attention/benchmark.py:315-316) - as they are, read as 16-bit by the
+    kernels (no conversion pass, half the decay traffic)."""
+    given = [x for x in (ldk, ldv) if x is not None]
+    if q.dtype in (torch.bfloat16, torch.float16) and all(x.dtype == q.dtype for x in given):
+        lk, lv = (None if x is None else x.detach().contiguous() for x in (ldk, ldv))
+        return lk, lv, _lib.FLAG_LD_16BIT
+    return _ld32(ldk), _ld32(ldv), 0
+
+
 def _segmentation(lib, q, lk, lv, cu, b, n, h, d, e, flags):
     """Few long sequences on the tensor path (ldk only, D = E = 128): cut every sequence into as many
     segments as keep one CTA per (segment, head) within the SM count, so that the chunk passes fill
@@ -63,15 +75,18 @@ class LavdFunction(torch.autograd.Function):
         if cu is not None and b != 1:
             raise AssertionError("cu_seqlens is only supported for batch size 1")
         nb = m if cu is not None else b
-        lk, lv = _ld32(ldk), _ld32(ldv)
+        lk, lv, f16 = _prep_decays(q, ldk, ldv)
+        flags = flags | f16
         s0 = None if initial_state is None else initial_state.detach().to(torch.float32).contiguous()
         seg = _segmentation(lib, q, lk, lv, cu, b, n, h, d, e, flags)
         if seg is not None:
             from .segmented import lavd_forward_segmented
             bounds, cap = seg
-            o, sf = lavd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e),
-                                           lk.view(1, b * n, h, d), s0, bounds, cap, flags)
-            ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu)
+            o, sf, s_seg = lavd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d),
+                                                  v.view(1, b * n, h, e), lk.view(1, b * n, h, d), s0, bounds, cap,
+                                                  flags)
+            # the states entering the segments (64 KB per segment and head) are kept for the backward
+            ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu, s_seg)
             ctx.flags = flags
             ctx.seg = seg
             ctx.state_dtype = None if initial_state is None else initial_state.dtype
@@ -85,7 +100,7 @@ class LavdFunction(torch.autograd.Function):
                                  _lib.ptr(s0), _lib.ptr(cu), _lib.ptr(o), _lib.ptr(sf),
                                  b, n, h, d, e, m, _lib.dtype_code(q), flags, _lib.stream_of(q))
         _lib.check(rc, "la_lavd_fwd")
-        ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu)
+        ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu, None)
         ctx.flags = flags
         ctx.state_dtype = None if initial_state is None else initial_state.dtype
         ctx.set_materialize_grads(False)
@@ -94,7 +109,7 @@ class LavdFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dfinal_state):
         lib = _lib.load()
-        q, k, v, ldk, ldv, s0, cu = ctx.saved_tensors
+        q, k, v, ldk, ldv, s0, cu, s_seg = ctx.saved_tensors
         b, n, h, d = q.shape
         e = v.shape[-1]
         m = 0 if cu is None else cu.numel() - 1
@@ -103,14 +118,14 @@ class LavdFunction(torch.autograd.Function):
             do = torch.zeros(b, n, h, e, dtype=q.dtype, device=q.device)
         do = do.contiguous().to(q.dtype)
         dsf = None if dfinal_state is None else dfinal_state.to(torch.float32).contiguous()
-        lk, lv = _ld32(ldk), _ld32(ldv)
+        lk, lv, _ = _prep_decays(q, ldk, ldv)
         want_ds0 = s0 is not None and ctx.needs_input_grad[5]
         if ctx.seg is not None:
             from .segmented import lavd_backward_segmented
             bounds, cap = ctx.seg
             dq, dk, dv, dldk, ds0 = lavd_backward_segmented(
                 q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), lk.view(1, b * n, h, d), s0,
-                do.view(1, b * n, h, e), dsf, bounds, cap, want_ds0, ctx.flags)
+                do.view(1, b * n, h, e), dsf, bounds, cap, want_ds0, ctx.flags, s_in=s_seg)
             if want_ds0:
                 ds0 = ds0.to(ctx.state_dtype)
             return (dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e),
