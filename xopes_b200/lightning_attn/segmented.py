@@ -70,14 +70,17 @@ def plan_segments(doc_bounds: List[Tuple[int, int]], cap: int):
 
 def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
     """Segmenting pays a state-only pass over all but the last segment of every cut sequence
-    (512 B per token and head on top of 1,024) and two small launches, so it is used when the plain
-    launch would leave most SMs idle or one sequence would run at least twice as long as a
-    balanced share."""
+    (512 B per token and head on top of 1,024) and two small launches; only sequences longer than
+    `cap` (one balanced share of the launch) are cut.  With few (sequence, head) pairs, where the
+    plain launch gives one CTA to each pair, it is used once a sequence is longer than 1.5 shares.
+    With more pairs the plain launch splits the chunk space evenly over the CTAs, and a sequence
+    longer than one share then spans three of them: the middle one cannot start before the first
+    has finished its part, so any such sequence is cut."""
     ctas = len(doc_bounds) * h
     longest = max(b - a for a, b in doc_bounds)
     if ctas <= sms // 4:
         return longest > cap + cap // 2
-    return ctas <= 2 * sms and longest > cap + cap // 4
+    return longest > cap
 
 
 class _Plan:
