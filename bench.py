@@ -259,9 +259,10 @@ class LasdStep:
 
 class LavdStep(LasdStep):
     # forward: state-only pass, fold, chunk pass, and two launches that only run if the decay leaves
-    # the range of the one before (two-reference chunk pass, scan); backward: 2 state-only passes,
-    # 2 folds, 3 chunk passes, 3 + 3 such conditional launches, 1 reverse cumulative sum
-    launches_per_step = 19
+    # the range of the one before (two-reference chunk pass, scan); backward: 1 state-only pass
+    # (reverse flow; the forward-flow states are kept from the forward), 1 fold, 3 chunk passes,
+    # 3 + 3 such conditional launches, 1 reverse cumulative sum
+    launches_per_step = 17
     main_launches = 4      # o, dq, dk, dv chunk passes
     kernel = "lavd_pass_kernel"
 
@@ -361,9 +362,9 @@ class VarlenStep:
         self.d["ld"] = self.d["ld"].to(dev)
         self.cu_host = w["cu_seqlens"]
         self.cu = self.cu_host.to(dev)
-        # one GPU: per-document weight prefix + chunk pass; a rank: state-only pass, fold, weight
-        # prefix, chunk pass, the fold of the gathered summaries and the correction (NCCL's own
-        # kernel is not counted)
+        # one GPU: per-document weight prefix + chunk pass; a rank: state-only pass, fold of the open
+        # document's pieces, fold of the gathered summaries, fold over all pieces, weight prefix,
+        # chunk pass (NCCL's own kernel is not counted)
         self.launches_per_step = 2 if world == 1 else 6
         self.main_launches = 1
         self.last = None

@@ -60,8 +60,8 @@ enum la_dtype { LA_F32 = 0, LA_BF16 = 1, LA_F16 = 2 };
  * benchmark passes, benchmarks/lightning_attention/benchmark.py:315-316) although the parameters
  * are declared `const float *`; the kernels widen them where they read them, so the decay tensor
  * costs 2 bytes per value in every pass instead of a conversion pass plus 4.  dldk / dldv stay
- * fp32.  Rejected with LA_ERR_UNSUPPORTED for fp32 inputs.  The decode entry points take fp32
- * decays only. */
+ * fp32.  Rejected with LA_ERR_UNSUPPORTED for fp32 inputs and by the scalar-decay entry points
+ * (ld is always fp32).  The decode entry points take fp32 decays only. */
 #define LA_FLAG_LD_16BIT 8u
 
 /* Library identification; bumps when the ABI changes. */

@@ -87,6 +87,13 @@ def test_argument_checks_return_codes_without_a_gpu(lib):
     rc = lib.la_lavd_fwd(one, one, one, None, None, None, None, one, None,
                          1, 4, 2, 8, 8, 0, _lib.LA_F32, 0, None)
     assert rc == -1
+    # 16-bit decays: only with 16-bit q, k, v, and only for the vector decay
+    rc = lib.la_lavd_fwd(one, one, one, one, None, None, None, one, None,
+                         1, 4, 2, 8, 8, 0, _lib.LA_F32, _lib.FLAG_LD_16BIT, None)
+    assert rc == -3
+    rc = lib.la_lasd_fwd(one, one, one, one, 0, 0, 1, None, None, one, None,
+                         1, 4, 2, 8, 8, 0, _lib.LA_BF16, _lib.FLAG_LD_16BIT, None)
+    assert rc == -3
     # dld requested without workspace
     rc = lib.la_lasd_bwd(one, one, one, one, 0, 0, 1, None, one, None, None, one, one, one, one,
                          None, None, 0, 1, 4, 2, 8, 8, 0, _lib.LA_F32, 0, None)

@@ -229,6 +229,7 @@ int la_lasd_fwd(const void *q, const void *k, const void *v, const float *ld, in
   int rc = check_common(q, k, v, B, N, H, D, E, M, cu_seqlens, dtype);
   if (rc != LA_OK) return rc;
   if (o == nullptr || ld == nullptr) return LA_ERR_NULL_POINTER;
+  if (flags & LA_FLAG_LD_16BIT) return LA_ERR_UNSUPPORTED;  // the scalar decay is always fp32
   const int path = la_lasd_path(N, D, E, dtype, flags);
   if (path < 0) return path;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -273,6 +274,7 @@ static int lasd_bwd_impl(const void *q, const void *k, const void *v, const floa
   if (rc != LA_OK) return rc;
   if (d_o == nullptr || dq == nullptr || dk == nullptr || dv == nullptr || ld == nullptr)
     return LA_ERR_NULL_POINTER;
+  if (flags & LA_FLAG_LD_16BIT) return LA_ERR_UNSUPPORTED;  // the scalar decay is always fp32
   const int path = la_lasd_path(N, D, E, dtype, flags);
   if (path < 0) return path;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -661,6 +663,7 @@ int la_lasd_state_pass(const void *y, const void *z, const float *ld, int64_t ld
   if (rc != LA_OK) return rc;
   if (ld == nullptr || states == nullptr) return LA_ERR_NULL_POINTER;
   if (D != 128 || E != 128 || !(dtype == LA_BF16 || dtype == LA_F16)) return LA_ERR_UNSUPPORTED;
+  if (flags & LA_FLAG_LD_16BIT) return LA_ERR_UNSUPPORTED;  // the scalar decay is always fp32
   StatePass p;
   p.y = y; p.z = z; p.ld = ld; p.ld_sb = ld_sb; p.ld_sn = ld_sn; p.ld_sh = ld_sh; p.cu = cu_seqlens;
   p.states = states; p.gsum = gsum; p.B = (int)B; p.N = (int)N; p.H = (int)H; p.M = (int)M; p.reverse = reverse != 0;
