@@ -167,7 +167,7 @@ LA_API int la_lasd_bwd_noalloc(const void *q, const void *k, const void *v, cons
  * ------------------------------------------------------------------------------------------- */
 
 /* Which kernel family a vector-decay call runs: 1 = tcgen05/TMA chunk kernels (16-bit inputs,
- * D = E = 128, N >= 128, ldk only), 0 = fp32 scan kernels.  On path 1 the decay decides, on the
+ * D = E = 128, N >= 128, exactly one of ldk / ldv), 0 = fp32 scan kernels.  On path 1 the decay decides, on the
  * device, how far the call gets: the one-reference kernels handle chunks whose halves (64 tokens)
  * decay by at most 2^-64 per feature (bf16; 2^-10 for fp16); if a chunk exceeds that, the
  * two-reference kernels rerun the call (safe while every 32-token quarter decays by at most 2^-96;

@@ -309,6 +309,57 @@ def test_lavd_tensor_path(shape, lens, regime, dtype, lib):
     assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("regime", ["weak", "reference_benchmark", "strong"])
+@pytest.mark.parametrize("shape,lens", [((2, 384, 2), None), ((1, 300, 3), None),
+                                        ((1, 700, 2), [1, 127, 128, 129, 300, 15]), ((1, 2048, 2), None)])
+def test_lavd_value_decay_on_the_tensor_path(shape, lens, regime, dtype, lib):
+    """Vector decay on the value features only (ldv, no ldk), D = E = 128, 16 bit: the same tcgen05
+    kernels with the roles of the passes exchanged (o and dv are the passes with the decay on the
+    output features, dq and dk those with the decay on the contraction).  Same three levels as the
+    key-decay case."""
+    import xopes_b200 as xb
+    from xopes_b200 import _lib
+    b, n, h = shape
+    d = e = 128
+    assert lib.la_lavd_path(n, d, e, _lib.dtype_code(torch.empty(0, dtype=dtype)), 0, 1, 0) == 1
+    assert lib.la_lavd_path(n, d, e, _lib.dtype_code(torch.empty(0, dtype=dtype)), 1, 1, 0) == 0
+    g = torch.Generator().manual_seed(19)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    x = torch.randn(b, n, h, e, generator=g)
+    ldv = {"weak": torch.nn.functional.logsigmoid(x) / 16,
+           "reference_benchmark": torch.nn.functional.logsigmoid(x),
+           "strong": torch.nn.functional.logsigmoid(x * 2 - 4)}[regime]
+    qf = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    kf = cast(torch.randn(b, n, h, d, generator=g))
+    vf = cast((1 - torch.exp(ldv)) * torch.randn(b, n, h, e, generator=g))
+    nb = b if lens is None else len(lens)
+    cu = None if lens is None else torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    s0 = 0.1 * torch.randn(nb, h, d, e, generator=g)
+    dof = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = 0.1 * torch.randn(nb, h, d, e, generator=g)
+    q, k, v, lv, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(ldv), leaf(s0)
+    o, sf = xb.lavd_fn(q, k, v, ldv=lv, initial_state=s0c, cu_seqlens=None if cu is None else cu.to(DEV))
+    flag_fwd = _lavd_unsafe_flag(lib)
+    ro, rsf = orc.lavd_forward(qf, kf, vf, None, ldv, s0, cu)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    flag_bwd = _lavd_unsafe_flag(lib)
+    if regime == "weak":
+        assert flag_fwd == 0 and flag_bwd == 0
+    if regime == "reference_benchmark" and dtype == torch.bfloat16:
+        assert flag_fwd <= 1 and flag_bwd <= 1, "logsigmoid(N(0,1)) decays must stay on the tensor cores"
+    if regime == "strong":
+        assert flag_fwd == 2 and flag_bwd == 2, "out-of-range decays must fall back to the scan"
+    rq, rk, rv, _, rlv, rs0 = orc.lavd_backward(qf, kf, vf, None, ldv, dof, s0, dsf, cu)
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    assert_close("dldv", rlv, lv.grad, TOL_BF16)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)
+
+
 def test_lavd_benchmark_length_slice():
     """A (B=1, H=2) slice of benchmark configuration 3 at its full length N = 16384 (bf16,
     ldk = logsigmoid(x)/16, k = (1 - exp(ldk)) k_raw, no initial state): every gradient the

@@ -446,6 +446,12 @@ int la_lavd_fwd(const void *q, const void *k, const void *v, const float *ldk, c
     if (cudaMemsetAsync(unsafe, 0, 2 * sizeof(int), st) != cudaSuccess) return LA_ERR_CUDA;
     LavdPass c;
     c.x = q; c.y = k; c.z = v; c.ldk = ldk; c.out = o; c.t0 = initial_state; c.tfinal = final_state;
+    if (ldk == nullptr) {
+      // decay on the value features: o_i[e] = sum_j (q_i . k_j) exp(cv_i[e] - cv_j[e]) v_j[e] has the
+      // shape of the dq pass of the key-decay case (decay on the features of Z and of the output),
+      // with the state in its natural layout
+      c.ldk = ldv; c.tmode = 1; c.state_transposed = 0;
+    }
     c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
     c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
     c.ld16 = ld16;
@@ -498,6 +504,36 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     c.ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;
     c.ld16 = ld16;
     c.ldk = ldk; c.B = s.B; c.N = s.N; c.H = s.H; c.M = s.M; c.cu = cu_seqlens; c.unsafe = unsafe;
+    if (ldk == nullptr) {
+      // Decay on the value features (ldv only): the four passes exchange roles with the key-decay
+      // case.  The decay now sits on the features of v, do, o and dv, so
+      //   o  (recomputed for the term o * do of dldv) and dv are T-mode passes (decay on Z and on
+      //      the output), the state in its natural layout;
+      //   dq and dk are N-mode passes (decay on the contraction of X Y^T), the state transposed.
+      // All on the caller's stream, in an order that lets the recomputed o use the dv buffer as its
+      // scratch output before the dv pass overwrites it.
+      c.ldk = ldv;
+      LavdPass po = c;  // o again: (q, k, v), forward; dldv = o * do; its end state feeds the state term
+      po.x = q; po.y = k; po.z = v; po.out = dv; po.tmode = 1; po.state_transposed = 0; po.reverse = 0;
+      po.t0 = initial_state; po.tfinal = ws_state; po.xrow = d_o; po.dld = dldv; po.dld_sub = 0;
+      LavdPass pv = po;  // dv: (k, q, do), reverse; dldv -= v * dv; its end state is d initial_state
+      pv.x = k; pv.y = q; pv.z = d_o; pv.out = dv; pv.reverse = 1;
+      pv.t0 = dfinal_state; pv.tfinal = dinitial_state; pv.xrow = v; pv.dld_sub = 1;
+      LavdPass pq = c;   // dq: (do, v, k), forward, state S^T
+      pq.x = d_o; pq.y = v; pq.z = k; pq.out = dq; pq.tmode = 0; pq.state_transposed = 1; pq.reverse = 0;
+      pq.t0 = initial_state; pq.tfinal = nullptr; pq.xrow = nullptr; pq.dld = nullptr;
+      LavdPass pk = pq;  // dk: (v, do, q), reverse, state dS^T
+      pk.x = v; pk.y = d_o; pk.z = q; pk.out = dk; pk.reverse = 1; pk.t0 = dfinal_state;
+      const LavdPass *order[4] = {&po, &pv, &pq, &pk};
+      for (int level = 0; level < 2 && rc == LA_OK; ++level)
+        for (int i = 0; i < 4 && rc == LA_OK; ++i) {
+          LavdPass x = *order[i];
+          if (level == 1) { x.ref2 = 1; x.enable = unsafe; x.unsafe = unsafe + 1; }
+          rc = launch_lavd_pass(x, dtype, st);
+        }
+      if (rc != LA_OK) return rc;
+      enable = unsafe + 1;
+    } else {
     // dv: (k, q, do), state dS, reverse; its end state is d initial_state.  It shares nothing
     // with the other two passes, so while one CTA per (sequence, head) leaves SMs idle it runs
     // beside them on a side stream.
@@ -563,6 +599,7 @@ int la_lavd_bwd(const void *q, const void *k, const void *v, const float *ldk, c
     }
     if (rc != LA_OK) return rc;
     enable = unsafe + 1;
+    }  // key decay
   }
   ScanParams p;
   const int ld_act = (flags & LA_FLAG_LD_LOGSIGMOID) ? 1 : 0;

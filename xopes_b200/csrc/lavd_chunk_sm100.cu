@@ -1121,7 +1121,9 @@ int launch_t(const LavdPass &p, int dtype, cudaStream_t stream) {
 }  // namespace
 
 bool lavd_chunk_supported(int64_t N, int64_t D, int64_t E, int dtype, bool has_ldk, bool has_ldv) {
-  return has_ldk && !has_ldv && (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
+  // exactly one decay: on the key features (ldk) or, by exchanging the roles of the passes, on the
+  // value features (ldv); both at once would need a second 64 KB decay tile per chunk
+  return (has_ldk != has_ldv) && (dtype == LA_BF16 || dtype == LA_F16) && D == 128 && E == 128 && N >= 128;
 }
 
 int launch_lavd_pass(const LavdPass &p, int dtype, cudaStream_t stream) {
