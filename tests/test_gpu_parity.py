@@ -579,3 +579,52 @@ def test_constant_decay_default_path_with_learnable_decay_and_no_decay():
     ro0, rs0 = orc.lasd_forward(qf, kf, vf, torch.zeros(b, n, h))
     assert_close("o (no decay)", ro0, o0, TOL_FP32)
     assert_close("state (no decay)", rs0, s0, TOL_FP32)
+
+
+@pytest.mark.parametrize("shape,which,lens,act", [
+    ((2, 384, 2, 64, 64), "ldk", None, False),
+    ((1, 300, 3, 64, 32), "ldk", None, True),
+    ((2, 256, 2, 128, 64), "ldv", None, False),
+    ((1, 700, 2, 96, 128), "ldk", [1, 127, 128, 129, 300, 15], False),
+])
+def test_lavd_narrow_heads_run_padded_on_the_tensor_path(shape, which, lens, act, lib):
+    """Vector decay with head dimensions below 128 in 16 bit: the operands are zero-padded to the
+    128-wide tiles of the tcgen05 kernels and the results cut back (the scan kernels are not
+    involved: level 0)."""
+    import xopes_b200 as xb
+    b, n, h, d, e = shape
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(23)
+    cast = lambda t: t.to(dtype).float()  # noqa: E731
+    f = d if which == "ldk" else e
+    x = torch.randn(b, n, h, f, generator=g) + (3.0 if act else 0.0)
+    ld = torch.nn.functional.logsigmoid(x.double()).float() if act else torch.nn.functional.logsigmoid(x) / 16
+    qf = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    kf = cast(torch.randn(b, n, h, d, generator=g) * d ** -0.5)
+    vf = cast(torch.randn(b, n, h, e, generator=g))
+    nb = b if lens is None else len(lens)
+    cu = None if lens is None else torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    s0 = 0.1 * torch.randn(nb, h, d, e, generator=g)
+    dof = cast(torch.randn(b, n, h, e, generator=g))
+    dsf = 0.1 * torch.randn(nb, h, d, e, generator=g)
+    q, k, v, lc, s0c = leaf(qf, dtype), leaf(kf, dtype), leaf(vf, dtype), leaf(x if act else ld), leaf(s0)
+    kw = {which: lc}
+    o, sf = xb.lavd_fn(q, k, v, initial_state=s0c, cu_seqlens=None if cu is None else cu.to(DEV),
+                       decay_activation="logsigmoid" if act else None, **kw)
+    assert tuple(o.shape) == (b, n, h, e) and tuple(sf.shape) == (nb, h, d, e)
+    assert _lavd_unsafe_flag(lib) == 0
+    ldk, ldv = (ld, None) if which == "ldk" else (None, ld)
+    ro, rsf = orc.lavd_forward(qf, kf, vf, ldk, ldv, s0, cu)
+    assert_close("o", ro, o.float(), TOL_BF16)
+    assert_close("final_state", rsf, sf, TOL_BF16)
+    ((o.float() * dof.to(DEV)).sum() + (sf * dsf.to(DEV)).sum()).backward()
+    rq, rk, rv, rlk, rlv, rs0 = orc.lavd_backward(qf, kf, vf, ldk, ldv, dof, s0, dsf, cu)
+    assert_close("dq", rq, q.grad.float(), TOL_BF16)
+    assert_close("dk", rk, k.grad.float(), TOL_BF16)
+    assert_close("dv", rv, v.grad.float(), TOL_BF16)
+    rl = rlk if which == "ldk" else rlv
+    if act:
+        rl = (rl.double() * torch.sigmoid(-x.double())).float()
+    assert tuple(lc.grad.shape) == (b, n, h, f)
+    assert_close("dld", rl, lc.grad, TOL_BF16)
+    assert_close("dinitial_state", rs0, s0c.grad, TOL_BF16)

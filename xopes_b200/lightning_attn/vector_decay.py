@@ -170,7 +170,33 @@ def _lavd(q, k, v, ldk, ldv, initial_state, cu_seqlens, flags):
     b = q.shape[0]
     nb = cu_seqlens.shape[0] - 1 if cu_seqlens is not None else b
     s0 = _prep_state(initial_state, nb, q.shape[2], q.shape[3], v.shape[3])
+    d, e = q.shape[3], v.shape[3]
+    if _pad_to_tensor_path(q, d, e, ldk, ldv, flags):
+        # Narrow heads: the tensor-core kernels work on 128-wide tiles, the scan kernels that would
+        # serve these shapes cost ~40x more per token at this size.  Zero features add nothing to any
+        # product and a zero log decay leaves them alone, so the operands are padded to 128 features
+        # here (one extra pass over each) and the results cut back; autograd carries the gradients
+        # through the padding and the slices.
+        pd, pe = 128 - d, 128 - e
+        fill = 80.0 if (flags & _lib.FLAG_LD_LOGSIGMOID) else 0.0   # logsigmoid(80) = 0 in fp32
+        pad = torch.nn.functional.pad
+        qp, kp, vp = pad(q, (0, pd)), pad(k, (0, pd)), pad(v, (0, pe))
+        lkp = None if ldk is None else pad(ldk, (0, pd), value=fill)
+        lvp = None if ldv is None else pad(ldv, (0, pe), value=fill)
+        s0p = None if s0 is None else pad(s0, (0, pe, 0, pd))
+        o, sf = LavdFunction.apply(qp, kp, vp, lkp, lvp, s0p, cu_seqlens, flags)
+        return o[..., :e], sf[..., :d, :e]
     return LavdFunction.apply(q, k, v, ldk, ldv, s0, cu_seqlens, flags)
+
+
+def _pad_to_tensor_path(q, d, e, ldk, ldv, flags) -> bool:
+    """16-bit inputs with head dimensions below 128 (and D * E >= 2048: below that the scan kernels
+    are no slower), one decay, at least one chunk of tokens: worth padding to the 128-wide tiles."""
+    if (flags & _lib.FLAG_FORCE_RECURRENCE) or q.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    if (ldk is None) == (ldv is None) or q.shape[1] < 128:
+        return False
+    return d <= 128 and e <= 128 and (d, e) != (128, 128) and d * e >= 2048
 
 
 def lavd_parallel_cuda(q: torch.Tensor, k: Optional[torch.Tensor] = None,
