@@ -716,6 +716,32 @@ def measure_lasd_shape(b, n, h, dev, steps, world, seed=0):
     return ms_f / steps, ms_fb / steps
 
 
+def measure_lavd_variants(b, n, h, dev, steps, world, seed=0):
+    """fwd+bwd ms of two more vector-decay calls at configuration 3's shape: the decay on the value
+    features only (ldv: the tensor-core passes with their roles exchanged) and ldk given in bf16
+    (read as 16-bit by the kernels).  Maximum over ranks."""
+    import xopes_b200 as xb
+    from xopes_b200 import workloads as W
+    quiet_cpu()
+    w = W.lavd_inputs(b, n, h, 128, 128, torch.bfloat16, seed)
+    d = {k: v.to(dev) for k, v in w.items()}
+    q, k, v = (d[x].requires_grad_() for x in ("q", "k", "v"))
+    out = {}
+    for name, kw in (("ldv_only", {"ldv": d["ldk"].clone().requires_grad_()}),
+                     ("ldk_bf16", {"ldk": d["ldk"].bfloat16().requires_grad_()})):
+        def fb():
+            o, _ = xb.lightning_attn_func(q, k, v, decay_type="vector", **kw)
+            o.backward(d["do"])
+            q.grad = k.grad = v.grad = None
+            for t in kw.values():
+                t.grad = None
+        ms, _ = time_steps(fb, steps, 3, world)
+        out[name + "_fwd_bwd_ms"] = ms / steps
+    del d, w
+    torch.cuda.empty_cache()
+    return out
+
+
 def measure_c5_single_gpu(args, rank, world, dev):
     """The whole configuration-5 stream on rank 0's GPU alone (the other ranks wait), so that a
     multi-GPU line carries the one-GPU time it is compared with."""
@@ -786,6 +812,8 @@ def main():
                 "fwd_ms": f, "bwd_ms": fb - f, "fwd_bwd_ms": fb,
                 "reference_published_A100_ms": {"fwd": 1.2220, "bwd": 4.1736,
                                                 "source": "benchmarks/lightning_attention/README.md:112,123"}}
+        if "rows" in want:
+            secondary["lavd_variants_B4_N16384_H16"] = measure_lavd_variants(4, 16384, 16, dev, steps2, world)
         # configuration 2 partitioned by batch x head over the ranks (strong scaling): every rank
         # takes B / N of the batches of the same global problem
         if cfg["B"] % world == 0 and "rows" in want:
