@@ -1118,7 +1118,7 @@ int launch_t(const ChunkPass &p, const ChunkPass *q, int dtype, cudaStream_t str
   sc.flags = nullptr;
   long long grid = pairs * npass;
   void *scratch = nullptr;
-  // Worth it when whole pairs per CTA would leave SMs idle in the last round (always the case
+  // Worth it when whole pairs per CTA would leave SMs idle in the last wave (always the case
   // with ragged documents).
   if (!p.no_scratch && ranges > 0 && pairs > ranges && (p.cu != nullptr || pairs % ranges != 0)) {
     // even split of the chunk space over one CTA per SM
