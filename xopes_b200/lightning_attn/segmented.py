@@ -317,31 +317,50 @@ def _incoming_states_vec(lib, y, z, ldk, pl: _Plan, ext, reverse: bool, act: int
     return incoming
 
 
-def lavd_forward_segmented(q, k, v, ldk, initial_state, doc_bounds, cap, flags):
-    """q, k, v (1, T, H, 128) 16-bit, ldk (1, T, H, 128) fp32 (or 16-bit with FLAG_LD_16BIT), all
-    contiguous; flags as for la_lavd_fwd (the decay flags reach the state-only pass too).  Returns (o, final states per
-    document, states entering the segments)."""
+def _tr(x):
+    """(.., D, E) -> contiguous (.., E, D), None passes through."""
+    return None if x is None else x.transpose(-1, -2).contiguous()
+
+
+def _seg_states_vec(lib, q, k, v, do, ld, pl, ext, reverse, act, value_decay):
+    """States entering the segments for the vector decay `ld`.  Key decay: the state-only pass runs on
+    (k, v) (forward flow) or (q, do) (reverse flow) and decays the features of its first operand.
+    Value decay: the decayed features are those of v / do, so the operands are exchanged, the pass
+    yields transposed states, and the (small) state tensors are transposed on the way in and out."""
+    if not value_decay:
+        y, z = (q, do) if reverse else (k, v)
+        return _incoming_states_vec(lib, y, z, ld, pl, ext, reverse, act)
+    y, z = (do, q) if reverse else (v, k)
+    return _tr(_incoming_states_vec(lib, y, z, ld, pl, _tr(ext), reverse, act))
+
+
+def lavd_forward_segmented(q, k, v, ld, initial_state, doc_bounds, cap, flags, value_decay=False):
+    """q, k, v (1, T, H, 128) 16-bit, ld (1, T, H, 128) the one vector decay - ldk, or ldv with
+    value_decay=True - fp32 (or 16-bit with FLAG_LD_16BIT), all contiguous; flags as for la_lavd_fwd
+    (the decay flags reach the state-only pass too).  Returns (o, final states per document, states
+    entering the segments)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
     dev = q.device
     pl = _plan(doc_bounds, cap, dev, h)
-    s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False,
-                                act=flags & (_lib.FLAG_LD_LOGSIGMOID | _lib.FLAG_LD_16BIT))
+    act = flags & (_lib.FLAG_LD_LOGSIGMOID | _lib.FLAG_LD_16BIT)
+    s_in = _seg_states_vec(lib, q, k, v, None, ld, pl, initial_state, False, act, value_decay)
     o = torch.empty(1, t, h, e, dtype=q.dtype, device=dev)
     st = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev)
+    lk, lv = (None, ld) if value_decay else (ld, None)
     with torch.cuda.device(dev):
-        rc = lib.la_lavd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ldk), None, _lib.ptr(s_in),
+        rc = lib.la_lavd_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lk), _lib.ptr(lv), _lib.ptr(s_in),
                              _lib.ptr(pl.cu_dev), _lib.ptr(o), _lib.ptr(st), 1, t, h, d, e, pl.nseg,
                              _lib.dtype_code(q), flags, _lib.stream_of(q))
         _lib.check(rc, "la_lavd_fwd (segmented)")
     return o, st.index_select(0, pl.last_idx), s_in
 
 
-def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_bounds, cap, want_ds0, flags,
-                            s_in=None):
+def lavd_backward_segmented(q, k, v, ld, initial_state, do, dfinal_state, doc_bounds, cap, want_ds0, flags,
+                            s_in=None, value_decay=False):
     """Backward twin (s_in: the forward's segment-entering states if it kept them).
-    Returns (dq, dk, dv, dldk (1,T,H,128) fp32, dinitial_state (ndocs,...) or None)."""
+    Returns (dq, dk, dv, gradient of the decay (1,T,H,128) fp32, dinitial_state (ndocs,...) or None)."""
     lib = _lib.load()
     _, t, h, d = q.shape
     e = v.shape[-1]
@@ -349,19 +368,21 @@ def lavd_backward_segmented(q, k, v, ldk, initial_state, do, dfinal_state, doc_b
     pl = _plan(doc_bounds, cap, dev, h)
     act = flags & (_lib.FLAG_LD_LOGSIGMOID | _lib.FLAG_LD_16BIT)
     if s_in is None:
-        s_in = _incoming_states_vec(lib, k, v, ldk, pl, initial_state, reverse=False, act=act)
-    ds_out = _incoming_states_vec(lib, q, do, ldk, pl, dfinal_state, reverse=True, act=act)
+        s_in = _seg_states_vec(lib, q, k, v, do, ld, pl, initial_state, False, act, value_decay)
+    ds_out = _seg_states_vec(lib, q, k, v, do, ld, pl, dfinal_state, True, act, value_decay)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    dldk = torch.empty(1, t, h, d, dtype=torch.float32, device=dev)
+    dld = torch.empty(1, t, h, ld.shape[-1], dtype=torch.float32, device=dev)
     ds0 = torch.empty(pl.nseg, h, d, e, dtype=torch.float32, device=dev) if want_ds0 else None
     ws_bytes = lib.la_lavd_bwd_workspace_bytes(1, t, h, d, e, pl.nseg)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    lk, lv = (None, ld) if value_decay else (ld, None)
+    dlk, dlv = (None, dld) if value_decay else (dld, None)
     with torch.cuda.device(dev):
-        rc = lib.la_lavd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ldk), None, _lib.ptr(s_in),
+        rc = lib.la_lavd_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(lk), _lib.ptr(lv), _lib.ptr(s_in),
                              _lib.ptr(do), _lib.ptr(ds_out), _lib.ptr(pl.cu_dev), _lib.ptr(dq), _lib.ptr(dk),
-                             _lib.ptr(dv), _lib.ptr(dldk), None, _lib.ptr(ds0), _lib.ptr(ws), ws_bytes, 1, t, h, d, e,
-                             pl.nseg, _lib.dtype_code(q), flags, _lib.stream_of(q))
+                             _lib.ptr(dv), _lib.ptr(dlk), _lib.ptr(dlv), _lib.ptr(ds0), _lib.ptr(ws), ws_bytes,
+                             1, t, h, d, e, pl.nseg, _lib.dtype_code(q), flags, _lib.stream_of(q))
         _lib.check(rc, "la_lavd_bwd (segmented)")
     if want_ds0:
         ds0 = ds0.index_select(0, pl.first_idx)
-    return dq, dk, dv, dldk, ds0
+    return dq, dk, dv, dld, ds0

@@ -45,13 +45,13 @@ def _prep_decays(q, ldk, ldv):
 
 
 def _segmentation(lib, q, lk, lv, cu, b, n, h, d, e, flags):
-    """Few long sequences on the tensor path (ldk only, D = E = 128): cut every sequence into as many
+    """Few long sequences on the tensor path (one decay, D = E = 128): cut every sequence into as many
     segments as keep one CTA per (segment, head) within the SM count, so that the chunk passes fill
     the GPU (xopes_b200/lightning_attn/segmented.py).  Returns (bounds, cap) or None."""
     from . import segmented as sg
-    if cu is not None or lk is None or lv is not None or d != 128 or e != 128:
+    if cu is not None or (lk is None) == (lv is None) or d != 128 or e != 128:
         return None
-    if lib.la_lavd_path(n, d, e, _lib.dtype_code(q), 1, 0, flags) != 1:
+    if lib.la_lavd_path(n, d, e, _lib.dtype_code(q), int(lk is not None), int(lv is not None), flags) != 1:
         return None
     parts = sg.num_sms(q.device) // max(1, b * h)
     if parts < 2 or n < 2 * 1024:
@@ -82,9 +82,10 @@ class LavdFunction(torch.autograd.Function):
         if seg is not None:
             from .segmented import lavd_forward_segmented
             bounds, cap = seg
+            ld1 = lk if lk is not None else lv   # the one decay given (D = E here)
             o, sf, s_seg = lavd_forward_segmented(q.view(1, b * n, h, d), k.view(1, b * n, h, d),
-                                                  v.view(1, b * n, h, e), lk.view(1, b * n, h, d), s0, bounds, cap,
-                                                  flags)
+                                                  v.view(1, b * n, h, e), ld1.view(1, b * n, h, d), s0, bounds, cap,
+                                                  flags, value_decay=lk is None)
             # the states entering the segments (64 KB per segment and head) are kept for the backward
             ctx.save_for_backward(q, k, v, ldk, ldv, s0, cu, s_seg)
             ctx.flags = flags
@@ -123,13 +124,15 @@ class LavdFunction(torch.autograd.Function):
         if ctx.seg is not None:
             from .segmented import lavd_backward_segmented
             bounds, cap = ctx.seg
-            dq, dk, dv, dldk, ds0 = lavd_backward_segmented(
-                q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), lk.view(1, b * n, h, d), s0,
-                do.view(1, b * n, h, e), dsf, bounds, cap, want_ds0, ctx.flags, s_in=s_seg)
+            ld1 = lk if lk is not None else lv
+            dq, dk, dv, dld1, ds0 = lavd_backward_segmented(
+                q.view(1, b * n, h, d), k.view(1, b * n, h, d), v.view(1, b * n, h, e), ld1.view(1, b * n, h, d), s0,
+                do.view(1, b * n, h, e), dsf, bounds, cap, want_ds0, ctx.flags, s_in=s_seg, value_decay=lk is None)
             if want_ds0:
                 ds0 = ds0.to(ctx.state_dtype)
-            return (dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e),
-                    dldk.view(b, n, h, d).to(ldk.dtype), None, ds0, None, None)
+            dld1 = dld1.view(b, n, h, d)
+            dldk, dldv = (dld1.to(ldk.dtype), None) if lk is not None else (None, dld1.to(ldv.dtype))
+            return (dq.view(b, n, h, d), dk.view(b, n, h, d), dv.view(b, n, h, e), dldk, dldv, ds0, None, None)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dldk = None if ldk is None else torch.empty(b, n, h, d, dtype=torch.float32, device=q.device)
         dldv = None if ldv is None else torch.empty(b, n, h, e, dtype=torch.float32, device=q.device)
