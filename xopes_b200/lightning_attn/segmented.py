@@ -79,12 +79,13 @@ def worth_segmenting(doc_bounds, h: int, cap: int, sms: int) -> bool:
     * Few pairs (a quarter of the SMs or fewer): cut once a sequence is longer than 1.5 shares
       (B = 1, H = 16, N = 32768 forward + backward: 0.56 ms against 1.48 ms).
     * In between the plain launch gives one CTA to each pair and lasts as long as its longest
-      sequence, but a CTA that shares HBM with few others moves a chunk faster (measured on B200,
-      microseconds per chunk: 1.6 with 32 CTAs, 2.2 with 64, 3.3 with 128, 3.7 with all 148), so
-      idle SMs cost less than their count suggests and equal-length batches are left alone
-      (48, 96, 128 pairs of N = 8192: cutting loses 7-27 %).  The cut is taken only when the longest
-      sequence makes the plain launch clearly longer than the balanced one, as for the ragged
-      documents of a sequence-parallel rank."""
+      sequence.  A CTA needs about 3 us per chunk at any occupancy, but with few pairs the
+      backward's launches run side by side on two streams, so idle SMs cost a forward + backward
+      step less than their count suggests; the effective cost per chunk and pass below is fitted to
+      measured steps on B200 (1.6 us with 32 pairs, 2.2 with 64, 3.3 with 128, 3.7 with every SM
+      busy).  Equal-length batches are left alone (48, 96, 128 pairs of N = 8192: cutting loses
+      7-27 %); the cut is taken only when the longest sequence makes the plain launch clearly longer
+      than the balanced one, as for the ragged documents of a sequence-parallel rank."""
     chunks = [-(-(b - a) // 128) for a, b in doc_bounds]
     longest = max(chunks)
     if longest * 128 <= cap:
